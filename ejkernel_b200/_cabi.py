@@ -1,0 +1,136 @@
+"""ctypes binding of ``libejk_rpa.so`` (the C ABI declared in ``include/ejk_rpa.h``).
+
+This is the host-side stub a reference maintainer would add for the CUDA platform: it plays
+the role ``jaxlib``'s ``gpu_triton`` custom call plays for the Triton kernels
+(ejkernel/callib/_triton_call.py:36,737-757).  There is no CPU fallback: if the library is
+missing or cannot be loaded the import of the CUDA operator fails loudly.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libejk_rpa.so"
+
+BF16, F16 = 0, 1
+
+ST_NUM_SEQS, ST_QLEN, ST_KVLEN, ST_PAGE_ID, ST_INTERNAL = 1, 2, 4, 8, 16
+STATUS_TEXT = {
+    ST_NUM_SEQS: "num_seqs exceeds block_tables.shape[0]",
+    ST_QLEN: "a sequence has q_len < 0, q_len > kv_len or query rows past total_tokens",
+    ST_KVLEN: "a context length is negative or exceeds pages_per_seq * page_size",
+    ST_PAGE_ID: "a page id outside [0, num_pages) was read from block_tables",
+    ST_INTERNAL: "the device planner ran out of workspace",
+}
+
+EXPORTS = (
+    "ejk_rpa_version",
+    "ejk_rpa_error_string",
+    "ejk_rpa_workspace_bytes",
+    "ejk_rpa_launch",
+    "ejk_rpa_set_option",
+    "ejk_rpa_get_option",
+    "ejk_rpa_last_launch_count",
+)
+
+
+class Shape(Structure):
+    _fields_ = [
+        ("total_tokens", c_int32),
+        ("max_num_seqs", c_int32),
+        ("pages_per_seq", c_int32),
+        ("num_pages", c_int32),
+        ("page_size", c_int32),
+        ("num_q_heads", c_int32),
+        ("num_kv_heads", c_int32),
+        ("head_dim", c_int32),
+        ("dtype", c_int32),
+    ]
+
+
+class Attrs(Structure):
+    _fields_ = [
+        ("softmax_scale", c_float),
+        ("logits_soft_cap", c_float),
+        ("sliding_window", c_int32),
+        ("num_sinks", c_int32),
+        ("sink_rows", c_int32),
+        ("num_kv_pages_per_block", c_int32),
+        ("num_queries_per_block", c_int32),
+    ]
+
+
+class RpaLibraryError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RpaLibraryError(
+            f"{LIB_PATH} is missing: build it with `python -m ejkernel_b200._build` "
+            "(there is no fallback implementation)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    lib.ejk_rpa_version.restype = c_int
+    lib.ejk_rpa_version.argtypes = []
+    lib.ejk_rpa_error_string.restype = c_char_p
+    lib.ejk_rpa_error_string.argtypes = [c_int]
+    lib.ejk_rpa_workspace_bytes.restype = c_size_t
+    lib.ejk_rpa_workspace_bytes.argtypes = [POINTER(Shape)]
+    lib.ejk_rpa_launch.restype = c_int
+    lib.ejk_rpa_launch.argtypes = [
+        c_void_p,  # queries
+        c_void_p,  # kv_pages
+        c_void_p,  # context_lens
+        c_void_p,  # block_tables
+        c_void_p,  # query_start_loc
+        c_void_p,  # num_seqs
+        c_void_p,  # softmax_aux
+        c_void_p,  # out
+        c_void_p,  # workspace
+        c_size_t,
+        c_void_p,  # status
+        POINTER(Shape),
+        POINTER(Attrs),
+        c_void_p,  # stream
+    ]
+    lib.ejk_rpa_set_option.restype = c_int
+    lib.ejk_rpa_set_option.argtypes = [c_char_p, c_int]
+    lib.ejk_rpa_get_option.restype = c_int
+    lib.ejk_rpa_get_option.argtypes = [c_char_p, POINTER(c_int)]
+    lib.ejk_rpa_last_launch_count.restype = c_int
+    lib.ejk_rpa_last_launch_count.argtypes = []
+    _lib = lib
+    return lib
+
+
+def error_string(code: int) -> str:
+    return load().ejk_rpa_error_string(int(code)).decode()
+
+
+def check(code: int, what: str = "ejk_rpa") -> None:
+    if code != 0:
+        raise RpaLibraryError(f"{what} failed with code {code}: {error_string(code)}")
+
+
+def set_option(name: str, value: int) -> None:
+    check(load().ejk_rpa_set_option(name.encode(), int(value)), f"set_option({name})")
+
+
+def get_option(name: str) -> int:
+    v = c_int(0)
+    check(load().ejk_rpa_get_option(name.encode(), ctypes.byref(v)), f"get_option({name})")
+    return v.value
+
+
+def decode_status(word: int) -> list[str]:
+    return [txt for bit, txt in STATUS_TEXT.items() if word & bit]

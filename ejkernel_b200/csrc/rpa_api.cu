@@ -1,0 +1,228 @@
+// C ABI of the ragged paged attention path (declared in include/ejk_rpa.h).
+#include <cmath>
+#include <cstring>
+
+#include "rpa_types.h"
+
+namespace ejk {
+namespace {
+
+struct Options {
+  int waves = 16;
+  int min_chunk = 256;
+  int path = 0;
+};
+Options g_opt;
+thread_local int t_last_launches = 0;
+
+struct DeviceInfo {
+  bool known = false;
+  int sm_count = 0;
+  int cc_major = 0;
+};
+DeviceInfo g_dev[64];
+
+const DeviceInfo* device_info() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  DeviceInfo& d = g_dev[dev];
+  if (!d.known) {
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
+    if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return nullptr;
+    d.known = true;
+  }
+  return &d;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int check_shape(const ejk_rpa_shape* s) {
+  if (!s) return EJK_RPA_E_NULL;
+  if (s->total_tokens <= 0 || s->max_num_seqs <= 0 || s->pages_per_seq <= 0 || s->num_pages <= 0 ||
+      s->page_size <= 0 || s->num_q_heads <= 0 || s->num_kv_heads <= 0)
+    return EJK_RPA_E_SHAPE;
+  if (s->num_q_heads % s->num_kv_heads != 0) return EJK_RPA_E_SHAPE;
+  if (s->head_dim != 64 && s->head_dim != 128 && s->head_dim != 256) return EJK_RPA_E_HEAD_DIM;
+  if (s->dtype != EJK_RPA_BF16 && s->dtype != EJK_RPA_F16) return EJK_RPA_E_DTYPE;
+  if ((long long)s->pages_per_seq * s->page_size > 0x3fffffffLL) return EJK_RPA_E_SHAPE;
+  return 0;
+}
+
+// Everything is sized from static shapes: the planner never needs more than
+//   target_units + max_tiles   work items / partial slots   (sum_t ceil(L_t/C) <= sum L/C + tiles)
+WorkspaceLayout layout_for(const ejk_rpa_shape& s, int n_sm) {
+  WorkspaceLayout L;
+  const int G = s.num_q_heads / s.num_kv_heads;
+  L.rows_per_tile = (G > 8) ? 16 : 8;
+  const long long rows = (long long)s.total_tokens * G;
+  const long long max_tiles = rows / L.rows_per_tile + s.max_num_seqs;
+  const int ctas = n_sm * 2;
+  long long tgt = ((long long)ctas * g_opt.waves + s.num_kv_heads - 1) / s.num_kv_heads;
+  if (tgt < 1) tgt = 1;
+  L.target_units = (int)tgt;
+  L.max_units = (int)(tgt + max_tiles);
+  L.max_merge = (int)max_tiles;
+  L.max_slots = (int)(tgt + max_tiles);
+  size_t off = 0;
+  L.header_off = off;
+  off = align_up(off + kHdrWords * sizeof(int32_t), 256);
+  L.units_off = off;
+  off = align_up(off + (size_t)L.max_units * sizeof(Unit), 256);
+  L.merge_off = off;
+  off = align_up(off + (size_t)L.max_merge * sizeof(MergeItem), 256);
+  L.part_ml_off = off;
+  off = align_up(off + (size_t)L.max_slots * s.num_kv_heads * L.rows_per_tile * sizeof(float2), 256);
+  L.part_o_off = off;
+  off = align_up(off + (size_t)L.max_slots * s.num_kv_heads * L.rows_per_tile * s.head_dim * sizeof(float), 256);
+  L.total = off;
+  return L;
+}
+
+}  // namespace
+}  // namespace ejk
+
+using namespace ejk;
+
+extern "C" {
+
+int ejk_rpa_version(void) { return EJK_RPA_VERSION; }
+
+const char* ejk_rpa_error_string(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case EJK_RPA_E_NULL: return "a required pointer is null";
+    case EJK_RPA_E_SHAPE: return "invalid shape (non-positive dimension, num_q_heads % num_kv_heads != 0, or kv capacity too large)";
+    case EJK_RPA_E_HEAD_DIM: return "head_dim must be 64, 128 or 256";
+    case EJK_RPA_E_DTYPE: return "dtype must be bf16 or f16";
+    case EJK_RPA_E_WORKSPACE: return "workspace too small or not 256-byte aligned";
+    case EJK_RPA_E_ARG: return "invalid attribute (sliding_window, logits_soft_cap, softmax_aux or option name)";
+    case EJK_RPA_E_DEVICE: return "current CUDA device is not an sm_100-class GPU";
+    case EJK_RPA_E_ALIGN: return "queries, kv_pages and out must be 16-byte aligned";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "unknown error code";
+}
+
+size_t ejk_rpa_workspace_bytes(const ejk_rpa_shape* shape) {
+  if (check_shape(shape) != 0) return 0;
+  const DeviceInfo* d = device_info();
+  if (!d) return 0;
+  return layout_for(*shape, d->sm_count).total;
+}
+
+int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* context_lens,
+                   const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
+                   const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
+                   int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
+  t_last_launches = 0;
+  if (!queries || !kv_pages || !context_lens || !block_tables || !query_start_loc || !num_seqs || !out ||
+      !workspace || !shape || !attrs)
+    return EJK_RPA_E_NULL;
+  if (int e = check_shape(shape)) return e;
+  const ejk_rpa_shape& s = *shape;
+  const ejk_rpa_attrs& a = *attrs;
+  if (!(a.softmax_scale == a.softmax_scale) || std::isinf(a.softmax_scale)) return EJK_RPA_E_ARG;
+  if (!(a.logits_soft_cap == a.logits_soft_cap) || std::isinf(a.logits_soft_cap)) return EJK_RPA_E_ARG;
+  if (a.num_sinks < 0 || (a.num_sinks > 0 && !softmax_aux)) return EJK_RPA_E_ARG;
+  if (a.num_sinks > 0 && a.sink_rows != s.num_q_heads && a.sink_rows != s.num_kv_heads && a.sink_rows != 1)
+    return EJK_RPA_E_ARG;
+  if ((reinterpret_cast<uintptr_t>(queries) | reinterpret_cast<uintptr_t>(kv_pages) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return EJK_RPA_E_ALIGN;
+  const DeviceInfo* d = device_info();
+  if (!d) return EJK_RPA_E_DEVICE;
+  if (d->cc_major != 10) return EJK_RPA_E_DEVICE;
+  const WorkspaceLayout L = layout_for(s, d->sm_count);
+  if (workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return EJK_RPA_E_WORKSPACE;
+
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  Params p;
+  std::memset(&p, 0, sizeof(p));
+  p.q = queries;
+  p.kv = kv_pages;
+  p.context_lens = context_lens;
+  p.block_tables = block_tables;
+  p.query_start_loc = query_start_loc;
+  p.num_seqs = num_seqs;
+  p.sinks = softmax_aux;
+  p.out = out;
+  p.header = reinterpret_cast<int32_t*>(ws + L.header_off);
+  p.units = reinterpret_cast<Unit*>(ws + L.units_off);
+  p.merge = reinterpret_cast<MergeItem*>(ws + L.merge_off);
+  p.part_o = reinterpret_cast<float*>(ws + L.part_o_off);
+  p.part_ml = reinterpret_cast<float2*>(ws + L.part_ml_off);
+  p.status = status;
+  p.T = s.total_tokens;
+  p.S_max = s.max_num_seqs;
+  p.pages_per_seq = s.pages_per_seq;
+  p.num_pages = s.num_pages;
+  p.page_size = s.page_size;
+  p.Hq = s.num_q_heads;
+  p.Hkv = s.num_kv_heads;
+  p.G = s.num_q_heads / s.num_kv_heads;
+  p.D = s.head_dim;
+  p.rows_per_tile = L.rows_per_tile;
+  p.max_units = L.max_units;
+  p.max_merge = L.max_merge;
+  p.max_slots = L.max_slots;
+  p.target_units = L.target_units;
+  p.min_chunk = g_opt.min_chunk;
+  p.window = a.sliding_window > 0 ? a.sliding_window : 0;
+  p.num_sinks = a.num_sinks;
+  p.sink_rows = a.sink_rows;
+  const float log2e = 1.4426950408889634f;
+  p.scale = a.softmax_scale;
+  p.scale_log2 = a.softmax_scale * log2e;
+  p.cap = a.logits_soft_cap;
+  p.cap_log2 = a.logits_soft_cap * log2e;
+  p.inv_cap_scale = (a.logits_soft_cap != 0.f) ? a.softmax_scale / a.logits_soft_cap : 0.f;
+  p.page_shift = -1;
+  if ((s.page_size & (s.page_size - 1)) == 0) {
+    int sh = 0;
+    while ((1 << sh) < s.page_size) ++sh;
+    p.page_shift = sh;
+  }
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_plan(p, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  ++t_last_launches;
+  e = launch_splitkv(p, s.dtype, d->sm_count, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  ++t_last_launches;
+  e = launch_merge(p, s.dtype, d->sm_count, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  ++t_last_launches;
+  return 0;
+}
+
+int ejk_rpa_set_option(const char* name, int value) {
+  if (!name) return EJK_RPA_E_NULL;
+  if (!std::strcmp(name, "waves")) {
+    if (value < 1 || value > 4096) return EJK_RPA_E_ARG;
+    g_opt.waves = value;
+  } else if (!std::strcmp(name, "min_chunk")) {
+    if (value < kTileTokens || value % kTileTokens) return EJK_RPA_E_ARG;
+    g_opt.min_chunk = value;
+  } else if (!std::strcmp(name, "path")) {
+    if (value < 0 || value > 2) return EJK_RPA_E_ARG;
+    g_opt.path = value;
+  } else {
+    return EJK_RPA_E_ARG;
+  }
+  return 0;
+}
+
+int ejk_rpa_get_option(const char* name, int* value) {
+  if (!name || !value) return EJK_RPA_E_NULL;
+  if (!std::strcmp(name, "waves")) *value = g_opt.waves;
+  else if (!std::strcmp(name, "min_chunk")) *value = g_opt.min_chunk;
+  else if (!std::strcmp(name, "path")) *value = g_opt.path;
+  else return EJK_RPA_E_ARG;
+  return 0;
+}
+
+int ejk_rpa_last_launch_count(void) { return t_last_launches; }
+
+}  // extern "C"

@@ -1,0 +1,243 @@
+// Device-side planner: turns (context_lens, query_start_loc, num_seqs), which live in device
+// memory and must not be read by the host, into the work list of the split-KV kernel.
+//
+// The reference walks sequences, 8-row query blocks and 64-page KV blocks in nested
+// data-dependent loops (ejkernel/kernels/_xla/ragged_page_attention/_xla_impl_fwd.py:187-201).
+// Here the same iteration space is flattened into (sequence, row tile, KV chunk) items of nearly
+// equal size so that 148 SMs stay evenly loaded when lengths differ by 64x.
+#include "rpa_types.h"
+
+namespace ejk {
+namespace {
+
+constexpr int kPlanThreads = 1024;
+
+struct SeqInfo {
+  int q_start, q_len, kv_len, rows, tiles;
+  bool ok;
+};
+
+__device__ __forceinline__ SeqInfo load_seq(const Params& p, int s, unsigned& flags) {
+  SeqInfo si;
+  int q0 = p.query_start_loc[s];
+  int q1 = p.query_start_loc[s + 1];
+  int kv = p.context_lens[s];
+  const int kv_cap = p.pages_per_seq * p.page_size;
+  if (kv < 0 || kv > kv_cap) {
+    flags |= EJK_RPA_ST_KVLEN;
+    kv = kv < 0 ? 0 : kv_cap;
+  }
+  int ql = q1 - q0;
+  si.ok = true;
+  if (ql < 0 || q0 < 0 || q1 > p.T) {
+    flags |= EJK_RPA_ST_QLEN;
+    si.ok = false;
+    ql = 0;
+  }
+  if (ql > kv) flags |= EJK_RPA_ST_QLEN;  // rows at negative positions see no key and produce 0
+  si.q_start = q0;
+  si.q_len = ql;
+  si.kv_len = kv;
+  si.rows = ql * p.G;
+  si.tiles = (si.rows + p.rows_per_tile - 1) / p.rows_per_tile;
+  if (ql == 0) si.ok = false;  // _xla_impl_fwd.py:189-193: sequences without queries are skipped
+  return si;
+}
+
+// Key range [lo, hi) visible to at least one row of tile t; lo is rounded down to a stage boundary.
+__device__ __forceinline__ void tile_range(const Params& p, const SeqInfo& si, int t, int& lo, int& hi) {
+  const int r_first = t * p.rows_per_tile;
+  int r_last = r_first + p.rows_per_tile;
+  if (r_last > si.rows) r_last = si.rows;
+  r_last -= 1;
+  const int qt_first = r_first / p.G;
+  const int qt_last = r_last / p.G;
+  const int base = si.kv_len - si.q_len;  // position of the sequence's first query row
+  hi = base + qt_last + 1;
+  if (hi < 0) hi = 0;
+  lo = 0;
+  if (p.window > 0) {
+    lo = base + qt_first - p.window + 1;
+    if (lo < 0) lo = 0;
+  }
+  lo = (lo / kTileTokens) * kTileTokens;
+  if (hi < lo) hi = lo;
+}
+
+__device__ __forceinline__ void chunking(int len, int chunk, int& n, int& csize) {
+  n = (len + chunk - 1) / chunk;
+  if (n < 1) n = 1;
+  csize = (len + n - 1) / n;
+  csize = ((csize + kTileTokens - 1) / kTileTokens) * kTileTokens;
+  if (csize < kTileTokens) csize = kTileTokens;
+}
+
+// inclusive block scan of three counters; returns this thread's exclusive prefix and the block total
+__device__ void block_scan3(int (&v)[3], int (&excl)[3], int (&total)[3], int (*s_warp)[3]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc[3];
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    int x = v[k];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    inc[k] = x;
+    if (lane == 31) s_warp[warp][k] = x;
+  }
+  __syncthreads();
+  if (warp == 0) {
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      int x = s_warp[lane][k];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      s_warp[lane][k] = x;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const int wprev = warp ? s_warp[warp - 1][k] : 0;
+    excl[k] = inc[k] - v[k] + wprev;
+    total[k] = s_warp[31][k];
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) {
+  __shared__ int s_warp[32][3];
+  __shared__ unsigned long long s_keys;
+  __shared__ int s_chunk;
+  const int tid = threadIdx.x;
+  unsigned flags = 0;
+
+  int S = p.num_seqs[0];
+  if (S > p.S_max) {
+    flags |= EJK_RPA_ST_NUM_SEQS;
+    S = p.S_max;
+  }
+  if (S < 0) S = 0;
+  if (tid == 0) s_keys = 0ull;
+  __syncthreads();
+
+  // ---- pass 1: total number of (tile, key) pairs -> chunk size
+  unsigned long long keys = 0;
+  for (int s = tid; s < S; s += kPlanThreads) {
+    unsigned f = 0;
+    SeqInfo si = load_seq(p, s, f);
+    if (!si.ok) continue;
+    for (int t = 0; t < si.tiles; ++t) {
+      int lo, hi;
+      tile_range(p, si, t, lo, hi);
+      keys += (unsigned long long)(hi - lo);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) keys += __shfl_xor_sync(0xffffffffu, keys, o);
+  if ((tid & 31) == 0 && keys) atomicAdd(&s_keys, keys);
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned long long total = s_keys;
+    const unsigned long long tgt = (unsigned long long)(p.target_units > 0 ? p.target_units : 1);
+    unsigned long long c = (total + tgt - 1) / tgt;
+    c = ((c + kTileTokens - 1) / kTileTokens) * kTileTokens;
+    if (c < (unsigned long long)p.min_chunk) c = p.min_chunk;
+    if (c < (unsigned long long)kTileTokens) c = kTileTokens;
+    if (c > 0x40000000ull) c = 0x40000000ull;
+    s_chunk = (int)c;
+    p.header[kHdrChunk] = (int)c;
+    p.header[kHdrTotalKeys] = (int)(total > 0x7fffffffull ? 0x7fffffffull : total);
+    p.header[kHdrQueue] = 0;
+  }
+  __syncthreads();
+  const int chunk = s_chunk;
+
+  // ---- pass 2: per-sequence counts -> offsets -> items
+  int base[3] = {0, 0, 0};  // units, merge items, partial slots
+  for (int s0 = 0; s0 < S; s0 += kPlanThreads) {
+    const int s = s0 + tid;
+    int cnt[3] = {0, 0, 0};
+    SeqInfo si;
+    si.ok = false;
+    if (s < S) {
+      si = load_seq(p, s, flags);
+      if (si.ok) {
+        for (int t = 0; t < si.tiles; ++t) {
+          int lo, hi, n, cs;
+          tile_range(p, si, t, lo, hi);
+          chunking(hi - lo, chunk, n, cs);
+          cnt[0] += n;
+          if (n > 1) {
+            cnt[1] += 1;
+            cnt[2] += n;
+          }
+        }
+      }
+    }
+    int excl[3], total[3];
+    block_scan3(cnt, excl, total, s_warp);
+    if (s < S && si.ok) {
+      int u = base[0] + excl[0], m = base[1] + excl[1], sl = base[2] + excl[2];
+      if (base[0] + excl[0] + cnt[0] > p.max_units || base[1] + excl[1] + cnt[1] > p.max_merge ||
+          base[2] + excl[2] + cnt[2] > p.max_slots) {
+        flags |= EJK_RPA_ST_INTERNAL;
+      } else {
+        for (int t = 0; t < si.tiles; ++t) {
+          int lo, hi, n, cs;
+          tile_range(p, si, t, lo, hi);
+          chunking(hi - lo, chunk, n, cs);
+          if (n > 1) {
+            MergeItem mi;
+            mi.row0 = t * p.rows_per_tile;
+            mi.slot0 = sl;
+            mi.n_chunks = n;
+            mi.q_start = si.q_start;
+            mi.q_len = si.q_len;
+            mi.pad[0] = mi.pad[1] = mi.pad[2] = 0;
+            p.merge[m++] = mi;
+          }
+          for (int c = 0; c < n; ++c) {
+            Unit un;
+            un.seq = s;
+            un.row0 = t * p.rows_per_tile;
+            un.kv_begin = lo + c * cs;
+            int e = lo + (c + 1) * cs;
+            un.kv_end = e < hi ? e : hi;
+            un.slot = (n > 1) ? sl++ : -1;
+            un.q_start = si.q_start;
+            un.q_len = si.q_len;
+            un.kv_len = si.kv_len;
+            p.units[u++] = un;
+          }
+        }
+      }
+    }
+    // units of sequences that overflowed are dropped; keep offsets consistent anyway
+    base[0] += total[0];
+    base[1] += total[1];
+    base[2] += total[2];
+  }
+  if (tid == 0) {
+    const bool over = base[0] > p.max_units || base[1] > p.max_merge || base[2] > p.max_slots;
+    p.header[kHdrNumUnits] = over ? 0 : base[0];
+    p.header[kHdrNumMerge] = over ? 0 : base[1];
+    p.header[kHdrNumSlots] = over ? 0 : base[2];
+    if (over) flags |= EJK_RPA_ST_INTERNAL;
+  }
+  if (flags && p.status) atomicOr(reinterpret_cast<unsigned*>(p.status), flags);
+}
+
+}  // namespace
+
+cudaError_t launch_plan(const Params& p, cudaStream_t stream) {
+  rpa_plan_kernel<<<1, kPlanThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace ejk

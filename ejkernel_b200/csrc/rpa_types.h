@@ -1,0 +1,87 @@
+// Shared host/device declarations of the ragged paged attention path.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ejk_rpa.h"
+
+namespace ejk {
+
+// Rows of one small-q tile are (query token, head-in-group) pairs of ONE kv head, flattened
+// as row = q_token * G + g, so a decode token with G <= 8 fills one 8-row tile and one read of a
+// KV page serves the whole GQA group.
+constexpr int kTileTokens = 64;  // KV tokens per pipeline stage (4 warps x 16)
+
+// Work item of the split-KV kernel: one (sequence, row tile, KV chunk); the kv head is the fastest
+// index of the flattened work id, so neighbouring CTAs read neighbouring heads of the same page.
+struct Unit {
+  int32_t seq;
+  int32_t row0;      // first row of the tile in (q_token*G+g) space
+  int32_t kv_begin;  // first key of the chunk (multiple of kTileTokens)
+  int32_t kv_end;    // one past the last key of the chunk
+  int32_t slot;      // partial slot, or -1: the chunk is the whole range, write the output directly
+  int32_t q_start;   // query_start_loc[seq]
+  int32_t q_len;
+  int32_t kv_len;
+};
+
+// One row tile whose chunks must be combined by the merge kernel.
+struct MergeItem {
+  int32_t row0;
+  int32_t slot0;     // partial slots slot0 .. slot0+n_chunks-1
+  int32_t n_chunks;
+  int32_t q_start;
+  int32_t q_len;
+  int32_t pad[3];
+};
+
+// int32 header at the start of the workspace, written by the planner.
+enum HeaderWord {
+  kHdrNumUnits = 0,
+  kHdrNumMerge = 1,
+  kHdrChunk = 2,
+  kHdrQueue = 3,      // work queue head of the gather kernel
+  kHdrNumSlots = 4,
+  kHdrTotalKeys = 5,
+  kHdrWords = 64,
+};
+
+struct WorkspaceLayout {
+  size_t header_off, units_off, merge_off, part_o_off, part_ml_off, total;
+  int32_t max_units, max_merge, max_slots, rows_per_tile, target_units;
+};
+
+struct Params {
+  const void* q;
+  const void* kv;
+  const int32_t* context_lens;
+  const int32_t* block_tables;
+  const int32_t* query_start_loc;
+  const int32_t* num_seqs;
+  const float* sinks;
+  void* out;
+  int32_t* header;
+  Unit* units;
+  MergeItem* merge;
+  float* part_o;   // [max_slots][Hkv][rows_per_tile][D]
+  float2* part_ml; // [max_slots][Hkv][rows_per_tile]  (m in log2 domain, l)
+  int32_t* status; // may be null
+  int32_t T, S_max, pages_per_seq, num_pages, page_size, Hq, Hkv, G, D;
+  int32_t rows_per_tile;
+  int32_t max_units, max_merge, max_slots, target_units, min_chunk;
+  int32_t window;      // <= 0: none
+  int32_t num_sinks, sink_rows;
+  float scale;         // softmax_scale
+  float scale_log2;    // softmax_scale * log2(e)
+  float cap;           // 0: none
+  float cap_log2;      // cap * log2(e)
+  float inv_cap_scale; // softmax_scale / cap
+  int32_t page_shift;  // log2(page_size) if a power of two, else -1
+};
+
+// launchers (each returns cudaError_t of the launch)
+cudaError_t launch_plan(const Params& p, cudaStream_t stream);
+cudaError_t launch_splitkv(const Params& p, int dtype, int n_sm, cudaStream_t stream);
+cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stream);
+
+}  // namespace ejk

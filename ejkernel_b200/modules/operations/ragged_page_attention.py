@@ -1,0 +1,216 @@
+"""Public ``ragged_page_attention`` operator: the ops-layer entry for the CUDA path.
+
+Mirrors ejkernel/modules/operations/ragged_page_attention.py:80-641 -- a ``RaggedPageAttention``
+kernel object (``get_impl`` / ``run`` / ``create_shard_map_wrapper`` / ``heuristic_cfg`` /
+``candidate_cfgs``) and the module-level function with seven positional-only arrays and the same
+keywords -- minus the reference's multi-backend selection: there is exactly one implementation, it
+is looked up in the registry under ``Platform.CUDA`` and nothing else is ever tried.  Asking for
+another platform raises.
+"""
+
+from __future__ import annotations
+
+from typing import Literal
+
+import torch
+
+from ...kernels._registry import Backend, Platform, kernel_registry
+from ...sharding import Mesh1D, PartitionSpec, all_gather_heads
+from .configs import RaggedPageAttentionConfig
+
+Array = torch.Tensor
+OP_ID = "ragged_page_attention"
+OP_VERSION = "0"  # "ragged_page_attention@v0", ejkernel/ops/core/kernel.py:137-161
+
+
+def _resolve_platform(platform) -> Platform:
+    """The reference's ``detect_platform`` (ejkernel/modules/base.py:45-111) picks among four
+    platforms; here "auto"/None/"cuda" all mean CUDA and anything else is an error."""
+    if platform in (None, "auto", "cuda", Platform.CUDA):
+        return Platform.CUDA
+    raise ValueError(
+        f"platform={platform!r} is not available: this package provides only the CUDA (sm_100a) "
+        "implementation of ragged_page_attention"
+    )
+
+
+class RaggedPageAttention:
+    """Kernel object of the operator (reference: ``RaggedPageAttention(Kernel)``, :80-523)."""
+
+    op_id = OP_ID
+    version = OP_VERSION
+
+    def get_impl(self, cfg: RaggedPageAttentionConfig):
+        platform = _resolve_platform(cfg.platform)
+        backend = Backend.GPU if cfg.backend in (None, "any", Backend.ANY) else cfg.backend
+        return kernel_registry.get(OP_ID, platform=platform, backend=backend)
+
+    def heuristic_cfg(self, inv=None) -> RaggedPageAttentionConfig:
+        return RaggedPageAttentionConfig(
+            num_kv_pages_per_block=None, num_queries_per_block=None, num_warps=4, num_stages=1,
+            platform="cuda", backend="gpu",
+        )
+
+    def candidate_cfgs(self, inv=None) -> list[RaggedPageAttentionConfig]:
+        """The device planner sizes KV chunks from the lengths at run time, so there is a single
+        candidate (the reference's GPU candidate list also collapses to one entry, :478-499)."""
+        return [self.heuristic_cfg(inv)]
+
+    candidate_cfgs_gpu = candidate_cfgs
+    candidate_cfgs_shard_map_gpu = candidate_cfgs
+
+    def run(
+        self,
+        queries: Array,
+        kv_pages: Array,
+        context_lens: Array,
+        block_tables: Array,
+        query_start_loc: Array,
+        num_seqs: Array | int,
+        platform: Literal["triton", "pallas", "cuda", "xla", "auto"] | None = None,
+        softmax_scale: float | None = None,
+        logits_soft_cap: float | None = None,
+        compute_dtype=torch.bfloat16,
+        optimized: bool = False,
+        sliding_window: int | None = None,
+        softmax_aux: Array | None = None,
+        mask_value: float | None = None,
+        vmem_limit_bytes: int | None = None,
+        *,
+        cfg: RaggedPageAttentionConfig,
+    ) -> Array:
+        if platform is not None:
+            cfg = RaggedPageAttentionConfig(
+                num_kv_pages_per_block=cfg.num_kv_pages_per_block,
+                num_queries_per_block=cfg.num_queries_per_block,
+                num_warps=cfg.num_warps,
+                num_stages=cfg.num_stages,
+                platform=platform,
+                backend=cfg.backend,
+            )
+        impl = self.get_impl(cfg)
+        return impl(
+            queries=queries,
+            kv_pages=kv_pages,
+            context_lens=context_lens,
+            block_tables=block_tables,
+            query_start_loc=query_start_loc,
+            num_seqs=num_seqs,
+            softmax_scale=softmax_scale,
+            logits_soft_cap=logits_soft_cap,
+            compute_dtype=compute_dtype,
+            optimized=optimized,
+            sliding_window=sliding_window,
+            softmax_aux=softmax_aux,
+            mask_value=mask_value,
+            num_kv_pages_per_block=cfg.num_kv_pages_per_block,
+            num_queries_per_block=cfg.num_queries_per_block,
+            vmem_limit_bytes=vmem_limit_bytes,
+            num_warps=cfg.num_warps,
+            num_stages=cfg.num_stages,
+        )
+
+    def create_shard_map_wrapper(
+        self,
+        queries: Array,
+        kv_pages: Array,
+        context_lens: Array,
+        block_tables: Array,
+        query_start_loc: Array,
+        num_seqs: Array | int,
+        softmax_scale: float | None = None,
+        logits_soft_cap: float | None = None,
+        compute_dtype=torch.bfloat16,
+        optimized: bool = False,
+        sliding_window: int | None = None,
+        softmax_aux: Array | None = None,
+        mask_value: float | None = None,
+        vmem_limit_bytes: int | None = None,
+        platform=None,
+        cfg: RaggedPageAttentionConfig | None = None,
+        mesh: Mesh1D | None = None,
+        in_specs: tuple[PartitionSpec, ...] | None = None,
+        out_specs: PartitionSpec | None = None,
+        check_vma: bool = False,
+    ):
+        """Returns ``(fn, call_args)`` like the reference (:114-208).  Every process passes its LOCAL
+        shards; ``fn`` runs the kernel on them and, if ``out_specs`` does not shard the head axis,
+        all-gathers the heads so each rank returns the full output."""
+        assert mesh is not None, "mesh must be provided for shard_map execution"
+        assert in_specs is not None, "in_specs must be provided for shard_map execution"
+        assert out_specs is not None, "out_specs must be provided for shard_map execution"
+        cfg = cfg or self.heuristic_cfg()
+        axis = mesh.axis_name
+        call_args = (queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, softmax_aux)
+        assert len(in_specs) == len(call_args), f"in_specs length {len(in_specs)} != call_args length {len(call_args)}"
+        q_spec, kv_spec = PartitionSpec(*in_specs[0]), PartitionSpec(*in_specs[1])
+        if mesh.size > 1:
+            if q_spec.sharded_dim(axis) != 1 or kv_spec.sharded_dim(axis) != 2:
+                raise NotImplementedError(
+                    "only the KV-head partitioning is supported: queries P(None, axis, None), "
+                    "kv_pages P(None, None, axis, None)"
+                )
+            for i in (2, 3, 4, 5):
+                if PartitionSpec(*in_specs[i]).sharded_dim(axis) is not None:
+                    raise NotImplementedError("context_lens, block_tables, query_start_loc and num_seqs must be replicated")
+        gather = mesh.size > 1 and PartitionSpec(*out_specs).sharded_dim(axis) is None
+
+        def fn(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, softmax_aux=None):
+            out = self.run(
+                queries=queries, kv_pages=kv_pages, context_lens=context_lens, block_tables=block_tables,
+                query_start_loc=query_start_loc, num_seqs=num_seqs, softmax_scale=softmax_scale,
+                logits_soft_cap=logits_soft_cap, compute_dtype=compute_dtype, optimized=optimized,
+                sliding_window=sliding_window, softmax_aux=softmax_aux, mask_value=mask_value,
+                vmem_limit_bytes=vmem_limit_bytes, platform=platform, cfg=cfg,
+            )
+            return all_gather_heads(out, mesh) if gather else out
+
+        return fn, call_args
+
+
+_kernel = RaggedPageAttention()
+
+
+def ragged_page_attention(
+    queries: Array,
+    kv_pages: Array,
+    context_lens: Array,
+    block_tables: Array,
+    query_start_loc: Array,
+    num_seqs: Array | int,
+    softmax_aux: Array | None = None,
+    /,
+    *,
+    softmax_scale: float | None = None,
+    logits_soft_cap: float | None = None,
+    compute_dtype=torch.bfloat16,
+    optimized: bool = False,
+    sliding_window: int | None = None,
+    mask_value: float | None = None,
+    vmem_limit_bytes: int | None = None,
+    platform: Literal["triton", "pallas", "cuda", "xla", "auto"] | None = None,
+    cfg: RaggedPageAttentionConfig | None = None,
+    mesh: Mesh1D | None = None,
+    in_specs: tuple[PartitionSpec | None, ...] | None = None,
+    out_specs: PartitionSpec | None = None,
+) -> Array:
+    """Ragged paged attention (reference: ejkernel/modules/operations/ragged_page_attention.py:540-641).
+
+    ``queries [T,Hq,D]``, ``kv_pages [P,page,2*Hkv,D]``, ``context_lens [S]``, ``block_tables
+    [S,pages_per_seq]``, ``query_start_loc [S+1]``, ``num_seqs`` (int32 ``[1]`` tensor or int), optional
+    ``softmax_aux`` sinks.  With ``mesh``, ``in_specs`` and ``out_specs`` all given the call runs in
+    shard-map mode on this process's local shards (see ``create_shard_map_wrapper``).
+    """
+    cfg = cfg or _kernel.heuristic_cfg()
+    common = dict(
+        softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap, compute_dtype=compute_dtype,
+        optimized=optimized, sliding_window=sliding_window, softmax_aux=softmax_aux, mask_value=mask_value,
+        vmem_limit_bytes=vmem_limit_bytes, platform=platform, cfg=cfg,
+    )
+    if mesh is not None and in_specs is not None and out_specs is not None:
+        fn, call_args = _kernel.create_shard_map_wrapper(
+            queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs,
+            mesh=mesh, in_specs=in_specs, out_specs=out_specs, **common,
+        )
+        return fn(*call_args)
+    return _kernel.run(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, **common)

@@ -1,0 +1,135 @@
+/*
+ * C ABI of the sm_100a ragged paged attention path.
+ *
+ * This is the boundary a host runtime binds to.  It replaces, for the CUDA platform, what
+ * the reference reaches through its registry entry
+ *   ejkernel/kernels/_xla/ragged_page_attention/_interface.py:25-109   (operator signature)
+ *   ejkernel/kernels/_triton/ragged_page_attention/_triton_impl_fwd.py:485-613 (GPU launch wrapper:
+ *       dense row-major strides, int32 index arrays, one output, the caller's stream)
+ * and what a `jax.ffi` custom call for the operator would hand to a GPU handler
+ *   ejkernel/callib/_triton_call.py:737-757 (operands in, results out, XLA's stream, no host sync).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current CUDA device unless stated otherwise;
+ *   - tensors are dense row-major:
+ *       queries          [total_tokens, num_q_heads, head_dim]
+ *       kv_pages         [num_pages, page_size, 2*num_kv_heads, head_dim]  (K_h at 2h, V_h at 2h+1)
+ *       context_lens     [max_num_seqs]                 int32
+ *       block_tables     [max_num_seqs, pages_per_seq]  int32
+ *       query_start_loc  [max_num_seqs + 1]             int32
+ *       num_seqs         [1]                            int32
+ *       out              [total_tokens, num_q_heads, head_dim], dtype of queries
+ *   - calls only enqueue work on `stream`; they never allocate, synchronise or read device
+ *     memory from the host, which is what an XLA custom call requires of its handler;
+ *   - return value: 0 = ok, negative = invalid argument (EJK_RPA_E_*), positive = cudaError_t;
+ *   - nothing throws.
+ */
+#ifndef EJK_RPA_H_
+#define EJK_RPA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EJK_RPA_VERSION 1
+
+#if defined(__GNUC__)
+#define EJK_RPA_API __attribute__((visibility("default")))
+#else
+#define EJK_RPA_API
+#endif
+
+/* dtype codes for queries / kv_pages / out */
+#define EJK_RPA_BF16 0
+#define EJK_RPA_F16 1
+
+/* invalid-argument codes */
+#define EJK_RPA_E_NULL (-1)      /* a required pointer is null */
+#define EJK_RPA_E_SHAPE (-2)     /* a dimension is <= 0, Hq % Hkv != 0, ... */
+#define EJK_RPA_E_HEAD_DIM (-3)  /* head_dim not in {64, 128, 256} */
+#define EJK_RPA_E_DTYPE (-4)     /* unknown dtype code */
+#define EJK_RPA_E_WORKSPACE (-5) /* workspace smaller than ejk_rpa_workspace_bytes() / misaligned */
+#define EJK_RPA_E_ARG (-6)       /* sliding_window / logits_soft_cap / sinks out of contract */
+#define EJK_RPA_E_DEVICE (-7)    /* current device is not sm_100 class */
+#define EJK_RPA_E_ALIGN (-8)     /* a tensor base pointer is not 16-byte aligned */
+
+/* bits of the device-side status word (OR-ed in by the kernels; 0 = clean).  Inputs that
+ * break the operator's contract never fault: the offending value is clamped or the sequence
+ * skipped, and the bit records it.  Contract: _pallas_impl_fwd.py:124-230 of the reference. */
+#define EJK_RPA_ST_NUM_SEQS 1u  /* num_seqs[0] > max_num_seqs */
+#define EJK_RPA_ST_QLEN 2u      /* q_len < 0, q_len > kv_len, or query rows past total_tokens */
+#define EJK_RPA_ST_KVLEN 4u     /* kv_len < 0 or > pages_per_seq * page_size */
+#define EJK_RPA_ST_PAGE_ID 8u   /* a page id outside [0, num_pages) was met (read as page 0) */
+#define EJK_RPA_ST_INTERNAL 16u /* planner produced more work items than the workspace holds */
+
+/* Static problem description: everything here is known from array shapes at trace time. */
+typedef struct ejk_rpa_shape {
+  int32_t total_tokens;  /* rows of queries / out */
+  int32_t max_num_seqs;  /* block_tables.shape[0] */
+  int32_t pages_per_seq; /* block_tables.shape[1] */
+  int32_t num_pages;     /* kv_pages.shape[0] */
+  int32_t page_size;     /* kv_pages.shape[1] */
+  int32_t num_q_heads;
+  int32_t num_kv_heads;  /* kv_pages.shape[2] / 2 */
+  int32_t head_dim;      /* 64, 128 or 256 */
+  int32_t dtype;         /* EJK_RPA_BF16 | EJK_RPA_F16 */
+} ejk_rpa_shape;
+
+/* Scalar attributes of one call (the keyword arguments of the reference operator). */
+typedef struct ejk_rpa_attrs {
+  float softmax_scale;   /* must be given; the Python layer substitutes head_dim**-0.5 for None
+                            (_interface.py:94-95) */
+  float logits_soft_cap; /* 0 = none (the reference rejects 0.0 as a cap, _pallas_impl_fwd.py:222) */
+  int32_t sliding_window;/* <= 0 = none; W keeps keys (pos-W, pos] (_xla_impl_fwd.py:128-134) */
+  int32_t num_sinks;     /* 0 = no softmax_aux */
+  int32_t sink_rows;     /* rows of softmax_aux: num_q_heads, num_kv_heads, or 1 (_xla_impl_fwd.py:60-77) */
+  int32_t num_kv_pages_per_block; /* tile hint, 0 = auto (RaggedPageAttentionConfig, configs.py:242-258) */
+  int32_t num_queries_per_block;  /* tile hint, 0 = auto */
+} ejk_rpa_attrs;
+
+/* Library version (EJK_RPA_VERSION of the build).  No reference counterpart; the reference
+ * versions operators as "ragged_page_attention@v0" in ejkernel/ops/core/kernel.py:137-161. */
+EJK_RPA_API int ejk_rpa_version(void);
+
+/* Human-readable text for a return code of this library.  Host pointer, static storage. */
+EJK_RPA_API const char* ejk_rpa_error_string(int code);
+
+/* Bytes of scratch the launch needs for this static shape on the current device (split-KV
+ * partials, the device-built work list, the merge list).  Depends on shapes only, never on
+ * lengths, so a tracing runtime can allocate it as an extra result buffer.  Returns 0 on an
+ * invalid shape.  The reference has no scratch: XLA materialises its own temporaries
+ * (_xla_impl_fwd.py:113-114). */
+EJK_RPA_API size_t ejk_rpa_workspace_bytes(const ejk_rpa_shape* shape);
+
+/* Enqueue one ragged paged attention call on `stream` (a cudaStream_t).
+ * Replaces _ragged_paged_attention (_xla_impl_fwd.py:25-201) / ragged_paged_attention_triton_call
+ * (_triton_impl_fwd.py:485-613).  `workspace` must be 256-byte aligned and hold
+ * ejk_rpa_workspace_bytes(shape) bytes; its contents need not be initialised.  `status`
+ * (device int32, may be null) gets EJK_RPA_ST_* bits OR-ed in; the caller zeroes it.
+ * `softmax_aux` is float32 [sink_rows, num_sinks] or null.  Rows of `out` that belong to no
+ * sequence (>= query_start_loc[num_seqs]) are left untouched. */
+EJK_RPA_API int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* context_lens,
+                   const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
+                   const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
+                   int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream);
+
+/* Process-wide tuning knobs (host side, not thread safe against concurrent launches):
+ *   "waves"      work items per resident CTA the device planner aims for (default 16)
+ *   "min_chunk"  smallest KV chunk, in tokens, a split may have (default 256)
+ *   "path"       0 = auto, 1 = force the cp.async gather, 2 = force the TMA gather
+ * Returns 0, or EJK_RPA_E_ARG for an unknown name.  Counterpart of the reference's
+ * EJKERNEL_* environment switches (ejkernel/ops/config/selection.py:328). */
+EJK_RPA_API int ejk_rpa_set_option(const char* name, int value);
+EJK_RPA_API int ejk_rpa_get_option(const char* name, int* value);
+
+/* Number of kernels the last ejk_rpa_launch on this thread enqueued (host-side counter, for
+ * benchmark bookkeeping). */
+EJK_RPA_API int ejk_rpa_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EJK_RPA_H_ */

@@ -1,0 +1,42 @@
+"""Shared helpers of the test-suite: run the CUDA operator and the CPU oracle on one batch."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ejkernel_b200.utils import RaggedBatch
+from oracle.rpa_oracle import compare, dense_reference
+
+ATOL = RTOL = 2e-2  # bf16 tolerance of the operator's parity criterion
+REL_RMS = 5e-2  # stricter: max error relative to the RMS of the expected output (bf16 P and output rounding give ~2-3e-2)
+
+
+def run_cuda(batch: RaggedBatch, **override) -> torch.Tensor:
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import ragged_page_attention
+
+    b = batch if batch.queries.is_cuda else batch.to("cuda")
+    kw = b.kwargs()
+    kw.update(override)
+    out = ragged_page_attention(*b.args(), **kw)
+    torch.cuda.synchronize()
+    return out
+
+
+def status_word(batch_cuda: RaggedBatch) -> int:
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import read_status
+
+    return read_status(batch_cuda.queries, batch_cuda.kv_pages, batch_cuda.block_tables)
+
+
+def oracle(batch: RaggedBatch, precision="fp64") -> np.ndarray:
+    b = batch if not batch.queries.is_cuda else batch.to("cpu")
+    return dense_reference(*b.args(), **b.kwargs(), precision=precision)
+
+
+def assert_parity(got: torch.Tensor, want: np.ndarray, rows: int, *, rel_rms=REL_RMS, what=""):
+    r = compare(got, want, atol=ATOL, rtol=RTOL, rows=rows)
+    assert r["finite"], f"{what}: non-finite output {r}"
+    assert r["allclose"], f"{what}: outside atol=rtol={ATOL}: {r}"
+    assert r["max_rel_rms"] <= rel_rms, f"{what}: max|err| / rms(expected) = {r['max_rel_rms']:.4g} > {rel_rms}: {r}"
+    return r

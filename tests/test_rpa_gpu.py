@@ -1,0 +1,258 @@
+"""Parity of the sm_100a kernels (called through the C ABI via the registered operator) with the
+CPU oracle on the same seeded inputs.  Tolerance: atol = rtol = 2e-2 for bf16 with fp32
+accumulation, plus max|err| <= 5e-2 * rms(expected) because on N(0,1) inputs with long contexts
+the outputs themselves are smaller than atol.  Index work (page gather, masking) is checked
+bit-exactly through integer-valued cases."""
+
+import numpy as np
+import pytest
+import torch
+
+from ejkernel_b200.utils import make_ragged_batch, make_workload
+from tests.helpers import assert_parity, oracle, run_cuda, status_word
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(batch, what, **kw):
+    bc = batch.to("cuda")
+    out = run_cuda(bc)
+    assert out.shape == bc.queries.shape and out.dtype == bc.queries.dtype
+    assert status_word(bc) == 0, "clean inputs must leave the status word at 0"
+    return assert_parity(out, oracle(batch), batch.total_tokens, what=what, **kw)
+
+
+def test_c1_decode_toy(rpa_lib):
+    _check(make_workload("c1"), "c1")
+
+
+@pytest.mark.parametrize("name,num_seqs,len_scale", [("c2", 24, 0.25), ("c4", 6, 0.25), ("c5", 3, 0.03)])
+def test_decode_workloads_reduced(rpa_lib, name, num_seqs, len_scale):
+    _check(make_workload(name, num_seqs=num_seqs, len_scale=len_scale), name)
+
+
+def test_c3_mixed_reduced(rpa_lib):
+    _check(make_workload("c3", num_seqs=12, len_scale=0.125), "c3")
+
+
+def test_reference_tpu_test_shapes(rpa_lib):
+    # shapes of test/kernels/_pallas/tpu/test_ragged_page_attention.py:465-554 of the reference
+    b = make_ragged_batch([64, 64], [64, 96], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16,
+                          pages_per_seq=8, num_pages=32, seed=11)
+    _check(b, "prefill 2 seqs")
+    b = make_ragged_batch([100, 50, 40, 10], [128, 64, 192, 96], num_q_heads=8, num_kv_heads=2, head_dim=128,
+                          page_size=16, pages_per_seq=12, num_pages=64, seed=12)
+    _check(b, "mixed 4 seqs")
+
+
+@pytest.mark.parametrize("head_dim", [64, 128, 256])
+@pytest.mark.parametrize("hq,hkv", [(8, 8), (8, 4), (16, 4), (8, 1), (32, 2), (6, 2)])
+def test_head_configs(rpa_lib, head_dim, hq, hkv):
+    b = make_ragged_batch([1, 3, 1, 17], [200, 64, 1, 90], num_q_heads=hq, num_kv_heads=hkv, head_dim=head_dim,
+                          page_size=16, seed=hq * 100 + hkv + head_dim)
+    _check(b, f"hq{hq} hkv{hkv} d{head_dim}")
+
+
+@pytest.mark.parametrize("page_size", [1, 3, 8, 16, 32, 64, 128])
+def test_page_sizes(rpa_lib, page_size):
+    b = make_ragged_batch([1, 1, 5, 1], [777, 129, 300, 64], num_q_heads=8, num_kv_heads=2, head_dim=128,
+                          page_size=page_size, seed=page_size)
+    _check(b, f"page_size {page_size}")
+
+
+@pytest.mark.parametrize("kv_len", list(range(1, 20)) + [63, 64, 65, 127, 128, 129, 255, 256, 257, 1023, 1025])
+def test_every_kv_remainder(rpa_lib, kv_len):
+    q_lens = [1, min(kv_len, 2), min(kv_len, 9)]
+    b = make_ragged_batch(q_lens, [kv_len] * 3, num_q_heads=4, num_kv_heads=2, head_dim=128, page_size=16, seed=kv_len)
+    _check(b, f"kv_len {kv_len}")
+
+
+@pytest.mark.parametrize("q_len", [1, 2, 3, 7, 8, 9, 127, 128, 129])
+def test_query_lengths(rpa_lib, q_len):
+    b = make_ragged_batch([q_len, 1, q_len], [q_len + 300, 50, q_len], num_q_heads=8, num_kv_heads=2, head_dim=128,
+                          page_size=16, seed=q_len)
+    _check(b, f"q_len {q_len}")
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100, 1000])
+@pytest.mark.parametrize("cap", [None, 30.0])
+def test_window_and_soft_cap(rpa_lib, window, cap):
+    b = make_ragged_batch([1, 4, 1, 33], [700, 350, 20, 400], num_q_heads=8, num_kv_heads=4, head_dim=128,
+                          page_size=16, seed=window, sliding_window=window, logits_soft_cap=cap)
+    _check(b, f"window {window} cap {cap}")
+
+
+def test_window_invariants_of_reference_tests(rpa_lib):
+    # test/kernels/_triton/test_ragged_page_attention.py:437-487: a window larger than every context
+    # equals no window; a huge soft cap approximates none
+    base = make_ragged_batch([1, 6], [200, 300], num_q_heads=8, num_kv_heads=4, head_dim=64, page_size=16, seed=5)
+    o0 = run_cuda(base)
+    o1 = run_cuda(base, sliding_window=1000)
+    assert torch.equal(o0, o1)
+    o2 = run_cuda(base, logits_soft_cap=1e6)
+    assert (o0.float() - o2.float()).abs().max().item() < 0.1
+    o3 = run_cuda(base, sliding_window=7)
+    assert (o0.float() - o3.float()).abs().max().item() > 1e-6
+
+
+def test_sinks(rpa_lib):
+    for rows in ("q", "kv", "flat"):
+        b = make_ragged_batch([1, 5, 1], [300, 70, 2000], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=21)
+        g = torch.Generator().manual_seed(3)
+        if rows == "q":
+            b.softmax_aux = torch.randn(8, 4, generator=g)
+        elif rows == "kv":
+            b.softmax_aux = torch.randn(2, 4, generator=g)
+        else:
+            b.softmax_aux = torch.randn(3, generator=g)
+        _check(b, f"sinks {rows}")
+
+
+def test_fp16(rpa_lib):
+    b = make_ragged_batch([1, 2, 40], [500, 77, 300], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16,
+                          seed=2, dtype=torch.float16)
+    _check(b, "fp16")
+
+
+def test_num_seqs_smaller_than_capacity_and_empty_sequences(rpa_lib):
+    b = make_ragged_batch([1, 0, 3, 0, 1], [100, 50, 64, 0, 9], num_q_heads=8, num_kv_heads=2, head_dim=128,
+                          page_size=16, max_num_seqs=9, pad_query_rows=5, seed=8)
+    bc = b.to("cuda")
+    out = run_cuda(bc)
+    assert_parity(out, oracle(b), b.total_tokens, what="ragged/empty")
+    assert torch.count_nonzero(out[b.total_tokens:]) == 0, "rows past the last sequence stay zero"
+    # an int num_seqs is accepted like a (1,) array (_xla_impl_fwd.py:195)
+    out2 = run_cuda(bc, )
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import ragged_page_attention
+    out3 = ragged_page_attention(bc.queries, bc.kv_pages, bc.context_lens, bc.block_tables, bc.query_start_loc, 5,
+                                 softmax_scale=bc.softmax_scale)
+    assert torch.equal(out2, out3)
+
+
+def test_zero_sequences(rpa_lib):
+    b = make_ragged_batch([1, 1], [10, 10], num_q_heads=4, num_kv_heads=2, head_dim=64, page_size=8, seed=1)
+    bc = b.to("cuda")
+    bc.num_seqs = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = run_cuda(bc)
+    assert torch.count_nonzero(out) == 0
+
+
+def test_page_gather_is_bit_exact(rpa_lib):
+    """q = 0 makes the softmax uniform, V carries small integers that identify (page, slot, head,
+    lane): the fp32 mean of integers below 2^11 over a power-of-two count is exact, so any wrong
+    page, slot, head or mask boundary changes the result."""
+    page, Hkv, G, D = 16, 2, 4, 128
+    kv_lens = [64, 256, 1024, 16]
+    b = make_ragged_batch([1] * 4, kv_lens, num_q_heads=Hkv * G, num_kv_heads=Hkv, head_dim=D, page_size=page, seed=77)
+    b.queries.zero_()
+    P = b.kv_pages.shape[0]
+    g = torch.Generator().manual_seed(5)
+    v = torch.randint(0, 256, (P, page, Hkv, D), generator=g).float()
+    k = torch.randn(P, page, Hkv, D, generator=g)
+    b.kv_pages = torch.stack([k, v], dim=3).reshape(P, page, 2 * Hkv, D).to(torch.bfloat16)
+    out = run_cuda(b).float().cpu()
+    want = oracle(b)
+    want_bf16 = torch.from_numpy(want).to(torch.bfloat16).float()
+    assert torch.equal(out, want_bf16)
+
+
+def test_planted_keys_give_order_one_outputs(rpa_lib):
+    """A few keys per sequence get a large score so the output is O(1) and dominated by specific
+    (page, slot) entries; catches gather errors that N(0,1) averaging would hide."""
+    b = make_ragged_batch([1, 1, 4], [4000, 900, 2500], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=31)
+    q = b.queries.float()
+    kv = b.kv_pages.float()
+    tab = b.block_tables
+    rng = np.random.default_rng(0)
+    cu = b.query_start_loc.tolist()
+    for s, kl in enumerate(b.meta["kv_lens"]):
+        for j in rng.choice(kl - 4, size=3, replace=False):
+            pg, sl = int(tab[s, j // 16]), int(j % 16)
+            for h in range(2):
+                kv[pg, sl, 2 * h] = q[cu[s], h * 4] * 0.6
+    b.kv_pages = kv.to(torch.bfloat16)
+    r = _check(b, "planted")
+    assert r["rms_want"] > 0.2
+
+
+def test_deterministic_and_unaffected_by_poisoned_scratch(rpa_lib):
+    """Two runs agree bitwise (the split-KV merge has no order dependence), and NaN in pool pages no
+    sequence owns, in the tail slots of last pages and in the workspace does not leak into the output."""
+    b = make_workload("c2", num_seqs=16, len_scale=0.5)
+    bc = b.to("cuda")
+    o1 = run_cuda(bc)
+    used = torch.zeros(bc.kv_pages.shape[0], dtype=torch.bool, device="cuda")
+    page = b.meta["page_size"]
+    for s, kl in enumerate(b.meta["kv_lens"]):
+        n = -(-kl // page)
+        used[bc.block_tables[s, :n].long()] = True
+        if kl % page:
+            bc.kv_pages[bc.block_tables[s, n - 1].long(), kl % page:] = float("nan")
+    bc.kv_pages[~used] = float("nan")
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import _workspace_cache
+    for ws in _workspace_cache.values():
+        ws.buffer.view(torch.float32)[: ws.nbytes // 4].fill_(float("nan"))
+    o2 = run_cuda(bc)
+    assert torch.equal(o1, o2)
+    assert torch.isfinite(o2.float()).all()
+
+
+def test_contract_violations_set_status_bits_and_never_fault(rpa_lib):
+    from ejkernel_b200 import _cabi
+    b = make_ragged_batch([1, 1, 1], [100, 50, 64], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=9)
+    bc = b.to("cuda")
+    bad = bc.to("cuda")
+    bad.block_tables = bc.block_tables.clone()
+    bad.block_tables[0, 1] = 10_000_000
+    bad.block_tables[1, 0] = -3
+    out = run_cuda(bad)
+    assert status_word(bad) & _cabi.ST_PAGE_ID
+    assert torch.isfinite(out.float()).all()
+    bad = bc.to("cuda")
+    bad.num_seqs = torch.tensor([50], dtype=torch.int32, device="cuda")
+    run_cuda(bad)
+    assert status_word(bad) & _cabi.ST_NUM_SEQS
+    bad = bc.to("cuda")
+    bad.context_lens = bc.context_lens.clone()
+    bad.context_lens[2] = 1 << 20
+    run_cuda(bad)
+    assert status_word(bad) & _cabi.ST_KVLEN
+    bad = bc.to("cuda")
+    bad.query_start_loc = torch.tensor([0, 5, 2, 3], dtype=torch.int32, device="cuda")
+    run_cuda(bad)
+    assert status_word(bad) & _cabi.ST_QLEN
+    # q_len > kv_len: rows at negative positions see nothing and come out as zeros
+    b2 = make_ragged_batch([4], [4], num_q_heads=4, num_kv_heads=2, head_dim=64, page_size=8, seed=1)
+    b2c = b2.to("cuda")
+    b2c.context_lens = torch.tensor([2], dtype=torch.int32, device="cuda")
+    out = run_cuda(b2c)
+    assert status_word(b2c) & _cabi.ST_QLEN
+    assert torch.count_nonzero(out[:2]) == 0 and torch.isfinite(out.float()).all()
+
+
+def test_host_errors(rpa_lib):
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import ragged_page_attention
+    b = make_ragged_batch([1], [10], num_q_heads=4, num_kv_heads=2, head_dim=64, page_size=8, seed=1).to("cuda")
+    with pytest.raises(ValueError):
+        ragged_page_attention(*b.args(), sliding_window=0)
+    with pytest.raises(ValueError):
+        ragged_page_attention(*b.args(), logits_soft_cap=0.0)
+    with pytest.raises(ValueError):
+        ragged_page_attention(b.queries, b.kv_pages, b.context_lens.long(), b.block_tables, b.query_start_loc, b.num_seqs)
+    with pytest.raises(NotImplementedError):
+        ragged_page_attention(b.queries.float(), b.kv_pages.float(), b.context_lens, b.block_tables, b.query_start_loc, b.num_seqs)
+    with pytest.raises(Exception):  # rank mismatch is a type-check error, as in the reference
+        ragged_page_attention(b.queries[0], b.kv_pages, b.context_lens, b.block_tables, b.query_start_loc, b.num_seqs)
+
+
+def test_public_module_entry(rpa_lib):
+    import ejkernel_b200 as ej
+    b = make_workload("c1")
+    bc = b.to("cuda")
+    out = ej.ragged_page_attention(bc.queries, bc.kv_pages, bc.context_lens, bc.block_tables, bc.query_start_loc,
+                                   bc.num_seqs, softmax_scale=bc.softmax_scale, platform="cuda")
+    torch.cuda.synchronize()
+    assert_parity(out, oracle(b), b.total_tokens, what="modules entry")
+    with pytest.raises(ValueError):
+        ej.ragged_page_attention(bc.queries, bc.kv_pages, bc.context_lens, bc.block_tables, bc.query_start_loc,
+                                 bc.num_seqs, platform="xla")
