@@ -1,0 +1,441 @@
+#!/usr/bin/env python
+"""Benchmark of the ragged paged attention hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload c2]
+
+One "step" is one ``ragged_page_attention`` call over one synthetic batch.  At N = 1 the
+workload is the Llama-3-8B-shaped decode batch ("c2": 256 sequences, q_len 1, kv_len uniform in
+[128, 8192], Hq 32 / Hkv 8 / D 128, page 16, bf16).  At N > 1 the batch grows to 256*N sequences
+and every rank serves Hkv/N kv heads of all of them (KV-head sharding, no collective in the data
+path), so the bytes per GPU stay fixed: weak scaling.  ``--workload`` / ``--num-seqs`` /
+``--len-scale`` select other cases (used for profiling small captures and for the long-context
+"c5" strong-scaling run with ``--strong``).
+
+Prints ONE JSON line (rank 0):  value = query tokens/s of the whole job with inputs resident in
+HBM; ``hbm_tbs`` = algorithmic KV bytes / time; ``roofline`` for the attention kernel timed with
+CUDA events inside the run; ``e2e`` = the same metric through the public operator with the step's
+inputs copied from pinned host memory and the output copied back, every step; ``cpu_baseline`` =
+the CPU restatement of the reference's XLA algorithm timed on this host's cores on a bounded
+sample of the same batch.  ``--impl reference`` times only that CPU restatement.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+METRIC = "paged_attn_query_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--num-seqs", type=int, default=None, help="override the number of sequences (per GPU-equivalent)")
+    ap.add_argument("--len-scale", type=float, default=1.0)
+    ap.add_argument("--strong", action="store_true", help="keep the batch fixed and split its kv heads over the ranks")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--waves", type=int, default=None)
+    ap.add_argument("--path", type=int, default=None)
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs
+    (read-only queries)."""
+
+    BAD = {
+        0x8: "hw_slowdown",
+        0x20: "sw_thermal_slowdown",
+        0x40: "hw_thermal_slowdown",
+    }
+    NOTE = {0x4: "sw_power_cap", 0x80: "hw_power_brake", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thr = None
+        self.period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            # CUDA_VISIBLE_DEVICES may remap indices; match by UUID when possible
+            uuid = torch.cuda.get_device_properties(index).uuid
+            self.h = None
+            for i in range(pynvml.nvmlDeviceGetCount()):
+                h = pynvml.nvmlDeviceGetHandleByIndex(i)
+                u = pynvml.nvmlDeviceGetUUID(h)
+                u = u.decode() if isinstance(u, bytes) else u
+                if str(uuid) in u:
+                    self.h = h
+                    break
+            if self.h is None:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in {**self.BAD, **self.NOTE}.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join()
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# --------------------------------------------------------------------------------------------
+# CPU restatement of the reference (the "reference arm" and the cpu_baseline leg)
+# --------------------------------------------------------------------------------------------
+def cpu_reference_rate(batch_cpu_sample, seconds: float, steps: int = 1, warmup: int = 0):
+    """Times oracle.blocked_as_written (the reference's XLA algorithm as written) on all host
+    threads over the given sample of sequences.  Returns (tokens/s, GB/s of algorithmic KV bytes,
+    ms per pass, cores)."""
+    from ejkernel_b200.utils import algorithmic_kv_bytes
+    from oracle.rpa_oracle import blocked_as_written
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    b = batch_cpu_sample
+    for _ in range(warmup):
+        blocked_as_written(*b.args(), **b.kwargs())
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        blocked_as_written(*b.args(), **b.kwargs())
+        n += 1
+        if n >= steps or time.perf_counter() - t0 > seconds:
+            break
+    dt = (time.perf_counter() - t0) / n
+    toks = b.total_tokens
+    return toks / dt, algorithmic_kv_bytes(b) / dt / 1e9, dt * 1e3, cores
+
+
+def compact_sample(batch, n_seqs: int):
+    """First ``n_seqs`` sequences of a (device) batch with their pages gathered into a small pool
+    on the host, page ids renumbered; lets the CPU leg run without copying a multi-GB pool."""
+    from ejkernel_b200.utils import RaggedBatch, cdiv
+
+    m = batch.meta
+    n = min(n_seqs, len(m["kv_lens"]))
+    page = m["page_size"]
+    kv_lens, q_lens = m["kv_lens"][:n], m["q_lens"][:n]
+    npg = [cdiv(k, page) for k in kv_lens]
+    tab = batch.block_tables[:n].clone()
+    ids = torch.cat([tab[s, : npg[s]] for s in range(n)]).long()
+    pool = batch.kv_pages[ids].cpu()
+    new_tab = torch.zeros((n, tab.shape[1]), dtype=torch.int32)
+    off = 0
+    for s in range(n):
+        new_tab[s, : npg[s]] = torch.arange(off, off + npg[s], dtype=torch.int32)
+        off += npg[s]
+    T = int(sum(q_lens))
+    cu = torch.zeros(n + 1, dtype=torch.int32)
+    cu[1:] = torch.cumsum(torch.tensor(q_lens), 0)
+    q = batch.queries[:T].cpu()
+    # 8 trailing rows keep the as-written 8-row block of the last sequence inside the array
+    q = torch.cat([q, torch.zeros((16, *q.shape[1:]), dtype=q.dtype)], 0)
+    meta = dict(m)
+    meta.update(kv_lens=kv_lens, q_lens=q_lens, total_tokens=T, num_pages=pool.shape[0])
+    return RaggedBatch(
+        q, pool, torch.tensor(kv_lens, dtype=torch.int32), new_tab, cu, torch.tensor([n], dtype=torch.int32),
+        batch.softmax_scale, batch.sliding_window, batch.logits_soft_cap, None, meta,
+    )
+
+
+def pick_sample_size(batch, seconds: float) -> int:
+    """Sequences whose as-written CPU pass should take roughly ``seconds`` (assumes ~1.5 GB/s of
+    KV traffic on the host; the real rate is what gets reported)."""
+    m = batch.meta
+    per_tok = 2 * m["num_kv_heads"] * m["head_dim"] * 2
+    budget = seconds * 1.5e9
+    acc, n = 0, 0
+    for k in m["kv_lens"]:
+        acc += k * per_tok
+        n += 1
+        if acc > budget:
+            break
+    return max(1, n)
+
+
+# --------------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+
+    from ejkernel_b200.utils import WORKLOADS, algorithmic_kv_bytes, make_ragged_batch, workload_lengths
+
+    base_seqs = {"c1": 8, "c2": 256, "c3": 68, "c4": 128, "c5": 64}[args.workload]
+    n_seqs = args.num_seqs or base_seqs
+    weak = not args.strong
+    total_seqs = n_seqs * (world if weak else 1)
+    wl_seed = 1000 + WORKLOADS.index(args.workload) + 1
+
+    def build(device, kv_head_slice):
+        q_l, kv_l, shape, extra = workload_lengths(args.workload, num_seqs=total_seqs, len_scale=args.len_scale)
+        return make_ragged_batch(q_l, kv_l, dtype=torch.bfloat16, device=device, seed=wl_seed,
+                                 kv_head_slice=kv_head_slice, **shape, **extra), shape
+
+    config = {
+        "workload": f"{args.workload}: {total_seqs} seqs" + (f" x len_scale {args.len_scale}" if args.len_scale != 1.0 else ""),
+        "partition": f"kv-head sharded over {world} GPU(s), {'weak' if weak else 'strong'}" if world > 1 else "single GPU",
+        "l2": "KV pool larger than the 126 MB L2; no flush needed" ,
+    }
+
+    # ---------------- reference arm: CPU restatement only, rank 0 only ----------------
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        # build only the sampled sequences on the host (the full pool is never needed)
+        q_l, kv_l, shape, extra = workload_lengths(args.workload, num_seqs=total_seqs, len_scale=args.len_scale)
+        per_tok = 2 * shape["num_kv_heads"] * shape["head_dim"] * 2
+        n = 0
+        acc = 0
+        for k in kv_l:
+            acc += int(k) * per_tok
+            n += 1
+            if acc > 1.2e9:
+                break
+        sub_shape = dict(shape)
+        sub_shape.pop("num_pages", None)
+        b = make_ragged_batch(q_l[:n], kv_l[:n], dtype=torch.bfloat16, device="cpu", seed=wl_seed,
+                              pad_query_rows=16, **sub_shape, **extra)
+        for _ in range(min(args.warmup, 1)):
+            cpu_reference_rate(b, 1e9, steps=1)
+        tps, gbs, ms, cores = cpu_reference_rate(b, 1e9, steps=max(1, min(args.steps, 5)))
+        steps_done = max(1, min(args.steps, 5))
+        sample = f"first {n} of {total_seqs} sequences of the batch, {steps_done} pass(es)"
+        line = {
+            "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": steps_done, "warmup": min(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak" if weak else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config, "hbm_tbs": gbs / 1e3,
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line))
+        return
+
+    # ---------------- our arm ----------------
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from ejkernel_b200 import _cabi
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import RpaWorkspace, ragged_page_attention_into
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import _shape_of
+    from ejkernel_b200.modules import ragged_page_attention as public_op
+
+    _cabi.load()
+    if args.waves:
+        _cabi.set_option("waves", args.waves)
+    if args.path is not None:
+        _cabi.set_option("path", args.path)
+
+    Hkv = {"c1": 2}.get(args.workload, 8)
+    if Hkv % world:
+        raise SystemExit(f"num_kv_heads={Hkv} cannot be split over {world} ranks")
+    per = Hkv // world
+    head_slice = (rank * per, (rank + 1) * per) if world > 1 else None
+    batch, shape = build(dev, head_slice)
+    T = batch.total_tokens
+    kv_bytes_rank = algorithmic_kv_bytes(batch)
+    ws = RpaWorkspace(_shape_of(batch.queries, batch.kv_pages, batch.block_tables), dev)
+    out = torch.zeros_like(batch.queries)
+    kw = dict(softmax_scale=batch.softmax_scale, sliding_window=batch.sliding_window,
+              logits_soft_cap=batch.logits_soft_cap)
+
+    def step():
+        ragged_page_attention_into(out, ws, *batch.args(), **kw)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    launches_per_step = _cabi.load().ejk_rpa_last_launch_count()
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    status = int(ws.status.item())
+
+    # attention-kernel-only duration (CUDA events recorded around each kernel on the launch stream)
+    _cabi.set_option("profile", 1)
+    main_ms, plan_ms, merge_ms = [], [], []
+    for _ in range(min(args.steps, 50)):
+        step()
+        a, b_, c = _cabi.profile_read()
+        plan_ms.append(a)
+        main_ms.append(b_)
+        merge_ms.append(c)
+    _cabi.set_option("profile", 0)
+    k_ms = statistics.mean(main_ms)
+
+    # ---------------- end-to-end leg: public operator, host buffers ----------------
+    e2e = None
+    if not args.no_e2e:
+        host_in = [t.cpu().pin_memory() for t in (batch.queries, batch.context_lens, batch.block_tables,
+                                                  batch.query_start_loc, batch.num_seqs)]
+        dev_in = [torch.empty_like(t, device=dev) for t in host_in]
+        host_out = torch.empty(batch.queries.shape, dtype=batch.queries.dtype).pin_memory()
+        h2d = sum(t.numel() * t.element_size() for t in host_in)
+        d2h = host_out.numel() * host_out.element_size()
+
+        def e2e_step():
+            for d, h in zip(dev_in, host_in):
+                d.copy_(h, non_blocking=True)
+            o = public_op(dev_in[0], batch.kv_pages, dev_in[1], dev_in[2], dev_in[3], dev_in[4], **kw)
+            host_out.copy_(o, non_blocking=True)
+            torch.cuda.current_stream().synchronize()  # the host reads the result every step
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        n_e2e = min(args.steps, 100)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms_e2e], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_e2e = float(t.item())
+        ms_e2e /= n_e2e
+        e2e = {"value": T / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": ms_e2e,
+               "note": "queries, lengths, page table copied in and output copied out every step; the paged KV pool is the "
+                       "resident cache the operator reads, not a per-step input"}
+
+    # ---------------- cpu baseline (rank 0, N = 1 only) ----------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        n = pick_sample_size(batch, 4.0)
+        sample = compact_sample(batch, n)
+        tps, gbs, ms, cores = cpu_reference_rate(sample, args.cpu_seconds, steps=3, warmup=0)
+        cpu = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "gb_per_s": gbs,
+               "sample": f"first {len(sample.meta['kv_lens'])} of {total_seqs} sequences (their pages compacted to a host pool), "
+                         f"as-written XLA algorithm restated with torch CPU ops, {ms:.0f} ms per pass"}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    pk = ROOT / "MEASURED_PEAKS.json"
+    peak_src = "fallback"
+    if pk.exists():
+        peaks = json.loads(pk.read_text())
+        peak_src = "measured"
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    total_bytes = kv_bytes_rank * world
+    achieved = kv_bytes_rank / (k_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC,
+        "value": T / (ms_step * 1e-3),
+        "unit": UNIT,
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(3, args.warmup),
+        "ms_per_step": ms_step,
+        "higher_is_better": True,
+        "scaling": "weak" if weak else "strong",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": config,
+        "hbm_tbs": total_bytes / (ms_step * 1e-3) / 1e12,
+        "kv_bytes_per_step": total_bytes,
+        "roofline": {
+            "bound": "hbm", "kernel": "rpa attention (gather + QK^T + softmax + PV)", "achieved": achieved,
+            "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
+            "frac_of_nominal_8tbs": achieved / 8000.0, "kernel_ms": k_ms, "plan_ms": statistics.mean(plan_ms),
+            "merge_ms": statistics.mean(merge_ms), "traffic": None,
+        },
+        "cpu_baseline": cpu,
+        "e2e": e2e,
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clk.summary(),
+        "status_word": status,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -16,13 +16,14 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libejk_rpa.so"
 
 BF16, F16 = 0, 1
 
-ST_NUM_SEQS, ST_QLEN, ST_KVLEN, ST_PAGE_ID, ST_INTERNAL = 1, 2, 4, 8, 16
+ST_NUM_SEQS, ST_QLEN, ST_KVLEN, ST_PAGE_ID, ST_INTERNAL, ST_TIMEOUT = 1, 2, 4, 8, 16, 32
 STATUS_TEXT = {
     ST_NUM_SEQS: "num_seqs exceeds block_tables.shape[0]",
     ST_QLEN: "a sequence has q_len < 0, q_len > kv_len or query rows past total_tokens",
     ST_KVLEN: "a context length is negative or exceeds pages_per_seq * page_size",
     ST_PAGE_ID: "a page id outside [0, num_pages) was read from block_tables",
     ST_INTERNAL: "the device planner ran out of workspace",
+    ST_TIMEOUT: "a bounded wait inside a kernel ran out; outputs are invalid",
 }
 
 EXPORTS = (
@@ -33,6 +34,7 @@ EXPORTS = (
     "ejk_rpa_set_option",
     "ejk_rpa_get_option",
     "ejk_rpa_last_launch_count",
+    "ejk_rpa_profile_read",
 )
 
 
@@ -109,6 +111,8 @@ def load() -> ctypes.CDLL:
     lib.ejk_rpa_get_option.argtypes = [c_char_p, POINTER(c_int)]
     lib.ejk_rpa_last_launch_count.restype = c_int
     lib.ejk_rpa_last_launch_count.argtypes = []
+    lib.ejk_rpa_profile_read.restype = c_int
+    lib.ejk_rpa_profile_read.argtypes = [POINTER(c_float), POINTER(c_float), POINTER(c_float)]
     _lib = lib
     return lib
 
@@ -130,6 +134,13 @@ def get_option(name: str) -> int:
     v = c_int(0)
     check(load().ejk_rpa_get_option(name.encode(), ctypes.byref(v)), f"get_option({name})")
     return v.value
+
+
+def profile_read() -> tuple[float, float, float]:
+    """(planner, attention, merge) device milliseconds of this thread's last profiled launch."""
+    a, b, c = c_float(0), c_float(0), c_float(0)
+    check(load().ejk_rpa_profile_read(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)), "profile_read")
+    return a.value, b.value, c.value
 
 
 def decode_status(word: int) -> list[str]:

@@ -8,12 +8,20 @@ namespace ejk {
 namespace {
 
 struct Options {
-  int waves = 16;
+  int waves = 8;
   int min_chunk = 256;
   int path = 0;
+  int profile = 0;
 };
 Options g_opt;
 thread_local int t_last_launches = 0;
+
+// cudaEvents around the three kernels of a launch; only touched when option "profile" is 1
+struct ProfileEvents {
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  bool created = false, recorded = false;
+};
+thread_local ProfileEvents t_prof;
 
 struct DeviceInfo {
   bool known = false;
@@ -184,16 +192,36 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
     p.page_shift = sh;
   }
 
+  p.tma_block_tokens = s.page_size < kTileTokens ? s.page_size : kTileTokens;
+  p.tma_block_shift = 0;
+  while ((1 << p.tma_block_shift) < p.tma_block_tokens) ++p.tma_block_shift;
+  const bool use_tma = (g_opt.path == 2) || (g_opt.path == 0 && tma_path_supported(p));
+  if (use_tma && !tma_path_supported(p)) return EJK_RPA_E_ARG;
+
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool prof = g_opt.profile != 0;
+  if (prof && !t_prof.created) {
+    for (auto& ev : t_prof.ev)
+      if (cudaError_t ce = cudaEventCreate(&ev); ce != cudaSuccess) return static_cast<int>(ce);
+    t_prof.created = true;
+  }
+  t_prof.recorded = false;
+  if (prof) cudaEventRecord(t_prof.ev[0], st);
   cudaError_t e = launch_plan(p, st);
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
-  e = launch_splitkv(p, s.dtype, d->sm_count, st);
+  if (prof) cudaEventRecord(t_prof.ev[1], st);
+  e = use_tma ? launch_splitkv_tma(p, s.dtype, d->sm_count, st) : launch_splitkv(p, s.dtype, d->sm_count, st);
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
+  if (prof) cudaEventRecord(t_prof.ev[2], st);
   e = launch_merge(p, s.dtype, d->sm_count, st);
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
+  if (prof) {
+    cudaEventRecord(t_prof.ev[3], st);
+    t_prof.recorded = true;
+  }
   return 0;
 }
 
@@ -208,6 +236,8 @@ int ejk_rpa_set_option(const char* name, int value) {
   } else if (!std::strcmp(name, "path")) {
     if (value < 0 || value > 2) return EJK_RPA_E_ARG;
     g_opt.path = value;
+  } else if (!std::strcmp(name, "profile")) {
+    g_opt.profile = value ? 1 : 0;
   } else {
     return EJK_RPA_E_ARG;
   }
@@ -219,10 +249,25 @@ int ejk_rpa_get_option(const char* name, int* value) {
   if (!std::strcmp(name, "waves")) *value = g_opt.waves;
   else if (!std::strcmp(name, "min_chunk")) *value = g_opt.min_chunk;
   else if (!std::strcmp(name, "path")) *value = g_opt.path;
+  else if (!std::strcmp(name, "profile")) *value = g_opt.profile;
   else return EJK_RPA_E_ARG;
   return 0;
 }
 
 int ejk_rpa_last_launch_count(void) { return t_last_launches; }
+
+int ejk_rpa_profile_read(float* plan_ms, float* main_ms, float* merge_ms) {
+  if (!t_prof.recorded) return EJK_RPA_E_ARG;
+  cudaError_t e = cudaEventSynchronize(t_prof.ev[3]);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  float* dst[3] = {plan_ms, main_ms, merge_ms};
+  for (int i = 0; i < 3; ++i) {
+    float ms = 0.f;
+    e = cudaEventElapsedTime(&ms, t_prof.ev[i], t_prof.ev[i + 1]);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dst[i]) *dst[i] = ms;
+  }
+  return 0;
+}
 
 }  // extern "C"

@@ -84,7 +84,6 @@ rpa_splitkv_kernel(const Params p) {
   float* obuf = reinterpret_cast<float*>(smem + C::OFF_OBUF);
   float* mbuf = reinterpret_cast<float*>(smem + C::OFF_MBUF);
   float* lbuf = reinterpret_cast<float*>(smem + C::OFF_LBUF);
-  float* fbuf = reinterpret_cast<float*>(smem + C::OFF_FBUF);
   float* row_scale = reinterpret_cast<float*>(smem + C::OFF_ROWSCALE);
   float* row_m = reinterpret_cast<float*>(smem + C::OFF_ROWM);
   float* row_l = reinterpret_cast<float*>(smem + C::OFF_ROWL);
@@ -94,8 +93,6 @@ rpa_splitkv_kernel(const Params p) {
   const int n_work = p.header[kHdrNumUnits] * p.Hkv;
   const int Hkv = p.Hkv, G = p.G;
   unsigned flags = 0;
-
-  for (int i = tid; i < RT * D; i += kThreads) obuf[i] = 0.f;
 
   auto load_cursor = [&](Cursor& c) {
     c.valid = c.wid < n_work;
@@ -344,6 +341,21 @@ rpa_splitkv_kernel(const Params p) {
           }
         }
       __syncthreads();
+      // Every lane derives the rescale factors of its own rows; the accumulators are then added
+      // into obuf in four rounds, warp w handling d-slice (w + round) % 4, so each address gets
+      // its four contributions in a fixed order (deterministic, no floating-point atomics).
+      float f_own[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int r = nt * 8 + (lane & 3) * 2 + j;
+          float mt = -INFINITY;
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) mt = fmaxf(mt, mbuf[w * RT + r]);
+          const float mu = (mt == -INFINITY) ? 0.f : mt;
+          f_own[nt][j] = fast_exp2(m_run[nt][j] - mu);
+        }
       if (tid < RT) {
         const int r = tid;
         float mt = -INFINITY;
@@ -352,14 +364,10 @@ rpa_splitkv_kernel(const Params p) {
         const float mu = (mt == -INFINITY) ? 0.f : mt;
         float lt = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-          const float f = fast_exp2(mbuf[w * RT + r] - mu);
-          fbuf[w * RT + r] = f;
-          lt += lbuf[w * RT + r] * f;
-        }
+        for (int w = 0; w < kWarps; ++w) lt += lbuf[w * RT + r] * fast_exp2(mbuf[w * RT + r] - mu);
         float sc = 1.f;
         if (cc.u.slot < 0) {
-          float m_fin = mt, l_fin = lt;
+          float l_fin = lt;
           if (p.num_sinks > 0 && r < n_rows) {
             // attention sinks join the denominator only (_xla_impl_fwd.py:161-172)
             const int R = cc.u.row0 + r;
@@ -368,11 +376,11 @@ rpa_splitkv_kernel(const Params p) {
             const float* sk = p.sinks + (size_t)srow * p.num_sinks;
             float sm = -INFINITY;
             for (int i = 0; i < p.num_sinks; ++i) sm = fmaxf(sm, sk[i] * kLog2e);
-            m_fin = fmaxf(mt, sm);
+            const float m_fin = fmaxf(mt, sm);
             const float mf = (m_fin == -INFINITY) ? 0.f : m_fin;
-            l_fin = lt * fast_exp2(mt - mf);
-            for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
             sc = fast_exp2(mt - mf);
+            l_fin = lt * sc;
+            for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
           }
           sc = (l_fin > 0.f) ? sc / l_fin : 0.f;
         }
@@ -380,26 +388,39 @@ rpa_splitkv_kernel(const Params p) {
         row_m[r] = mt;
         row_l[r] = lt;
       }
-      __syncthreads();
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const int r0 = nt * 8 + (lane & 3) * 2;
-        const float f0 = fbuf[warp * RT + r0], f1 = fbuf[warp * RT + r0 + 1];
-        const bool ok0 = r0 < n_rows, ok1 = r0 + 1 < n_rows;
+      for (int round = 0; round < kWarps; ++round) {
+        const int slice = (warp + round) % kWarps;
 #pragma unroll
-        for (int mt = 0; mt < KT; ++mt) {
-          const int d = mt * 16 + (lane >> 2);
-          if (ok0) {
-            atomicAdd(&obuf[r0 * D + d], acc[nt][mt][0] * f0);
-            atomicAdd(&obuf[r0 * D + d + 8], acc[nt][mt][2] * f0);
-          }
-          if (ok1) {
-            atomicAdd(&obuf[(r0 + 1) * D + d], acc[nt][mt][1] * f1);
-            atomicAdd(&obuf[(r0 + 1) * D + d + 8], acc[nt][mt][3] * f1);
+        for (int nt = 0; nt < NT; ++nt) {
+          const int r0 = nt * 8 + (lane & 3) * 2;
+          const float f0 = f_own[nt][0], f1 = f_own[nt][1];
+#pragma unroll
+          for (int mi = 0; mi < KT / kWarps; ++mi) {
+#pragma unroll
+            for (int sl = 0; sl < kWarps; ++sl) {
+              if (sl == slice) {  // compile-time accumulator index in every branch
+                const int mt = sl * (KT / kWarps) + mi;
+                const int d = mt * 16 + (lane >> 2);
+                float* o0 = &obuf[r0 * D + d];
+                float* o1 = &obuf[(r0 + 1) * D + d];
+                if (round == 0) {
+                  o0[0] = acc[nt][mt][0] * f0;
+                  o0[8] = acc[nt][mt][2] * f0;
+                  o1[0] = acc[nt][mt][1] * f1;
+                  o1[8] = acc[nt][mt][3] * f1;
+                } else {
+                  o0[0] += acc[nt][mt][0] * f0;
+                  o0[8] += acc[nt][mt][2] * f0;
+                  o1[0] += acc[nt][mt][1] * f1;
+                  o1[8] += acc[nt][mt][3] * f1;
+                }
+              }
+            }
           }
         }
+        __syncthreads();
       }
-      __syncthreads();
       if (cc.u.slot < 0) {
         T* out = reinterpret_cast<T*>(p.out);
         for (int i = tid; i < n_rows * (D / 2); i += kThreads) {
@@ -408,7 +429,6 @@ rpa_splitkv_kernel(const Params p) {
           const int qt = R / G, g = R - qt * G;
           const float sc = row_scale[r];
           const float2 v = *reinterpret_cast<float2*>(&obuf[r * D + d]);
-          *reinterpret_cast<float2*>(&obuf[r * D + d]) = make_float2(0.f, 0.f);
           const uint32_t pk = Mma<T>::pack(v.x * sc, v.y * sc);
           *reinterpret_cast<uint32_t*>(out + ((size_t)(cc.u.q_start + qt) * p.Hq + cc.h * G + g) * D + d) = pk;
         }
@@ -418,12 +438,11 @@ rpa_splitkv_kernel(const Params p) {
         for (int i = tid; i < n_rows * (D / 4); i += kThreads) {
           const int r = i / (D / 4), d = (i % (D / 4)) * 4;
           const float4 v = *reinterpret_cast<float4*>(&obuf[r * D + d]);
-          *reinterpret_cast<float4*>(&obuf[r * D + d]) = make_float4(0.f, 0.f, 0.f, 0.f);
           *reinterpret_cast<float4*>(po + r * D + d) = v;
         }
         if (tid < n_rows) pml[tid] = make_float2(row_m[tid], row_l[tid]);
       }
-      // the next reader/writer of obuf/mbuf is separated from here by the stage barrier below
+      // the next item's writes to mbuf/obuf/row_* are separated from these reads by the stage barrier
     }
 
     // advance the consumer
@@ -472,7 +491,7 @@ cudaError_t dispatch(const Params& p, int n_sm, cudaStream_t stream) {
     case 128:
       return wide ? launch_one<T, 128, 2, 3>(p, n_sm, stream) : launch_one<T, 128, 1, 3>(p, n_sm, stream);
     case 256:
-      return wide ? launch_one<T, 256, 2, 3>(p, n_sm, stream) : launch_one<T, 256, 1, 3>(p, n_sm, stream);
+      return wide ? launch_one<T, 256, 2, 2>(p, n_sm, stream) : launch_one<T, 256, 1, 3>(p, n_sm, stream);
   }
   return cudaErrorInvalidValue;
 }

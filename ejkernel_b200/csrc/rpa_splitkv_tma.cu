@@ -1,0 +1,668 @@
+// Split-KV ragged paged attention, TMA variant: the page-table driven gather is issued by one
+// producer warp as bulk tensor copies (cp.async.bulk.tensor, one box per KV page block, mbarrier
+// tracked), four consumer warps do the math.  Same work items, same shared-memory tile layout and
+// the same transposed mma formulation as rpa_splitkv.cu; what changes is who moves the bytes:
+//
+//   producer warp : pulls work items from a device queue, looks up page ids, issues one 5-D TMA
+//                   box {64 elems, PB tokens, D/64, (K_h,V_h), 1 page} per page block of the
+//                   64-token stage with SWIZZLE_128B, stages the item's query tile, publishes
+//                   per-stage metadata, and runs up to NS stages ahead across item boundaries.
+//   consumer warps: wait on the stage's "full" mbarrier, take 16 tokens each, release the stage
+//                   through the "empty" mbarrier; at the end of an item they combine through
+//                   shared memory and write final rows or a split-KV partial.
+//
+// Replaces ejkernel/kernels/_xla/ragged_page_attention/_xla_impl_fwd.py:99-159 of the reference
+// (page gather + two einsums + online softmax).  No cluster multicast is used anywhere.
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the warp raises
+// EJK_RPA_ST_TIMEOUT, sets the CTA's abort flag and returns, and every other wait of the CTA
+// gives up as soon as it sees the flag, so a protocol error can never hang the device.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "rpa_device.cuh"
+#include "rpa_types.h"
+
+namespace ejk {
+namespace {
+
+constexpr int kConsumerWarps = 4;
+constexpr int kThreadsTma = (kConsumerWarps + 1) * 32;
+constexpr int kRingTma = 8;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLazyRescale = 8.0f;  // rescale the accumulators only when the max grows by 2^8
+
+struct ItemDesc {
+  Unit u;
+  int32_t h;
+  int32_t pad[7];
+};
+
+template <int D, int NT, int NS>
+struct CfgT {
+  static constexpr int TK = kTileTokens;
+  static constexpr int RT = 8 * NT;
+  static constexpr int STAGE_BYTES = TK * 2 * D * 2;
+  static constexpr int Q_ROW_BYTES = D * 2 + 16;
+  static constexpr int Q_BYTES = RT * Q_ROW_BYTES;
+  static constexpr int OFF_Q = NS * STAGE_BYTES;
+  static constexpr int OFF_OBUF = OFF_Q + NS * Q_BYTES;
+  static constexpr int OFF_MBUF = OFF_OBUF + RT * D * 4;
+  static constexpr int OFF_LBUF = OFF_MBUF + kConsumerWarps * RT * 4;
+  static constexpr int OFF_FBUF = OFF_LBUF + kConsumerWarps * RT * 4;
+  static constexpr int OFF_ROWSCALE = OFF_FBUF + kConsumerWarps * RT * 4;
+  static constexpr int OFF_ROWM = OFF_ROWSCALE + RT * 4;
+  static constexpr int OFF_ROWL = OFF_ROWM + RT * 4;
+  static constexpr int OFF_RING = (OFF_ROWL + RT * 4 + 63) / 64 * 64;
+  static constexpr int OFF_META = OFF_RING + kRingTma * (int)sizeof(ItemDesc);
+  static constexpr int OFF_BAR = OFF_META + NS * 8;        // full[NS], empty[NS], cbar
+  static constexpr int OFF_ABORT = OFF_BAR + (2 * NS + 1) * 8;
+  static constexpr int SMEM_BYTES = OFF_ABORT + 16 + 1024;  // + alignment slack
+};
+
+// ---- mbarrier / TMA wrappers ----
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait, called by all 32 lanes of a warp; false = gave up (timeout or another warp
+// aborted).  The verdict is made warp-uniform so the lanes never part ways on it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  bool ok = false;
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) {
+      ok = true;
+      break;
+    }
+    if ((i & 255u) == 255u && *abort_flag) break;
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (!ok) *abort_flag = 1;
+  return ok;
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+
+template <typename T, int D, int NT, int NS>
+__global__ void __launch_bounds__(kThreadsTma, (CfgT<D, NT, NS>::SMEM_BYTES <= 112 * 1024) ? 2 : 1)
+rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
+  using C = CfgT<D, NT, NS>;
+  constexpr int TK = C::TK, RT = C::RT;
+  constexpr int KT = D / 16;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  float* obuf = reinterpret_cast<float*>(smem + C::OFF_OBUF);
+  float* mbuf = reinterpret_cast<float*>(smem + C::OFF_MBUF);
+  float* lbuf = reinterpret_cast<float*>(smem + C::OFF_LBUF);
+  float* row_scale = reinterpret_cast<float*>(smem + C::OFF_ROWSCALE);
+  float* row_m = reinterpret_cast<float*>(smem + C::OFF_ROWM);
+  float* row_l = reinterpret_cast<float*>(smem + C::OFF_ROWL);
+  ItemDesc* ring = reinterpret_cast<ItemDesc*>(smem + C::OFF_RING);
+  int2* metas = reinterpret_cast<int2*>(smem + C::OFF_META);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT);
+  const uint32_t bar_full = smem_base + C::OFF_BAR;
+  const uint32_t bar_empty = bar_full + NS * 8;
+  const uint32_t bar_c = bar_empty + NS * 8;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int Hkv = p.Hkv, G = p.G;
+  const int n_work = p.header[kHdrNumUnits] * Hkv;
+  const int pb = p.tma_block_tokens;       // tokens per TMA box (power of two, >= 8)
+  const int pb_shift = p.tma_block_shift;
+  unsigned flags = 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_empty + s * 8, kConsumerWarps);
+    }
+    mbar_init(bar_c, kConsumerWarps);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // =============================== producer warp ===============================
+    const int blocks_per_stage = TK >> pb_shift;
+    const uint32_t box_bytes = (uint32_t)pb * 2 * D * sizeof(T);
+    int s = 0;
+    uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1: all stages start empty
+    int k = 0;
+    int wid = 0;
+    if (lane == 0) wid = atomicAdd(&p.header[kHdrQueue], 1);
+    wid = __shfl_sync(0xffffffffu, wid, 0);
+    bool alive = true;
+    while (alive) {
+      if (wid >= n_work) {
+        // end-of-stream marker for the consumers
+        if (!mbar_wait(bar_empty + s * 8, empty_parity, abort_flag)) break;
+        if (lane == 0) {
+          metas[s] = make_int2(-1, 0);
+          mbar_arrive(bar_full + s * 8);
+        }
+        break;
+      }
+      const int ui = wid / Hkv;
+      const int h = wid - ui * Hkv;
+      Unit u;
+      {
+        const int4* src = reinterpret_cast<const int4*>(p.units + ui);
+        const int4 a = __ldg(src), b = __ldg(src + 1);
+        u.seq = a.x; u.row0 = a.y; u.kv_begin = a.z; u.kv_end = a.w;
+        u.slot = b.x; u.q_start = b.y; u.q_len = b.z; u.kv_len = b.w;
+      }
+      const int ring_slot = k % kRingTma;
+      int wid_next = 0;
+      if (lane == 0) wid_next = atomicAdd(&p.header[kHdrQueue], 1);  // consumed only at the next item
+      const int32_t* tab = p.block_tables + (size_t)u.seq * p.pages_per_seq;
+      bool first = true;
+      for (int pos = u.kv_begin; first || pos < u.kv_end; pos += TK) {
+        if (!mbar_wait(bar_empty + s * 8, empty_parity, abort_flag)) {
+          alive = false;
+          break;
+        }
+        if (first) {
+          // the item's descriptor and query tile travel with its first stage
+          if (lane == 0) {
+            ItemDesc d;
+            d.u = u;
+            d.h = h;
+            ring[ring_slot] = d;
+          }
+          constexpr int QCH = D / 8;
+          uint8_t* qdst = smem + C::OFF_Q + s * C::Q_BYTES;
+          const int rows_total = u.q_len * G;
+          for (int cidx = lane; cidx < RT * QCH; cidx += 32) {
+            const int r = cidx / QCH, ch = cidx % QCH;
+            const int R = u.row0 + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (R < rows_total) {
+              const int qt = R / G, g = R - qt * G;
+              v = __ldg(reinterpret_cast<const uint4*>(
+                  reinterpret_cast<const uint8_t*>(p.q) +
+                  ((size_t)(u.q_start + qt) * p.Hq + h * G + g) * D * sizeof(T) + ch * 16));
+            }
+            *reinterpret_cast<uint4*>(qdst + r * C::Q_ROW_BYTES + ch * 16) = v;
+          }
+        }
+        int nblk = (u.kv_end - pos + pb - 1) >> pb_shift;
+        if (nblk > blocks_per_stage) nblk = blocks_per_stage;
+        if (nblk < 0) nblk = 0;
+        __syncwarp();
+        if (lane == 0) {
+          metas[s] = make_int2(ring_slot, pos);
+          if (nblk > 0) mbar_arrive_expect_tx(bar_full + s * 8, (uint32_t)nblk * box_bytes);
+          else mbar_arrive(bar_full + s * 8);
+        }
+        __syncwarp();
+        if (lane < nblk) {
+          const int key = pos + (lane << pb_shift);
+          int pi, off;
+          if (p.page_shift >= 0) {
+            pi = key >> p.page_shift;
+            off = key & (p.page_size - 1);
+          } else {
+            pi = key / p.page_size;
+            off = key - pi * p.page_size;
+          }
+          int page = __ldg(tab + pi);
+          if ((unsigned)page >= (unsigned)p.num_pages) {
+            flags |= EJK_RPA_ST_PAGE_ID;
+            page = 0;
+          }
+          tma_load_5d(smem_base + s * C::STAGE_BYTES + lane * box_bytes, &tmap, bar_full + s * 8, 0, off, 0, 2 * h, page);
+        }
+        first = false;
+        if (++s == NS) {
+          s = 0;
+          empty_parity ^= 1u;
+        }
+      }
+      ++k;
+      wid = __shfl_sync(0xffffffffu, wid_next, 0);
+    }
+    // Leave only after every bulk copy this warp issued has landed: wait (bounded) for the
+    // consumers to drain all stages, which implies all "full" phases completed.
+    for (int i = 0; i < NS; ++i) {
+      if (!mbar_wait(bar_empty + s * 8, empty_parity, abort_flag)) break;
+      if (++s == NS) {
+        s = 0;
+        empty_parity ^= 1u;
+      }
+    }
+    if (*abort_flag) flags |= EJK_RPA_ST_TIMEOUT;
+  } else {
+    // =============================== consumer warps ===============================
+    // per-thread shared-memory offsets of the ldmatrix rows (constant for the whole kernel)
+    const uint32_t swz = (uint32_t)(lane & 7) << 4;
+    const uint32_t dc_stride = (uint32_t)pb * 128;
+    uint32_t k_off, v_off;
+    {
+      const int tl = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;  // K: second matrix = tokens 8..15
+      const int j = tl >> pb_shift, tp = tl & (pb - 1);
+      k_off = (uint32_t)((j * 2) * (D / 64)) * dc_stride + (uint32_t)tp * 128;
+      const int tv = warp * 16 + (lane & 7) + (lane >> 4) * 8;        // V: third/fourth matrix = tokens 8..15
+      const int jv = tv >> pb_shift, tpv = tv & (pb - 1);
+      v_off = (uint32_t)((jv * 2 + 1) * (D / 64)) * dc_stride + (uint32_t)tpv * 128;
+    }
+    const int k_dhalf = lane >> 4, v_dhalf = (lane >> 3) & 1;
+
+    uint32_t qf[NT][KT][2];
+    float acc[NT][KT][4];
+    float m_run[NT][2], l_run[NT][2];
+    int pos_r[NT][2], lo_r[NT][2];
+    int pos_min = 0, lo_max = 0;
+    int s = 0;
+    uint32_t full_parity = 0, c_parity = 0;
+
+    auto consumer_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_c);
+      const bool ok = mbar_wait(bar_c, c_parity, abort_flag);
+      c_parity ^= 1u;
+      return ok;
+    };
+
+    while (true) {
+      if (!mbar_wait(bar_full + s * 8, full_parity, abort_flag)) break;
+      const int2 meta = metas[s];
+      if (meta.x < 0) break;
+      const ItemDesc& it = ring[meta.x];
+      const Unit u = it.u;
+      const int h = it.h;
+      const int pos = meta.y;
+      const uint32_t sbase = smem_base + s * C::STAGE_BYTES;
+      const int rows_total = u.q_len * G;
+      int n_rows = rows_total - u.row0;
+      if (n_rows > RT) n_rows = RT;
+
+      if (pos == u.kv_begin) {
+        const uint8_t* qs = smem + C::OFF_Q + s * C::Q_BYTES;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint8_t* qrow = qs + (nt * 8 + (lane >> 2)) * C::Q_ROW_BYTES + (lane & 3) * 4;
+#pragma unroll
+          for (int kt = 0; kt < KT; ++kt) {
+            qf[nt][kt][0] = *reinterpret_cast<const uint32_t*>(qrow + kt * 32);
+            qf[nt][kt][1] = *reinterpret_cast<const uint32_t*>(qrow + kt * 32 + 16);
+          }
+        }
+        const int base = u.kv_len - u.q_len;
+        pos_min = base + u.row0 / G;
+        lo_max = (p.window > 0) ? (base + (u.row0 + n_rows - 1) / G - p.window) : -1;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int R = u.row0 + nt * 8 + (lane & 3) * 2 + j;
+            const int ps = (R < rows_total) ? base + R / G : -1;
+            pos_r[nt][j] = ps;
+            lo_r[nt][j] = (p.window > 0) ? ps - p.window : -1;
+            m_run[nt][j] = -INFINITY;
+            l_run[nt][j] = 0.f;
+          }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int kt = 0; kt < KT; ++kt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[nt][kt][e] = 0.f;
+      }
+
+      const int key0 = pos + warp * 16;
+      if (key0 < u.kv_end) {
+        float sc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) sc[nt][e] = 0.f;
+#pragma unroll
+        for (int kt = 0; kt < KT; ++kt) {
+          const int d16 = kt * 2;  // + k_dhalf at run time; both fold into one XOR below
+          uint32_t a[4];
+          ldmatrix_x4(a, sbase + k_off + (uint32_t)(d16 >> 3) * dc_stride +
+                             ((((uint32_t)(d16 & 7) | (uint32_t)k_dhalf) << 4) ^ swz));
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) Mma<T>::run(sc[nt], a, qf[nt][kt][0], qf[nt][kt][1]);
+        }
+        const bool tail = key0 + 16 > u.kv_end;  // tokens past the chunk end: stale or unowned bytes
+        const bool need_mask = tail || (key0 + 15 > pos_min) || (key0 <= lo_max);
+        uint32_t pbf[NT][2];
+        bool grow = false;
+        float mx[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float x = sc[nt][e];
+            if (p.cap != 0.f) x = p.cap_log2 * soft_cap_tanh(x * p.inv_cap_scale);
+            else x *= p.scale_log2;
+            if (need_mask) {
+              const int key = key0 + (lane >> 2) + (e >> 1) * 8;
+              const int j = e & 1;
+              if (key > pos_r[nt][j] || key <= lo_r[nt][j]) x = -INFINITY;
+            }
+            sc[nt][e] = x;
+          }
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            float v = fmaxf(sc[nt][j], sc[nt][j + 2]);
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+            mx[nt][j] = v;
+            // lazy rescaling: keep the old reference maximum unless the new one is 2^8 larger
+            grow |= (v > m_run[nt][j] + kLazyRescale) || (m_run[nt][j] == -INFINITY && v > -INFINITY);
+          }
+        }
+        if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            float alpha[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const bool g = (mx[nt][j] > m_run[nt][j] + kLazyRescale) || (m_run[nt][j] == -INFINITY && mx[nt][j] > -INFINITY);
+              const float m_new = g ? mx[nt][j] : m_run[nt][j];
+              alpha[j] = g ? fast_exp2(m_run[nt][j] - m_new) : 1.f;  // exp2(-inf) = 0 on the first tile
+              m_run[nt][j] = m_new;
+              l_run[nt][j] *= alpha[j];
+            }
+#pragma unroll
+            for (int kt = 0; kt < KT; ++kt) {
+              acc[nt][kt][0] *= alpha[0];
+              acc[nt][kt][1] *= alpha[1];
+              acc[nt][kt][2] *= alpha[0];
+              acc[nt][kt][3] *= alpha[1];
+            }
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const float m_use = (m_run[nt][j] == -INFINITY) ? 0.f : m_run[nt][j];
+            const float p0 = fast_exp2(sc[nt][j] - m_use);
+            const float p1 = fast_exp2(sc[nt][j + 2] - m_use);
+            sc[nt][j] = p0;
+            sc[nt][j + 2] = p1;
+            l_run[nt][j] += p0 + p1;
+          }
+          pbf[nt][0] = movmatrix_trans(Mma<T>::pack(sc[nt][0], sc[nt][1]));
+          pbf[nt][1] = movmatrix_trans(Mma<T>::pack(sc[nt][2], sc[nt][3]));
+        }
+        // V^T fragments; in a tail tile the registers of tokens >= kv_end are cleared so that
+        // 0 * (stale NaN) can never reach the accumulators
+        uint32_t vmask_lo = 0xffffffffu, vmask_hi = 0xffffffffu;
+        if (tail) {
+          const int t0 = key0 + (lane & 3) * 2;
+          vmask_lo = (t0 < u.kv_end ? 0x0000ffffu : 0u) | (t0 + 1 < u.kv_end ? 0xffff0000u : 0u);
+          vmask_hi = (t0 + 8 < u.kv_end ? 0x0000ffffu : 0u) | (t0 + 9 < u.kv_end ? 0xffff0000u : 0u);
+        }
+#pragma unroll
+        for (int mt = 0; mt < KT; ++mt) {
+          const int d16 = mt * 2;
+          uint32_t a[4];
+          ldmatrix_x4_trans(a, sbase + v_off + (uint32_t)(d16 >> 3) * dc_stride +
+                                   ((((uint32_t)(d16 & 7) | (uint32_t)v_dhalf) << 4) ^ swz));
+          if (tail) {
+            a[0] &= vmask_lo;
+            a[1] &= vmask_lo;
+            a[2] &= vmask_hi;
+            a[3] &= vmask_hi;
+          }
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) Mma<T>::run(acc[nt][mt], a, pbf[nt][0], pbf[nt][1]);
+        }
+      }
+      // this warp is done with the stage's bytes (query fragments are in registers by now)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty + s * 8);
+
+      if (pos + TK >= u.kv_end) {
+        // ---- end of item: combine the four warps ----
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            float l = l_run[nt][j];
+            l += __shfl_xor_sync(0xffffffffu, l, 4);
+            l += __shfl_xor_sync(0xffffffffu, l, 8);
+            l += __shfl_xor_sync(0xffffffffu, l, 16);
+            if (lane < 4) {
+              const int r = nt * 8 + lane * 2 + j;
+              mbuf[warp * RT + r] = m_run[nt][j];
+              lbuf[warp * RT + r] = l;
+            }
+          }
+        if (!consumer_sync()) break;
+        // Every lane derives the rescale factors of its own rows from the four (m, l) pairs; the
+        // accumulators are then added into obuf in four rounds, warp w handling the d-slice
+        // (w + round) % 4, so each address receives its four contributions in a fixed order and
+        // the result does not depend on warp timing (no floating-point atomics).
+        float f_own[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int r = nt * 8 + (lane & 3) * 2 + j;
+            float mt = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) mt = fmaxf(mt, mbuf[w * RT + r]);
+            const float mu = (mt == -INFINITY) ? 0.f : mt;
+            f_own[nt][j] = fast_exp2(m_run[nt][j] - mu);
+          }
+        if (tid < RT) {
+          const int r = tid;
+          float mt = -INFINITY;
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w) mt = fmaxf(mt, mbuf[w * RT + r]);
+          const float mu = (mt == -INFINITY) ? 0.f : mt;
+          float lt = 0.f;
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w) lt += lbuf[w * RT + r] * fast_exp2(mbuf[w * RT + r] - mu);
+          float scl = 1.f;
+          if (u.slot < 0) {
+            float l_fin = lt;
+            if (p.num_sinks > 0 && r < n_rows) {
+              // attention sinks join the denominator only (_xla_impl_fwd.py:161-172)
+              const int R = u.row0 + r;
+              const int hq = h * G + (R % G);
+              const int srow = (p.sink_rows == p.Hq) ? hq : (p.sink_rows == Hkv ? h : 0);
+              const float* sk = p.sinks + (size_t)srow * p.num_sinks;
+              float sm = -INFINITY;
+              for (int i = 0; i < p.num_sinks; ++i) sm = fmaxf(sm, sk[i] * kLog2e);
+              const float m_fin = fmaxf(mt, sm);
+              const float mf = (m_fin == -INFINITY) ? 0.f : m_fin;
+              scl = fast_exp2(mt - mf);
+              l_fin = lt * scl;
+              for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
+            }
+            scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
+          }
+          row_scale[r] = scl;
+          row_m[r] = mt;
+          row_l[r] = lt;
+        }
+        bool alive_c = true;
+#pragma unroll
+        for (int round = 0; round < kConsumerWarps; ++round) {
+          const int slice = (warp + round) % kConsumerWarps;
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const int r0 = nt * 8 + (lane & 3) * 2;
+            const float f0 = f_own[nt][0], f1 = f_own[nt][1];
+#pragma unroll
+            for (int mi = 0; mi < KT / kConsumerWarps; ++mi) {
+              // compile-time accumulator index in every branch keeps acc[] in registers
+#pragma unroll
+              for (int sl = 0; sl < kConsumerWarps; ++sl) {
+                if (sl == slice) {
+                  const int mt = sl * (KT / kConsumerWarps) + mi;
+                  const int d = mt * 16 + (lane >> 2);
+                  float* o0 = &obuf[r0 * D + d];
+                  float* o1 = &obuf[(r0 + 1) * D + d];
+                  if (round == 0) {
+                    o0[0] = acc[nt][mt][0] * f0;
+                    o0[8] = acc[nt][mt][2] * f0;
+                    o1[0] = acc[nt][mt][1] * f1;
+                    o1[8] = acc[nt][mt][3] * f1;
+                  } else {
+                    o0[0] += acc[nt][mt][0] * f0;
+                    o0[8] += acc[nt][mt][2] * f0;
+                    o1[0] += acc[nt][mt][1] * f1;
+                    o1[8] += acc[nt][mt][3] * f1;
+                  }
+                }
+              }
+            }
+          }
+          if (!consumer_sync()) {
+            alive_c = false;
+            break;
+          }
+        }
+        if (!alive_c) break;
+        constexpr int kCT = kConsumerWarps * 32;
+        if (u.slot < 0) {
+          T* out = reinterpret_cast<T*>(p.out);
+          for (int i = tid; i < n_rows * (D / 2); i += kCT) {
+            const int r = i / (D / 2), d = (i % (D / 2)) * 2;
+            const int R = u.row0 + r;
+            const int qt = R / G, g = R - qt * G;
+            const float scl = row_scale[r];
+            const float2 v = *reinterpret_cast<float2*>(&obuf[r * D + d]);
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(u.q_start + qt) * p.Hq + h * G + g) * D + d) =
+                Mma<T>::pack(v.x * scl, v.y * scl);
+          }
+        } else {
+          float* po = p.part_o + ((size_t)u.slot * Hkv + h) * RT * D;
+          float2* pml = p.part_ml + ((size_t)u.slot * Hkv + h) * RT;
+          for (int i = tid; i < n_rows * (D / 4); i += kCT) {
+            const int r = i / (D / 4), d = (i % (D / 4)) * 4;
+            const float4 v = *reinterpret_cast<float4*>(&obuf[r * D + d]);
+            *reinterpret_cast<float4*>(po + r * D + d) = v;
+          }
+          if (tid < n_rows) pml[tid] = make_float2(row_m[tid], row_l[tid]);
+        }
+        // The next item's writes to mbuf/lbuf come before its first consumer_sync, but they only
+        // race with readers of mbuf/lbuf, and those finished before round 0's sync above; its
+        // writes to obuf/row_* come after its first consumer_sync, which every warp reaches only
+        // after finishing the loops above.
+      }
+      if (++s == NS) {
+        s = 0;
+        full_parity ^= 1u;
+      }
+    }
+    if (*abort_flag) flags |= EJK_RPA_ST_TIMEOUT;
+  }
+  if (flags && p.status) atomicOr(reinterpret_cast<unsigned*>(p.status), flags);
+}
+
+// ---- host side: tensor map over kv_pages ----
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeFn>(ptr);
+  }
+  return fn;
+}
+
+template <typename T, int D, int NT, int NS>
+cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream) {
+  using C = CfgT<D, NT, NS>;
+  auto kern = rpa_splitkv_tma_kernel<T, D, NT, NS>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int per_sm = (C::SMEM_BYTES <= 112 * 1024) ? 2 : 1;
+  kern<<<n_sm * per_sm, kThreadsTma, C::SMEM_BYTES, stream>>>(map, p);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t dispatch(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream) {
+  const bool wide = p.rows_per_tile == 16;
+  switch (p.D) {
+    case 64:
+      return wide ? launch_one<T, 64, 2, 4>(p, map, n_sm, stream) : launch_one<T, 64, 1, 4>(p, map, n_sm, stream);
+    case 128:
+      return wide ? launch_one<T, 128, 2, 3>(p, map, n_sm, stream) : launch_one<T, 128, 1, 3>(p, map, n_sm, stream);
+    case 256:
+      return wide ? launch_one<T, 256, 2, 2>(p, map, n_sm, stream) : launch_one<T, 256, 1, 3>(p, map, n_sm, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+bool tma_path_supported(const Params& p) {
+  const int ps = p.page_size;
+  if (ps < 8 || (ps & (ps - 1)) != 0) return false;  // boxes must be whole 1024-byte swizzle atoms
+  return encode_fn() != nullptr;
+}
+
+cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return cudaErrorNotSupported;
+  const uint64_t esz = 2;
+  const uint64_t D = p.D, C2 = 2ull * p.Hkv;
+  // dims, innermost first: 64 elements | token in page | 64-element chunk of D | combined head | page
+  cuuint64_t dims[5] = {64, (cuuint64_t)p.page_size, D / 64, C2, (cuuint64_t)p.num_pages};
+  cuuint64_t strides[4] = {C2 * D * esz, 64 * esz, D * esz, (cuuint64_t)p.page_size * C2 * D * esz};
+  cuuint32_t box[5] = {64, (cuuint32_t)p.tma_block_tokens, (cuuint32_t)(D / 64), 2, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUtensorMap map;
+  const CUtensorMapDataType dt = (dtype == EJK_RPA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = enc(&map, dt, 5, const_cast<void*>(p.kv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16>(p, map, n_sm, stream);
+  return dispatch<__half>(p, map, n_sm, stream);
+}
+
+}  // namespace ejk

@@ -77,11 +77,15 @@ struct Params {
   float cap_log2;      // cap * log2(e)
   float inv_cap_scale; // softmax_scale / cap
   int32_t page_shift;  // log2(page_size) if a power of two, else -1
+  int32_t tma_block_tokens;  // tokens per TMA box = min(page_size, kTileTokens)
+  int32_t tma_block_shift;   // log2 of the above
 };
 
 // launchers (each returns cudaError_t of the launch)
 cudaError_t launch_plan(const Params& p, cudaStream_t stream);
 cudaError_t launch_splitkv(const Params& p, int dtype, int n_sm, cudaStream_t stream);
+bool tma_path_supported(const Params& p);
+cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 
 }  // namespace ejk

@@ -64,6 +64,7 @@ extern "C" {
 #define EJK_RPA_ST_KVLEN 4u     /* kv_len < 0 or > pages_per_seq * page_size */
 #define EJK_RPA_ST_PAGE_ID 8u   /* a page id outside [0, num_pages) was met (read as page 0) */
 #define EJK_RPA_ST_INTERNAL 16u /* planner produced more work items than the workspace holds */
+#define EJK_RPA_ST_TIMEOUT 32u  /* a bounded wait inside a kernel ran out (outputs are invalid) */
 
 /* Static problem description: everything here is known from array shapes at trace time. */
 typedef struct ejk_rpa_shape {
@@ -117,9 +118,10 @@ EJK_RPA_API int ejk_rpa_launch(const void* queries, const void* kv_pages, const 
                    int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream);
 
 /* Process-wide tuning knobs (host side, not thread safe against concurrent launches):
- *   "waves"      work items per resident CTA the device planner aims for (default 16)
+ *   "waves"      work items per resident CTA the device planner aims for (default 8)
  *   "min_chunk"  smallest KV chunk, in tokens, a split may have (default 256)
  *   "path"       0 = auto, 1 = force the cp.async gather, 2 = force the TMA gather
+ *   "profile"    1 = record CUDA events around each kernel of a launch (see ejk_rpa_profile_read)
  * Returns 0, or EJK_RPA_E_ARG for an unknown name.  Counterpart of the reference's
  * EJKERNEL_* environment switches (ejkernel/ops/config/selection.py:328). */
 EJK_RPA_API int ejk_rpa_set_option(const char* name, int value);
@@ -128,6 +130,13 @@ EJK_RPA_API int ejk_rpa_get_option(const char* name, int* value);
 /* Number of kernels the last ejk_rpa_launch on this thread enqueued (host-side counter, for
  * benchmark bookkeeping). */
 EJK_RPA_API int ejk_rpa_last_launch_count(void);
+
+/* With option "profile" = 1, waits for the calling thread's last launch and returns the device
+ * time of its planner, gather/attention and merge kernels in milliseconds (null pointers are
+ * skipped).  EJK_RPA_E_ARG if no profiled launch exists.  This call synchronises; it is the
+ * measuring hook that replaces the reference's wall-clock Tuner.measure
+ * (ejkernel/ops/config/selection.py:226-245). */
+EJK_RPA_API int ejk_rpa_profile_read(float* plan_ms, float* main_ms, float* merge_ms);
 
 #ifdef __cplusplus
 }

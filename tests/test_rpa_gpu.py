@@ -169,10 +169,10 @@ def test_planted_keys_give_order_one_outputs(rpa_lib):
         for j in rng.choice(kl - 4, size=3, replace=False):
             pg, sl = int(tab[s, j // 16]), int(j % 16)
             for h in range(2):
-                kv[pg, sl, 2 * h] = q[cu[s], h * 4] * 0.6
+                kv[pg, sl, 2 * h] = q[cu[s], h * 4]
     b.kv_pages = kv.to(torch.bfloat16)
     r = _check(b, "planted")
-    assert r["rms_want"] > 0.2
+    assert r["rms_want"] > 0.15
 
 
 def test_deterministic_and_unaffected_by_poisoned_scratch(rpa_lib):
