@@ -90,14 +90,14 @@ def all_gather_heads(local_out: torch.Tensor, mesh: Mesh1D) -> torch.Tensor:
     if n == 1:
         return local_out
     T, Hl, D = local_out.shape
-    buf = torch.empty((n, T, Hl, D), dtype=local_out.dtype, device=local_out.device)
+    src = local_out.contiguous()
     if local_out.is_cuda:
-        dist.all_gather_into_tensor(buf, local_out.contiguous(), group=mesh.group)
-    else:  # gloo has no all_gather_into_tensor for every dtype; use the list form
-        parts = list(buf.unbind(0))
-        src = local_out.contiguous()
-        if src.dtype == torch.bfloat16:  # gloo moves bf16 as raw 16-bit words
-            dist.all_gather([p.view(torch.int16) for p in parts], src.view(torch.int16), group=mesh.group)
-        else:
-            dist.all_gather(parts, src, group=mesh.group)
+        buf = torch.empty((n, T, Hl, D), dtype=local_out.dtype, device=local_out.device)
+        dist.all_gather_into_tensor(buf, src, group=mesh.group)
+    else:
+        # gloo (CPU tests): list form, 16-bit floats moved as raw bytes
+        raw = src.view(torch.uint8) if src.element_size() == 2 else src
+        parts = [torch.empty_like(raw) for _ in range(n)]
+        dist.all_gather(parts, raw, group=mesh.group)
+        buf = torch.stack(parts, 0).view(local_out.dtype).reshape(n, T, Hl, D)
     return buf.permute(1, 0, 2, 3).reshape(T, n * Hl, D)

@@ -207,7 +207,7 @@ def blocked_as_written(
     out = torch.zeros_like(q)
     sinks = None
     if softmax_aux is not None:
-        sinks = torch.as_tensor(_sinks_per_q_head(softmax_aux, Hq, Hkv)).float().reshape(Hkv, G, -1)
+        sinks = torch.as_tensor(np.array(_sinks_per_q_head(softmax_aux, Hq, Hkv))).float().reshape(Hkv, G, -1)
 
     kv_tokens_per_block = page * kvblocks
     base_k = torch.arange(kv_tokens_per_block)

@@ -22,6 +22,15 @@ def _check(batch, what, **kw):
     return assert_parity(out, oracle(batch), batch.total_tokens, what=what, **kw)
 
 
+def test_golden_fixtures(rpa_lib):
+    from pathlib import Path
+    from tests.golden.make_golden import cases
+    golden = np.load(Path(__file__).parent / "golden" / "rpa_golden.npz")
+    for name, b in cases():
+        out = run_cuda(b)
+        assert_parity(out, golden[f"{name}.out"].astype(np.float64), b.total_tokens, what=f"golden {name}")
+
+
 def test_c1_decode_toy(rpa_lib):
     _check(make_workload("c1"), "c1")
 
