@@ -15,6 +15,8 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libejk_rpa.so"
 
 BF16, F16 = 0, 1
+STATIC_SCRATCH_BYTES = 32 << 20
+E_SCRATCH = -9
 
 ST_NUM_SEQS, ST_QLEN, ST_KVLEN, ST_PAGE_ID, ST_INTERNAL, ST_TIMEOUT = 1, 2, 4, 8, 16, 32
 STATUS_TEXT = {
@@ -35,6 +37,7 @@ EXPORTS = (
     "ejk_rpa_get_option",
     "ejk_rpa_last_launch_count",
     "ejk_rpa_profile_read",
+    "ejk_rpa_launch_static_scratch",
 )
 
 
@@ -111,6 +114,16 @@ def load() -> ctypes.CDLL:
     lib.ejk_rpa_get_option.argtypes = [c_char_p, POINTER(c_int)]
     lib.ejk_rpa_last_launch_count.restype = c_int
     lib.ejk_rpa_last_launch_count.argtypes = []
+    lib.ejk_rpa_launch_static_scratch.restype = c_int
+    lib.ejk_rpa_launch_static_scratch.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # queries .. num_seqs
+        c_void_p,  # softmax_aux
+        c_void_p,  # out
+        c_void_p,  # status
+        POINTER(Shape),
+        POINTER(Attrs),
+        c_void_p,  # stream
+    ]
     lib.ejk_rpa_profile_read.restype = c_int
     lib.ejk_rpa_profile_read.argtypes = [POINTER(c_float), POINTER(c_float), POINTER(c_float)]
     _lib = lib

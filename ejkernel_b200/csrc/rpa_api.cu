@@ -106,6 +106,9 @@ const char* ejk_rpa_error_string(int code) {
     case EJK_RPA_E_ARG: return "invalid attribute (sliding_window, logits_soft_cap, softmax_aux or option name)";
     case EJK_RPA_E_DEVICE: return "current CUDA device is not an sm_100-class GPU";
     case EJK_RPA_E_ALIGN: return "queries, kv_pages and out must be 16-byte aligned";
+    case EJK_RPA_E_SCRATCH:
+      return "this shape needs more scratch than the library's built-in static buffer holds "
+             "(EJK_RPA_STATIC_SCRATCH_BYTES); use ejk_rpa_launch with a caller-provided workspace";
     default: break;
   }
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -223,6 +226,42 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
     t_prof.recorded = true;
   }
   return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Launch without a caller-provided workspace.
+//
+// The scratch (work list, merge list, split-KV partials) lives in this file-scope device array,
+// so the call path contains no allocation of any kind.  The array is part of the loaded module:
+// every GPU that loads the library holds EJK_RPA_STATIC_SCRATCH_BYTES of it until the process
+// exits.  In host code the name `g_static_scratch` is only a handle for the runtime, not a device
+// address; the address a kernel may use comes from cudaGetSymbolAddress, looked up once per device
+// (with that device current) on the first call there.
+static __device__ __align__(256) unsigned char g_static_scratch[EJK_RPA_STATIC_SCRATCH_BYTES];
+
+namespace {
+void* g_static_scratch_ptr[64] = {};
+}
+
+int ejk_rpa_launch_static_scratch(const void* queries, const void* kv_pages, const int32_t* context_lens,
+                                  const int32_t* block_tables, const int32_t* query_start_loc,
+                                  const int32_t* num_seqs, const float* softmax_aux, void* out, int32_t* status,
+                                  const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
+  if (int e = check_shape(shape)) return e;
+  if (g_opt.profile) return EJK_RPA_E_ARG;  // the profiling hook creates CUDA events; not on this path
+  const DeviceInfo* d = device_info();
+  if (!d) return EJK_RPA_E_DEVICE;
+  if (layout_for(*shape, d->sm_count).total > (size_t)EJK_RPA_STATIC_SCRATCH_BYTES) return EJK_RPA_E_SCRATCH;
+  int dev = 0;
+  if (cudaError_t ce = cudaGetDevice(&dev); ce != cudaSuccess) return static_cast<int>(ce);
+  if (dev < 0 || dev >= 64) return EJK_RPA_E_DEVICE;
+  if (!g_static_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    if (cudaError_t ce = cudaGetSymbolAddress(&ptr, g_static_scratch); ce != cudaSuccess) return static_cast<int>(ce);
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  return ejk_rpa_launch(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, softmax_aux, out,
+                        g_static_scratch_ptr[dev], (size_t)EJK_RPA_STATIC_SCRATCH_BYTES, status, shape, attrs, stream);
 }
 
 int ejk_rpa_set_option(const char* name, int value) {

@@ -198,6 +198,55 @@ def ragged_page_attention_into(
     _cabi.check(rc, "ejk_rpa_launch")
 
 
+def ragged_page_attention_static_scratch_into(
+    out: torch.Tensor,
+    status: torch.Tensor,
+    queries: torch.Tensor,
+    kv_pages: torch.Tensor,
+    context_lens: torch.Tensor,
+    block_tables: torch.Tensor,
+    query_start_loc: torch.Tensor,
+    num_seqs: torch.Tensor,
+    *,
+    softmax_scale: float,
+    logits_soft_cap: float | None = None,
+    sliding_window: int | None = None,
+    softmax_aux: torch.Tensor | None = None,
+    stream: torch.cuda.Stream | None = None,
+) -> None:
+    """Enqueue one call through ``ejk_rpa_launch_static_scratch``: like
+    ``ragged_page_attention_into`` but with no workspace argument.
+
+    For callers that cannot allocate device memory where they call from (a custom-call handler
+    that only receives operand/result buffers, a host that forbids ``cudaMalloc`` outside its own
+    pool, a path that must not risk an allocation-induced sync).  The scratch is a fixed 32 MiB
+    array inside the library's device image; shapes that need more raise ``RpaLibraryError``
+    (code ``E_SCRATCH``) -- use the workspace form for those.  All calls on a GPU share that
+    array, so calls must not overlap on the device (keep them on one stream).  ``out`` (same
+    shape/dtype as ``queries``) and ``status`` (int32 ``[1]``) are caller-owned, as are all inputs.
+    """
+    lib = _cabi.load()
+    shape = _shape_of(queries, kv_pages, block_tables)
+    attrs = _cabi.Attrs(
+        float(softmax_scale),
+        0.0 if logits_soft_cap is None else float(logits_soft_cap),
+        0 if sliding_window is None else int(sliding_window),
+        0 if softmax_aux is None else int(softmax_aux.shape[-1]),
+        0 if softmax_aux is None else int(softmax_aux.shape[0]),
+        0,
+        0,
+    )
+    st = stream if stream is not None else torch.cuda.current_stream(queries.device)
+    with torch.cuda.device(queries.device):
+        rc = lib.ejk_rpa_launch_static_scratch(
+            queries.data_ptr(), kv_pages.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(),
+            query_start_loc.data_ptr(), num_seqs.data_ptr(),
+            None if softmax_aux is None else softmax_aux.data_ptr(),
+            out.data_ptr(), status.data_ptr(), ctypes.byref(shape), ctypes.byref(attrs), st.cuda_stream,
+        )
+    _cabi.check(rc, "ejk_rpa_launch_static_scratch")
+
+
 @kernel_registry.register("ragged_page_attention", Platform.CUDA, Backend.GPU)
 @jaxtyping.jaxtyped(typechecker=beartype)
 def ragged_page_attention(

@@ -55,6 +55,7 @@ extern "C" {
 #define EJK_RPA_E_ARG (-6)       /* sliding_window / logits_soft_cap / sinks out of contract */
 #define EJK_RPA_E_DEVICE (-7)    /* current device is not sm_100 class */
 #define EJK_RPA_E_ALIGN (-8)     /* a tensor base pointer is not 16-byte aligned */
+#define EJK_RPA_E_SCRATCH (-9)   /* shape needs more than EJK_RPA_STATIC_SCRATCH_BYTES of scratch */
 
 /* bits of the device-side status word (OR-ed in by the kernels; 0 = clean).  Inputs that
  * break the operator's contract never fault: the offending value is clamped or the sequence
@@ -116,6 +117,38 @@ EJK_RPA_API int ejk_rpa_launch(const void* queries, const void* kv_pages, const 
                    const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                    const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
                    int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream);
+
+/* Size of the scratch buffer built into the library for ejk_rpa_launch_static_scratch. */
+#define EJK_RPA_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* Same operation as ejk_rpa_launch for callers that have no way to obtain device memory at the
+ * point of the call: a custom-call handler whose runtime gave it only operand and result buffers,
+ * a plugin running under another framework's memory pool that forbids foreign cudaMalloc, or code
+ * on a latency-critical path where an allocation (which may synchronise the device) is not
+ * acceptable.  It has no counterpart in the reference, whose XLA path lets the compiler allocate
+ * temporaries.
+ *
+ * The scratch comes from a fixed EJK_RPA_STATIC_SCRATCH_BYTES (32 MiB) array compiled into the
+ * library's device image; each GPU that loads the library keeps that much memory reserved until
+ * the process exits.  The caller still passes every input, `out` and `status` exactly as for
+ * ejk_rpa_launch.  The call itself performs no cudaMalloc / cudaFree and calls no allocating
+ * library routine.
+ *   - A shape whose ejk_rpa_workspace_bytes() exceeds the array is refused with
+ *     EJK_RPA_E_SCRATCH (roughly: decode batches up to a few hundred sequences fit, batches with
+ *     thousands of prefill rows do not); nothing is launched in that case.
+ *   - The first call on each device looks up the array's device address (a one-time set-up with
+ *     that device current); make that first call outside any stream capture.
+ *   - All calls on one GPU share the one array, and it keeps whatever the previous call left in
+ *     it.  Nothing in it needs clearing between calls -- the planner kernel rewrites every word
+ *     that is later read -- but two calls whose kernels overlap on the GPU (different streams, or
+ *     different host threads) would overwrite each other's work lists and partial results: issue
+ *     them on one stream, or otherwise order them.
+ *   - Refused with EJK_RPA_E_ARG while option "profile" is 1. */
+EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* kv_pages, const int32_t* context_lens,
+                                              const int32_t* block_tables, const int32_t* query_start_loc,
+                                              const int32_t* num_seqs, const float* softmax_aux, void* out,
+                                              int32_t* status, const ejk_rpa_shape* shape,
+                                              const ejk_rpa_attrs* attrs, void* stream);
 
 /* Process-wide tuning knobs (host side, not thread safe against concurrent launches):
  *   "waves"      work items per resident CTA the device planner aims for (default 8)
