@@ -12,6 +12,7 @@ struct Options {
   int min_chunk = 256;
   int path = 0;
   int profile = 0;
+  int prefill_rows = 64;  // sequences with at least this many (token, head-in-group) rows use 128-row tensor tiles
 };
 Options g_opt;
 thread_local int t_last_launches = 0;
@@ -71,6 +72,7 @@ WorkspaceLayout layout_for(const ejk_rpa_shape& s, int n_sm) {
   L.max_units = (int)(tgt + max_tiles);
   L.max_merge = (int)max_tiles;
   L.max_slots = (int)(tgt + max_tiles);
+  L.max_punits = (int)(rows / kPrefillRows + s.max_num_seqs);
   size_t off = 0;
   L.header_off = off;
   off = align_up(off + kHdrWords * sizeof(int32_t), 256);
@@ -78,6 +80,8 @@ WorkspaceLayout layout_for(const ejk_rpa_shape& s, int n_sm) {
   off = align_up(off + (size_t)L.max_units * sizeof(Unit), 256);
   L.merge_off = off;
   off = align_up(off + (size_t)L.max_merge * sizeof(MergeItem), 256);
+  L.punits_off = off;
+  off = align_up(off + (size_t)L.max_punits * sizeof(Unit), 256);
   L.part_ml_off = off;
   off = align_up(off + (size_t)L.max_slots * s.num_kv_heads * L.rows_per_tile * sizeof(float2), 256);
   L.part_o_off = off;
@@ -160,6 +164,7 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
   p.out = out;
   p.header = reinterpret_cast<int32_t*>(ws + L.header_off);
   p.units = reinterpret_cast<Unit*>(ws + L.units_off);
+  p.punits = reinterpret_cast<Unit*>(ws + L.punits_off);
   p.merge = reinterpret_cast<MergeItem*>(ws + L.merge_off);
   p.part_o = reinterpret_cast<float*>(ws + L.part_o_off);
   p.part_ml = reinterpret_cast<float2*>(ws + L.part_ml_off);
@@ -177,6 +182,7 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
   p.max_units = L.max_units;
   p.max_merge = L.max_merge;
   p.max_slots = L.max_slots;
+  p.max_punits = L.max_punits;
   p.target_units = L.target_units;
   p.min_chunk = g_opt.min_chunk;
   p.window = a.sliding_window > 0 ? a.sliding_window : 0;
@@ -200,6 +206,12 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
   while ((1 << p.tma_block_shift) < p.tma_block_tokens) ++p.tma_block_shift;
   const bool use_tma = (g_opt.path == 2) || (g_opt.path == 0 && tma_path_supported(p));
   if (use_tma && !tma_path_supported(p)) return EJK_RPA_E_ARG;
+  // Batches that can hold a sequence with many query rows also get the tcgen05 prefill-tile
+  // kernel; whether any sequence actually qualifies is decided by the planner on the device.
+  const bool use_prefill = use_tma && g_opt.prefill_rows > 0 && prefill_path_supported(p) &&
+                           (long long)s.total_tokens * p.G >= g_opt.prefill_rows &&
+                           s.total_tokens > s.max_num_seqs;  // more query rows than sequences: some are multi-token
+  p.prefill_min_rows = use_prefill ? g_opt.prefill_rows : 0;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool prof = g_opt.profile != 0;
@@ -214,6 +226,11 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
   if (prof) cudaEventRecord(t_prof.ev[1], st);
+  if (use_prefill) {
+    e = launch_prefill(p, s.dtype, d->sm_count, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    ++t_last_launches;
+  }
   e = use_tma ? launch_splitkv_tma(p, s.dtype, d->sm_count, st) : launch_splitkv(p, s.dtype, d->sm_count, st);
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
@@ -277,6 +294,9 @@ int ejk_rpa_set_option(const char* name, int value) {
     g_opt.path = value;
   } else if (!std::strcmp(name, "profile")) {
     g_opt.profile = value ? 1 : 0;
+  } else if (!std::strcmp(name, "prefill_rows")) {
+    if (value < 0) return EJK_RPA_E_ARG;
+    g_opt.prefill_rows = value;
   } else {
     return EJK_RPA_E_ARG;
   }
@@ -289,6 +309,7 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "min_chunk")) *value = g_opt.min_chunk;
   else if (!std::strcmp(name, "path")) *value = g_opt.path;
   else if (!std::strcmp(name, "profile")) *value = g_opt.profile;
+  else if (!std::strcmp(name, "prefill_rows")) *value = g_opt.prefill_rows;
   else return EJK_RPA_E_ARG;
   return 0;
 }

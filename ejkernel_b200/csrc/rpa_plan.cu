@@ -15,6 +15,7 @@ constexpr int kPlanThreads = 1024;
 struct SeqInfo {
   int q_start, q_len, kv_len, rows, tiles;
   bool ok;
+  bool prefill;  // many query rows: 128-row tiles for the tcgen05 kernel, no KV split
 };
 
 __device__ __forceinline__ SeqInfo load_seq(const Params& p, int s, unsigned& flags) {
@@ -39,15 +40,18 @@ __device__ __forceinline__ SeqInfo load_seq(const Params& p, int s, unsigned& fl
   si.q_len = ql;
   si.kv_len = kv;
   si.rows = ql * p.G;
-  si.tiles = (si.rows + p.rows_per_tile - 1) / p.rows_per_tile;
+  si.prefill = p.prefill_min_rows > 0 && si.rows >= p.prefill_min_rows;
+  const int rpt = si.prefill ? kPrefillRows : p.rows_per_tile;
+  si.tiles = (si.rows + rpt - 1) / rpt;
   if (ql == 0) si.ok = false;  // _xla_impl_fwd.py:189-193: sequences without queries are skipped
   return si;
 }
 
 // Key range [lo, hi) visible to at least one row of tile t; lo is rounded down to a stage boundary.
-__device__ __forceinline__ void tile_range(const Params& p, const SeqInfo& si, int t, int& lo, int& hi) {
-  const int r_first = t * p.rows_per_tile;
-  int r_last = r_first + p.rows_per_tile;
+__device__ __forceinline__ void tile_range(const Params& p, const SeqInfo& si, int t, int& lo, int& hi,
+                                           int rows_per_tile) {
+  const int r_first = t * rows_per_tile;
+  int r_last = r_first + rows_per_tile;
   if (r_last > si.rows) r_last = si.rows;
   r_last -= 1;
   const int qt_first = r_first / p.G;
@@ -72,12 +76,13 @@ __device__ __forceinline__ void chunking(int len, int chunk, int& n, int& csize)
   if (csize < kTileTokens) csize = kTileTokens;
 }
 
-// inclusive block scan of three counters; returns this thread's exclusive prefix and the block total
-__device__ void block_scan3(int (&v)[3], int (&excl)[3], int (&total)[3], int (*s_warp)[3]) {
+// inclusive block scan of kCnt counters; returns this thread's exclusive prefix and the block total
+constexpr int kCnt = 4;
+__device__ void block_scan(int (&v)[kCnt], int (&excl)[kCnt], int (&total)[kCnt], int (*s_warp)[kCnt]) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int inc[3];
+  int inc[kCnt];
 #pragma unroll
-  for (int k = 0; k < 3; ++k) {
+  for (int k = 0; k < kCnt; ++k) {
     int x = v[k];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -90,7 +95,7 @@ __device__ void block_scan3(int (&v)[3], int (&excl)[3], int (&total)[3], int (*
   __syncthreads();
   if (warp == 0) {
 #pragma unroll
-    for (int k = 0; k < 3; ++k) {
+    for (int k = 0; k < kCnt; ++k) {
       int x = s_warp[lane][k];
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -102,7 +107,7 @@ __device__ void block_scan3(int (&v)[3], int (&excl)[3], int (&total)[3], int (*
   }
   __syncthreads();
 #pragma unroll
-  for (int k = 0; k < 3; ++k) {
+  for (int k = 0; k < kCnt; ++k) {
     const int wprev = warp ? s_warp[warp - 1][k] : 0;
     excl[k] = inc[k] - v[k] + wprev;
     total[k] = s_warp[31][k];
@@ -111,7 +116,7 @@ __device__ void block_scan3(int (&v)[3], int (&excl)[3], int (&total)[3], int (*
 }
 
 __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) {
-  __shared__ int s_warp[32][3];
+  __shared__ int s_warp[32][kCnt];
   __shared__ unsigned long long s_keys;
   __shared__ int s_chunk;
   const int tid = threadIdx.x;
@@ -131,10 +136,10 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   for (int s = tid; s < S; s += kPlanThreads) {
     unsigned f = 0;
     SeqInfo si = load_seq(p, s, f);
-    if (!si.ok) continue;
+    if (!si.ok || si.prefill) continue;
     for (int t = 0; t < si.tiles; ++t) {
       int lo, hi;
-      tile_range(p, si, t, lo, hi);
+      tile_range(p, si, t, lo, hi, p.rows_per_tile);
       keys += (unsigned long long)(hi - lo);
     }
   }
@@ -154,23 +159,27 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
     p.header[kHdrChunk] = (int)c;
     p.header[kHdrTotalKeys] = (int)(total > 0x7fffffffull ? 0x7fffffffull : total);
     p.header[kHdrQueue] = 0;
+    p.header[kHdrPrefillQueue] = 0;
   }
   __syncthreads();
   const int chunk = s_chunk;
 
   // ---- pass 2: per-sequence counts -> offsets -> items
-  int base[3] = {0, 0, 0};  // units, merge items, partial slots
+  int base[kCnt] = {0, 0, 0, 0};  // units, merge items, partial slots, prefill tiles
   for (int s0 = 0; s0 < S; s0 += kPlanThreads) {
     const int s = s0 + tid;
-    int cnt[3] = {0, 0, 0};
+    int cnt[kCnt] = {0, 0, 0, 0};
     SeqInfo si;
     si.ok = false;
+    si.prefill = false;
     if (s < S) {
       si = load_seq(p, s, flags);
-      if (si.ok) {
+      if (si.ok && si.prefill) {
+        cnt[3] = si.tiles;
+      } else if (si.ok) {
         for (int t = 0; t < si.tiles; ++t) {
           int lo, hi, n, cs;
-          tile_range(p, si, t, lo, hi);
+          tile_range(p, si, t, lo, hi, p.rows_per_tile);
           chunking(hi - lo, chunk, n, cs);
           cnt[0] += n;
           if (n > 1) {
@@ -180,17 +189,32 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
         }
       }
     }
-    int excl[3], total[3];
-    block_scan3(cnt, excl, total, s_warp);
+    int excl[kCnt], total[kCnt];
+    block_scan(cnt, excl, total, s_warp);
     if (s < S && si.ok) {
-      int u = base[0] + excl[0], m = base[1] + excl[1], sl = base[2] + excl[2];
-      if (base[0] + excl[0] + cnt[0] > p.max_units || base[1] + excl[1] + cnt[1] > p.max_merge ||
-          base[2] + excl[2] + cnt[2] > p.max_slots) {
+      int u = base[0] + excl[0], m = base[1] + excl[1], sl = base[2] + excl[2], pu = base[3] + excl[3];
+      if (u + cnt[0] > p.max_units || m + cnt[1] > p.max_merge || sl + cnt[2] > p.max_slots ||
+          pu + cnt[3] > p.max_punits) {
         flags |= EJK_RPA_ST_INTERNAL;
+      } else if (si.prefill) {
+        for (int t = 0; t < si.tiles; ++t) {
+          int lo, hi;
+          tile_range(p, si, t, lo, hi, kPrefillRows);
+          Unit un;
+          un.seq = s;
+          un.row0 = t * kPrefillRows;
+          un.kv_begin = lo;
+          un.kv_end = hi;
+          un.slot = -1;
+          un.q_start = si.q_start;
+          un.q_len = si.q_len;
+          un.kv_len = si.kv_len;
+          p.punits[pu++] = un;
+        }
       } else {
         for (int t = 0; t < si.tiles; ++t) {
           int lo, hi, n, cs;
-          tile_range(p, si, t, lo, hi);
+          tile_range(p, si, t, lo, hi, p.rows_per_tile);
           chunking(hi - lo, chunk, n, cs);
           if (n > 1) {
             MergeItem mi;
@@ -218,16 +242,15 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
         }
       }
     }
-    // units of sequences that overflowed are dropped; keep offsets consistent anyway
-    base[0] += total[0];
-    base[1] += total[1];
-    base[2] += total[2];
+#pragma unroll
+    for (int k = 0; k < kCnt; ++k) base[k] += total[k];
   }
   if (tid == 0) {
-    const bool over = base[0] > p.max_units || base[1] > p.max_merge || base[2] > p.max_slots;
+    const bool over = base[0] > p.max_units || base[1] > p.max_merge || base[2] > p.max_slots || base[3] > p.max_punits;
     p.header[kHdrNumUnits] = over ? 0 : base[0];
     p.header[kHdrNumMerge] = over ? 0 : base[1];
     p.header[kHdrNumSlots] = over ? 0 : base[2];
+    p.header[kHdrNumPrefill] = over ? 0 : base[3];
     if (over) flags |= EJK_RPA_ST_INTERNAL;
   }
   if (flags && p.status) atomicOr(reinterpret_cast<unsigned*>(p.status), flags);

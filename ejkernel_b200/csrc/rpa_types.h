@@ -11,6 +11,7 @@ namespace ejk {
 // as row = q_token * G + g, so a decode token with G <= 8 fills one 8-row tile and one read of a
 // KV page serves the whole GQA group.
 constexpr int kTileTokens = 64;  // KV tokens per pipeline stage (4 warps x 16)
+constexpr int kPrefillRows = 128;  // rows of one prefill tile (the M of a tcgen05.mma)
 
 // Work item of the split-KV kernel: one (sequence, row tile, KV chunk); the kv head is the fastest
 // index of the flattened work id, so neighbouring CTAs read neighbouring heads of the same page.
@@ -43,12 +44,14 @@ enum HeaderWord {
   kHdrQueue = 3,      // work queue head of the gather kernel
   kHdrNumSlots = 4,
   kHdrTotalKeys = 5,
+  kHdrNumPrefill = 6,     // work items of the tcgen05 prefill-tile kernel
+  kHdrPrefillQueue = 7,   // its work queue head
   kHdrWords = 64,
 };
 
 struct WorkspaceLayout {
-  size_t header_off, units_off, merge_off, part_o_off, part_ml_off, total;
-  int32_t max_units, max_merge, max_slots, rows_per_tile, target_units;
+  size_t header_off, units_off, merge_off, part_o_off, part_ml_off, punits_off, total;
+  int32_t max_units, max_merge, max_slots, rows_per_tile, target_units, max_punits;
 };
 
 struct Params {
@@ -62,6 +65,7 @@ struct Params {
   void* out;
   int32_t* header;
   Unit* units;
+  Unit* punits;    // prefill tiles: row0 is a multiple of kPrefillRows, slot unused
   MergeItem* merge;
   float* part_o;   // [max_slots][Hkv][rows_per_tile][D]
   float2* part_ml; // [max_slots][Hkv][rows_per_tile]  (m in log2 domain, l)
@@ -69,6 +73,8 @@ struct Params {
   int32_t T, S_max, pages_per_seq, num_pages, page_size, Hq, Hkv, G, D;
   int32_t rows_per_tile;
   int32_t max_units, max_merge, max_slots, target_units, min_chunk;
+  int32_t max_punits;
+  int32_t prefill_min_rows;  // sequences with q_len*G >= this go to the prefill-tile kernel; 0 = never
   int32_t window;      // <= 0: none
   int32_t num_sinks, sink_rows;
   float scale;         // softmax_scale
@@ -86,6 +92,8 @@ cudaError_t launch_plan(const Params& p, cudaStream_t stream);
 cudaError_t launch_splitkv(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 bool tma_path_supported(const Params& p);
 cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream);
+bool prefill_path_supported(const Params& p);
+cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 
 }  // namespace ejk
