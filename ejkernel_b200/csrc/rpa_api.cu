@@ -12,6 +12,7 @@ struct Options {
   int min_chunk = 256;
   int path = 0;
   int profile = 0;
+  int wait_ms = 2000;      // bound of every in-kernel wait; expiry sets EJK_RPA_ST_TIMEOUT
   int prefill_rows = 64;  // sequences with at least this many (token, head-in-group) rows use 128-row tensor tiles
 };
 Options g_opt;
@@ -204,6 +205,7 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
   p.tma_block_tokens = s.page_size < kTileTokens ? s.page_size : kTileTokens;
   p.tma_block_shift = 0;
   while ((1 << p.tma_block_shift) < p.tma_block_tokens) ++p.tma_block_shift;
+  p.wait_timeout_ms = g_opt.wait_ms;
   const bool use_tma = (g_opt.path == 2) || (g_opt.path == 0 && tma_path_supported(p));
   if (use_tma && !tma_path_supported(p)) return EJK_RPA_E_ARG;
   // Batches that can hold a sequence with many query rows also get the tcgen05 prefill-tile
@@ -294,6 +296,9 @@ int ejk_rpa_set_option(const char* name, int value) {
     g_opt.path = value;
   } else if (!std::strcmp(name, "profile")) {
     g_opt.profile = value ? 1 : 0;
+  } else if (!std::strcmp(name, "wait_ms")) {
+    if (value < 1) return EJK_RPA_E_ARG;
+    g_opt.wait_ms = value;
   } else if (!std::strcmp(name, "prefill_rows")) {
     if (value < 0) return EJK_RPA_E_ARG;
     g_opt.prefill_rows = value;
@@ -309,6 +314,7 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "min_chunk")) *value = g_opt.min_chunk;
   else if (!std::strcmp(name, "path")) *value = g_opt.path;
   else if (!std::strcmp(name, "profile")) *value = g_opt.profile;
+  else if (!std::strcmp(name, "wait_ms")) *value = g_opt.wait_ms;
   else if (!std::strcmp(name, "prefill_rows")) *value = g_opt.prefill_rows;
   else return EJK_RPA_E_ARG;
   return 0;

@@ -69,6 +69,56 @@ struct Mma<__half> {
   __device__ static __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
 };
 
+// ---- mbarrier helpers shared by the TMA kernels ----
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+// Bounded wait, executed by all 32 lanes of a warp.  Gives up when `timeout_ns` of wall time have
+// passed or when another warp of the CTA has raised `abort_flag`; the verdict is made
+// warp-uniform so the lanes never part ways on it.  false = gave up (the flag is then set).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long timeout_ns) {
+  bool ok = mbar_try_wait(bar, parity);
+  if (!ok) {
+    const unsigned long long t0 = global_timer_ns();
+    while (true) {
+      if (mbar_try_wait(bar, parity)) {
+        ok = true;
+        break;
+      }
+      if (*abort_flag) break;
+      if (global_timer_ns() - t0 > timeout_ns) break;
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (!ok) *abort_flag = 1;
+  return ok;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));

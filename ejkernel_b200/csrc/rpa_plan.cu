@@ -11,6 +11,7 @@ namespace ejk {
 namespace {
 
 constexpr int kPlanThreads = 1024;
+constexpr int kLenBuckets = 1024;  // prefill tiles are queued longest first (bucketed by stage count)
 
 struct SeqInfo {
   int q_start, q_len, kv_len, rows, tiles;
@@ -119,6 +120,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   __shared__ int s_warp[32][kCnt];
   __shared__ unsigned long long s_keys;
   __shared__ int s_chunk;
+  __shared__ int s_bucket[kLenBuckets];  // histogram, then write cursor, of prefill tiles per length bucket
   const int tid = threadIdx.x;
   unsigned flags = 0;
 
@@ -129,6 +131,18 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   }
   if (S < 0) S = 0;
   if (tid == 0) s_keys = 0ull;
+  for (int i = tid; i < kLenBuckets; i += kPlanThreads) s_bucket[i] = 0;
+  // bucket = stages >> bshift, sized so the longest possible tile lands in the last bucket
+  int bshift = 0;
+  {
+    const long long max_stages = ((long long)p.pages_per_seq * p.page_size + kTileTokens - 1) / kTileTokens;
+    while ((max_stages >> bshift) >= kLenBuckets) ++bshift;
+  }
+  auto bucket_of = [&](int lo, int hi) {
+    const int st = (hi - lo + kTileTokens - 1) / kTileTokens;
+    const int b = st >> bshift;
+    return b < kLenBuckets ? b : kLenBuckets - 1;
+  };
   __syncthreads();
 
   // ---- pass 1: total number of (tile, key) pairs -> chunk size
@@ -136,7 +150,15 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   for (int s = tid; s < S; s += kPlanThreads) {
     unsigned f = 0;
     SeqInfo si = load_seq(p, s, f);
-    if (!si.ok || si.prefill) continue;
+    if (!si.ok) continue;
+    if (si.prefill) {
+      for (int t = 0; t < si.tiles; ++t) {
+        int lo, hi;
+        tile_range(p, si, t, lo, hi, kPrefillRows);
+        atomicAdd(&s_bucket[bucket_of(lo, hi)], 1);
+      }
+      continue;
+    }
     for (int t = 0; t < si.tiles; ++t) {
       int lo, hi;
       tile_range(p, si, t, lo, hi, p.rows_per_tile);
@@ -163,6 +185,19 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   }
   __syncthreads();
   const int chunk = s_chunk;
+
+  // histogram -> descending exclusive offsets: the longest tiles get the lowest queue positions, so
+  // the persistent CTAs of the tensor-tile kernel take them first (longest-processing-time order)
+  int n_prefill_total = 0;
+  {
+    static_assert(kLenBuckets == kPlanThreads, "one bucket per planner thread");
+    int v[kCnt] = {s_bucket[kLenBuckets - 1 - tid], 0, 0, 0};
+    int excl[kCnt], total[kCnt];
+    block_scan(v, excl, total, s_warp);
+    s_bucket[kLenBuckets - 1 - tid] = excl[0];
+    n_prefill_total = total[0];
+    __syncthreads();
+  }
 
   // ---- pass 2: per-sequence counts -> offsets -> items
   int base[kCnt] = {0, 0, 0, 0};  // units, merge items, partial slots, prefill tiles
@@ -197,7 +232,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
           pu + cnt[3] > p.max_punits) {
         flags |= EJK_RPA_ST_INTERNAL;
       } else if (si.prefill) {
-        for (int t = 0; t < si.tiles; ++t) {
+        for (int t = 0; t < si.tiles && n_prefill_total <= p.max_punits; ++t) {
           int lo, hi;
           tile_range(p, si, t, lo, hi, kPrefillRows);
           Unit un;
@@ -209,8 +244,9 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
           un.q_start = si.q_start;
           un.q_len = si.q_len;
           un.kv_len = si.kv_len;
-          p.punits[pu++] = un;
+          p.punits[atomicAdd(&s_bucket[bucket_of(lo, hi)], 1)] = un;
         }
+        (void)pu;
       } else {
         for (int t = 0; t < si.tiles; ++t) {
           int lo, hi, n, cs;

@@ -40,7 +40,6 @@ constexpr int kBM = kPrefillRows;  // 128
 constexpr int kBN = kTileTokens;   // 64
 constexpr int kThreadsP = 192;
 constexpr int kRingP = 4;
-constexpr uint32_t kSpinLimitP = 1u << 22;
 constexpr float kLog2eP = 1.4426950408889634f;
 constexpr float kLazyP = 8.0f;
 
@@ -75,43 +74,7 @@ struct CfgP {
   static constexpr uint32_t TMEM_COLS = (2 * kBN + D <= 256) ? 256 : 512;  // power of two >= 128 + D
 };
 
-// ---- PTX wrappers ----
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait executed by all 32 lanes of a warp; warp-uniform verdict.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  bool ok = false;
-  for (uint32_t i = 0; i < kSpinLimitP; ++i) {
-    if (mbar_try_wait(bar, parity)) {
-      ok = true;
-      break;
-    }
-    if ((i & 255u) == 255u && *abort_flag) break;
-  }
-  ok = __all_sync(0xffffffffu, ok);
-  if (!ok) *abort_flag = 1;
-  return ok;
-}
+// ---- PTX wrappers (mbarrier helpers live in rpa_device.cuh) ----
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
                                             int c3, int c4) {
   asm volatile(
@@ -211,6 +174,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   const int Hkv = p.Hkv, G = p.G;
   const int n_work = p.header[kHdrNumPrefill] * Hkv;
   const int pb = p.tma_block_tokens, pb_shift = p.tma_block_shift;
+  const unsigned long long wait_ns = (unsigned long long)p.wait_timeout_ms * 1000000ull;
   unsigned flags = 0;
 
   if (tid == 0) {
@@ -258,7 +222,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       const int s = gi % NS;
       const uint32_t empty_parity = ((gi / NS) & 1) ^ 1;
       if (wid >= n_work) {
-        if (!mbar_wait(bar_kv_empty(s), empty_parity, abort_flag)) break;
+        if (!mbar_wait(bar_kv_empty(s), empty_parity, abort_flag, wait_ns)) break;
         if (lane == 0) {
           metas[s] = make_int2(-1, 0);
           mbar_arrive(bar_kv_full(s));
@@ -281,7 +245,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       bool first = true;
       for (int pos = u.kv_begin; first || pos < u.kv_end; pos += kBN) {
         const int st = gi % NS;
-        if (!mbar_wait(bar_kv_empty(st), ((gi / NS) & 1) ^ 1, abort_flag)) {
+        if (!mbar_wait(bar_kv_empty(st), ((gi / NS) & 1) ^ 1, abort_flag, wait_ns)) {
           alive = false;
           break;
         }
@@ -339,87 +303,90 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     for (int i = 0; i < NS && gi > 0; ++i) {
       const int g2 = gi + i;
       if (g2 < NS) continue;  // never used
-      if (!mbar_wait(bar_kv_empty(g2 % NS), ((g2 / NS) & 1) ^ 1, abort_flag)) break;
+      if (!mbar_wait(bar_kv_empty(g2 % NS), ((g2 / NS) & 1) ^ 1, abort_flag, wait_ns)) break;
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
     constexpr uint32_t idesc_s = instr_desc<T>(kBN, false);
     constexpr uint32_t idesc_pv = instr_desc<T>(D, true);
     int gi = 0;       // stage whose S is issued next
-    int k_items = 0;  // items whose first S has been issued
-    // software pipeline: S(gi) is issued one stage ahead of PV(gi-1)
-    bool have_prev = false;
+    int k_items = 0;  // items started
+    bool have_prev = false, prev_first = false;
     int prev_st = 0, prev_gi = 0;
-    bool prev_first = false;
-    bool done = false;
-    while (true) {
-      bool cur_valid = false, cur_first = false;
-      int cur_st = 0;
-      if (!done) {
-        cur_st = gi % NS;
-        if (!mbar_wait(bar_kv_full(cur_st), (gi / NS) & 1, abort_flag)) break;
-        const int2 meta = metas[cur_st];
-        if (meta.x < 0) {
-          done = true;
-        } else {
-          cur_valid = true;
-          const ItemDescP& it = ring[meta.x];
-          cur_first = (meta.y == it.u.kv_begin);
-          const int b = gi & 1;
-          // S buffer b must have been drained by the softmax warps (use gi/2 - 1)
-          if (!mbar_wait(bar_s_free(b), ((gi >> 1) & 1) ^ 1, abort_flag)) break;
-          if (cur_first) {
-            if (!mbar_wait(bar_q_full, k_items & 1, abort_flag)) break;
-            ++k_items;
-          }
-          tc_fence_after();
-          if (lane == 0) {
-            const uint32_t q_base = sb + C::OFF_Q;
-            const uint32_t k_base = sb + C::OFF_KV + cur_st * C::STAGE_BYTES;
+    bool ok = true;
+
+    // S(gi) = Q . K^T of stage `st` into S buffer gi & 1
+    auto issue_s = [&](int st) -> bool {
+      const int b = gi & 1;
+      // the softmax warps must have drained the previous use of this S buffer
+      if (!mbar_wait(bar_s_free(b), ((gi >> 1) & 1) ^ 1, abort_flag, wait_ns)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t q_base = sb + C::OFF_Q;
+        const uint32_t k_base = sb + C::OFF_KV + st * C::STAGE_BYTES;
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-              const uint32_t coff = (uint32_t)(kk >> 2), koff = (uint32_t)(kk & 3) * 32;
-              const uint64_t ad = smem_desc(q_base + coff * (kBM * 128) + koff, 16, 1024);
-              const uint64_t bd = smem_desc(k_base + coff * (kBN * 128) + koff, 16, 1024);
-              tc_mma(tmem_base + C::TMEM_S + b * kBN, ad, bd, idesc_s, kk > 0);
-            }
-            tc_commit(bar_s_full(b));
-          }
-          __syncwarp();
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t coff = (uint32_t)(kk >> 2), koff = (uint32_t)(kk & 3) * 32;
+          const uint64_t ad = smem_desc(q_base + coff * (kBM * 128) + koff, 16, 1024);
+          const uint64_t bd = smem_desc(k_base + coff * (kBN * 128) + koff, 16, 1024);
+          tc_mma(tmem_base + C::TMEM_S + b * kBN, ad, bd, idesc_s, kk > 0);
         }
+        tc_commit(bar_s_full(b));
       }
-      if (have_prev) {
-        const int pbuf = prev_gi % NP;
-        if (!mbar_wait(bar_p_full(pbuf), (prev_gi / NP) & 1, abort_flag)) break;
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t p_base = sb + C::OFF_P + pbuf * C::P_BYTES;
-          const uint32_t v_base = sb + C::OFF_KV + prev_st * C::STAGE_BYTES + C::KV_HALF;
+      __syncwarp();
+      return true;
+    };
+    // O (+)= P . V of the previous stage
+    auto issue_pv = [&]() -> bool {
+      const int pbuf = prev_gi % NP;
+      if (!mbar_wait(bar_p_full(pbuf), (prev_gi / NP) & 1, abort_flag, wait_ns)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t p_base = sb + C::OFF_P + pbuf * C::P_BYTES;
+        const uint32_t v_base = sb + C::OFF_KV + prev_st * C::STAGE_BYTES + C::KV_HALF;
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) {
-            const uint64_t ad = smem_desc(p_base + kk * 32, 16, 1024);
-            // V: MN-major, 64-element chunks of D are kBN*128 bytes apart (LBO), 8-token groups 1024 (SBO)
-            const uint64_t bd = smem_desc(v_base + kk * (16 * 128), kBN * 128, 1024);
-            tc_mma(tmem_base + C::TMEM_O, ad, bd, idesc_pv, !(prev_first && kk == 0));
-          }
-          tc_commit(bar_p_free(pbuf));     // P buffer reusable, and O/PV of this stage complete
-          tc_commit(bar_kv_empty(prev_st));  // both MMAs that read this KV stage are complete
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          const uint64_t ad = smem_desc(p_base + kk * 32, 16, 1024);
+          // V: MN-major, 64-element chunks of D are kBN*128 bytes apart (LBO), 8-token groups 1024 (SBO)
+          const uint64_t bd = smem_desc(v_base + kk * (16 * 128), kBN * 128, 1024);
+          tc_mma(tmem_base + C::TMEM_O, ad, bd, idesc_pv, !(prev_first && kk == 0));
         }
-        __syncwarp();
-        have_prev = false;
+        tc_commit(bar_p_free(pbuf));       // P buffer reusable; O holds this stage
+        tc_commit(bar_kv_empty(prev_st));  // both MMAs that read this KV stage are complete
       }
-      if (!cur_valid) {
-        if (done) break;
-        continue;
+      __syncwarp();
+      have_prev = false;
+      return true;
+    };
+
+    while (ok) {
+      const int st = gi % NS;
+      if (!mbar_wait(bar_kv_full(st), (gi / NS) & 1, abort_flag, wait_ns)) break;
+      const int2 meta = metas[st];
+      if (meta.x < 0) {
+        if (have_prev) issue_pv();
+        break;
       }
-      if (cur_first && k_items > 1) {
-        // the first PV of this item overwrites O: the previous item's epilogue must have read it
-        if (!mbar_wait(bar_o_free, k_items & 1, abort_flag)) break;
+      const bool first = (meta.y == ring[meta.x].u.kv_begin);
+      if (!first) {
+        // steady state: S of this stage goes to the tensor pipe before P.V of the previous one, so
+        // the pipe has work while the softmax warps exponentiate
+        ok = issue_s(st);
+        if (ok && have_prev) ok = issue_pv();
+      } else {
+        // item boundary: finish the previous item first -- its epilogue must read O before this
+        // item's query tile is loaded and before the first P.V of this item overwrites O
+        if (have_prev) ok = issue_pv();
+        if (ok) ok = mbar_wait(bar_q_full, k_items & 1, abort_flag, wait_ns);
+        if (ok && k_items > 0) ok = mbar_wait(bar_o_free, (k_items - 1) & 1, abort_flag, wait_ns);
+        ++k_items;
+        if (ok) ok = issue_s(st);
       }
+      if (!ok) break;
       have_prev = true;
-      prev_st = cur_st;
+      prev_st = st;
       prev_gi = gi;
-      prev_first = cur_first;
+      prev_first = first;
       ++gi;
     }
   } else {
@@ -437,7 +404,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     int h = 0;
     while (true) {
       const int st = gi % NS;
-      if (!mbar_wait(bar_kv_full(st), (gi / NS) & 1, abort_flag)) break;
+      if (!mbar_wait(bar_kv_full(st), (gi / NS) & 1, abort_flag, wait_ns)) break;
       const int2 meta = metas[st];
       if (meta.x < 0) break;
       const int pos = meta.y;
@@ -470,7 +437,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         mbar_arrive(bar_q_full);
       }
       const int b = gi & 1;
-      if (!mbar_wait(bar_s_full(b), (gi >> 1) & 1, abort_flag)) break;
+      if (!mbar_wait(bar_s_full(b), (gi >> 1) & 1, abort_flag, wait_ns)) break;
       tc_fence_after();
       uint32_t sr[2][32];
       tc_ld32(tmem_base + lane_addr + C::TMEM_S + b * kBN, sr[0]);
@@ -479,28 +446,63 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       tc_fence_before();
       mbar_arrive(bar_s_free(b));
 
-      // logits in the log2 domain, soft cap, masks (_xla_impl_fwd.py:125-138)
+      // logits in the log2 domain, soft cap, masks (_xla_impl_fwd.py:125-138).  The common case (no
+      // cap, stage entirely visible to this row) keeps the raw dot products and folds the scale into
+      // the exponent's FMA; everything else materialises the transformed logits first.
       const bool full_vis = (pos + kBN - 1 <= pos_row) && (pos > lo_row);
-      float mx = -INFINITY;
+      const bool plain = full_vis && p.cap == 0.f;
+      float e_scale = p.scale_log2;  // p = exp2(v * e_scale - m)
+      float mx;
+      if (plain) {
+        // max of scale*v is scale*max(v) or scale*min(v) depending on the sign of the scale
+        // (four independent chains: one warp per scheduler has nothing else to hide latency with)
+        float ext[4];
 #pragma unroll
-      for (int hlf = 0; hlf < 2; ++hlf)
+        for (int a = 0; a < 4; ++a) ext[a] = __uint_as_float(sr[0][a]);
+        if (p.scale_log2 >= 0.f) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float x = __uint_as_float(sr[hlf][c]);
-          if (p.cap != 0.f) x = p.cap_log2 * soft_cap_tanh(x * p.inv_cap_scale);
-          else x *= p.scale_log2;
-          if (!full_vis) {
-            const int key = pos + hlf * 32 + c;
-            if (key > pos_row || key <= lo_row) x = -INFINITY;
-          }
-          sr[hlf][c] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
+          for (int hlf = 0; hlf < 2; ++hlf)
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ext[c & 3] = fmaxf(ext[c & 3], __uint_as_float(sr[hlf][c]));
+          mx = fmaxf(fmaxf(ext[0], ext[1]), fmaxf(ext[2], ext[3])) * p.scale_log2;
+        } else {
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf)
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ext[c & 3] = fminf(ext[c & 3], __uint_as_float(sr[hlf][c]));
+          mx = fminf(fminf(ext[0], ext[1]), fminf(ext[2], ext[3])) * p.scale_log2;
         }
+      } else {
+        mx = -INFINITY;
+        e_scale = 1.f;
+        if (p.cap != 0.f) {
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf)
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              sr[hlf][c] = __float_as_uint(p.cap_log2 * soft_cap_tanh(__uint_as_float(sr[hlf][c]) * p.inv_cap_scale));
+        } else {
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf)
+#pragma unroll
+            for (int c = 0; c < 32; ++c) sr[hlf][c] = __float_as_uint(__uint_as_float(sr[hlf][c]) * p.scale_log2);
+        }
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            float x = __uint_as_float(sr[hlf][c]);
+            const int key = pos + hlf * 32 + c;
+            if (!full_vis && (key > pos_row || key <= lo_row)) x = -INFINITY;
+            sr[hlf][c] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
+          }
+      }
       const bool first_stage = (pos == u.kv_begin);
       const bool grow = (mx > m_run + kLazyP) || (m_run == -INFINITY && mx > -INFINITY);
       const int pbuf = gi % NP;
       // P buffer pbuf was last read by PV(gi - NP)
-      if (!mbar_wait(bar_p_free(pbuf), ((gi / NP) & 1) ^ 1, abort_flag)) break;
+      if (!mbar_wait(bar_p_free(pbuf), ((gi / NP) & 1) ^ 1, abort_flag, wait_ns)) break;
       if (__any_sync(0xffffffffu, grow)) {
         float alpha = 1.f;
         if (grow) {
@@ -513,7 +515,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           // PV(gi-1) must have completed first.
           if (NP == 2) {
             const int pprev = (gi - 1) % NP;
-            if (!mbar_wait(bar_p_free(pprev), ((gi - 1) / NP) & 1, abort_flag)) break;
+            if (!mbar_wait(bar_p_free(pprev), ((gi - 1) / NP) & 1, abort_flag, wait_ns)) break;
           }
           tc_fence_after();
 #pragma unroll 1
@@ -530,7 +532,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         }
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      float lsum = 0.f;
+      float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint8_t* prow = smem + C::OFF_P + pbuf * C::P_BYTES + row * 128;
 #pragma unroll
       for (int c8 = 0; c8 < 8; ++c8) {
@@ -538,14 +540,14 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int c = c8 * 8 + e * 2;
-          const float p0 = fast_exp2(__uint_as_float(sr[c >> 5][c & 31]) - m_use);
-          const float p1 = fast_exp2(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_use);
-          lsum += p0 + p1;
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), e_scale, -m_use));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), e_scale, -m_use));
+          lsum4[e] += p0 + p1;
           pk[e] = Mma<T>::pack(p0, p1);
         }
         *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
-      l_run += lsum;
+      l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
       if (pos + kBN > u.kv_end) {
         // Tail stage: V rows of keys >= kv_end were either never fetched (stale shared memory) or lie
         // past the sequence's length inside its last page (unowned, possibly NaN).  Their
@@ -567,7 +569,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
 
       if (pos + kBN >= u.kv_end) {
         // ---- last stage of the item: wait for its PV, normalise, store ----
-        if (!mbar_wait(bar_p_free(pbuf), (gi / NP) & 1, abort_flag)) break;
+        if (!mbar_wait(bar_p_free(pbuf), (gi / NP) & 1, abort_flag, wait_ns)) break;
         tc_fence_after();
         float scl = 1.f, l_fin = l_run;
         if (p.num_sinks > 0 && row_ok) {

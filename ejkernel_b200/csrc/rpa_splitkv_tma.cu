@@ -14,7 +14,7 @@
 // Replaces ejkernel/kernels/_xla/ragged_page_attention/_xla_impl_fwd.py:99-159 of the reference
 // (page gather + two einsums + online softmax).  No cluster multicast is used anywhere.
 //
-// Every wait on an mbarrier is bounded: after kSpinLimit polls the warp raises
+// Every wait on an mbarrier is bounded in wall time (option "wait_ms"): on expiry the warp raises
 // EJK_RPA_ST_TIMEOUT, sets the CTA's abort flag and returns, and every other wait of the CTA
 // gives up as soon as it sees the flag, so a protocol error can never hang the device.
 #include <cuda.h>
@@ -30,7 +30,6 @@ namespace {
 constexpr int kConsumerWarps = 4;
 constexpr int kThreadsTma = (kConsumerWarps + 1) * 32;
 constexpr int kRingTma = 8;
-constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLazyRescale = 8.0f;  // rescale the accumulators only when the max grows by 2^8
 
@@ -62,44 +61,7 @@ struct CfgT {
   static constexpr int SMEM_BYTES = OFF_ABORT + 16 + 1024;  // + alignment slack
 };
 
-// ---- mbarrier / TMA wrappers ----
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait, called by all 32 lanes of a warp; false = gave up (timeout or another warp
-// aborted).  The verdict is made warp-uniform so the lanes never part ways on it.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  bool ok = false;
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) {
-      ok = true;
-      break;
-    }
-    if ((i & 255u) == 255u && *abort_flag) break;
-  }
-  ok = __all_sync(0xffffffffu, ok);
-  if (!ok) *abort_flag = 1;
-  return ok;
-}
+// ---- TMA wrapper (mbarrier helpers live in rpa_device.cuh) ----
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
                                             int c3, int c4) {
   asm volatile(
@@ -136,6 +98,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
   const int n_work = p.header[kHdrNumUnits] * Hkv;
   const int pb = p.tma_block_tokens;       // tokens per TMA box (power of two, >= 8)
   const int pb_shift = p.tma_block_shift;
+  const unsigned long long wait_ns = (unsigned long long)p.wait_timeout_ms * 1000000ull;
   unsigned flags = 0;
 
   if (tid == 0) {
@@ -164,7 +127,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     while (alive) {
       if (wid >= n_work) {
         // end-of-stream marker for the consumers
-        if (!mbar_wait(bar_empty + s * 8, empty_parity, abort_flag)) break;
+        if (!mbar_wait(bar_empty + s * 8, empty_parity, abort_flag, wait_ns)) break;
         if (lane == 0) {
           metas[s] = make_int2(-1, 0);
           mbar_arrive(bar_full + s * 8);
@@ -186,7 +149,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
       const int32_t* tab = p.block_tables + (size_t)u.seq * p.pages_per_seq;
       bool first = true;
       for (int pos = u.kv_begin; first || pos < u.kv_end; pos += TK) {
-        if (!mbar_wait(bar_empty + s * 8, empty_parity, abort_flag)) {
+        if (!mbar_wait(bar_empty + s * 8, empty_parity, abort_flag, wait_ns)) {
           alive = false;
           break;
         }
@@ -253,7 +216,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     // Leave only after every bulk copy this warp issued has landed: wait (bounded) for the
     // consumers to drain all stages, which implies all "full" phases completed.
     for (int i = 0; i < NS; ++i) {
-      if (!mbar_wait(bar_empty + s * 8, empty_parity, abort_flag)) break;
+      if (!mbar_wait(bar_empty + s * 8, empty_parity, abort_flag, wait_ns)) break;
       if (++s == NS) {
         s = 0;
         empty_parity ^= 1u;
@@ -287,13 +250,13 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
     auto consumer_sync = [&]() -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_c);
-      const bool ok = mbar_wait(bar_c, c_parity, abort_flag);
+      const bool ok = mbar_wait(bar_c, c_parity, abort_flag, wait_ns);
       c_parity ^= 1u;
       return ok;
     };
 
     while (true) {
-      if (!mbar_wait(bar_full + s * 8, full_parity, abort_flag)) break;
+      if (!mbar_wait(bar_full + s * 8, full_parity, abort_flag, wait_ns)) break;
       const int2 meta = metas[s];
       if (meta.x < 0) break;
       const ItemDesc& it = ring[meta.x];

@@ -85,6 +85,7 @@ struct Params {
   int32_t page_shift;  // log2(page_size) if a power of two, else -1
   int32_t tma_block_tokens;  // tokens per TMA box = min(page_size, kTileTokens)
   int32_t tma_block_shift;   // log2 of the above
+  int32_t wait_timeout_ms;   // wall-time bound of every in-kernel mbarrier wait
 };
 
 // launchers (each returns cudaError_t of the launch)

@@ -266,12 +266,14 @@ def blocked_as_written(
     return out[:T].reshape(T, Hq, D)
 
 
-def compare(got, want, *, atol=2e-2, rtol=2e-2, rows: int | None = None) -> dict:
+def compare(got, want, *, atol=2e-2, rtol=2e-2, rows: int | None = None, rms_tol=3e-2, rel_tol=1e-2) -> dict:
     """Error summary of ``got`` against ``want`` on rows ``[0, rows)``.
 
-    Besides the elementwise ``|got-want| <= atol + rtol*|want|`` criterion, reports the
-    maximum error relative to the RMS of the expected output, because on N(0,1) inputs with
-    long contexts the outputs themselves are smaller than ``atol``.
+    ``allclose`` is the stated criterion ``|got-want| <= atol + rtol*|want|``.  On N(0,1) inputs with
+    long contexts the outputs themselves are smaller than ``atol`` (an all-zero result would pass),
+    so ``tight`` additionally demands ``|got-want| <= rms_tol*rms(want) + rel_tol*|want|``: an
+    absolute floor that scales with the size of the expected output plus 1 % relative error, which is
+    what bf16 rounding of the probabilities and of the output allows.
     """
     g = _np(got, np.float64)
     w = _np(want, np.float64)
@@ -281,6 +283,7 @@ def compare(got, want, *, atol=2e-2, rtol=2e-2, rows: int | None = None) -> dict
     rms = float(np.sqrt(np.mean(w * w))) if w.size else 0.0
     return dict(
         max_abs=float(err.max()) if err.size else 0.0,
+        tight=bool(np.all(err <= rms_tol * rms + rel_tol * np.abs(w))),
         rms_want=rms,
         max_rel_rms=float(err.max() / max(rms, 1e-30)) if err.size else 0.0,
         allclose=bool(np.all(err <= atol + rtol * np.abs(w))),

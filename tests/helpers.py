@@ -9,7 +9,7 @@ from ejkernel_b200.utils import RaggedBatch
 from oracle.rpa_oracle import compare, dense_reference
 
 ATOL = RTOL = 2e-2  # bf16 tolerance of the operator's parity criterion
-REL_RMS = 5e-2  # stricter: max error relative to the RMS of the expected output (bf16 P and output rounding give ~2-3e-2)
+REL_RMS = 1.0  # loose sanity bound on max error / RMS of the expected output; the sharp check is compare()["tight"]
 
 
 def run_cuda(batch: RaggedBatch, **override) -> torch.Tensor:
@@ -38,5 +38,6 @@ def assert_parity(got: torch.Tensor, want: np.ndarray, rows: int, *, rel_rms=REL
     r = compare(got, want, atol=ATOL, rtol=RTOL, rows=rows)
     assert r["finite"], f"{what}: non-finite output {r}"
     assert r["allclose"], f"{what}: outside atol=rtol={ATOL}: {r}"
+    assert r["tight"], f"{what}: outside 3e-2*rms(expected) + 1e-2*|expected|: {r}"
     assert r["max_rel_rms"] <= rel_rms, f"{what}: max|err| / rms(expected) = {r['max_rel_rms']:.4g} > {rel_rms}: {r}"
     return r

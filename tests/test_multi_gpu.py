@@ -68,6 +68,6 @@ def test_two_gpu_head_sharding_matches_oracle(rpa_lib):
     want = dense_reference(*b.args(), **b.kwargs())
     sharded = np.concatenate([o[False] for o in outs], axis=1)
     r = compare(sharded, want, atol=ATOL, rtol=RTOL)
-    assert r["finite"] and r["allclose"] and r["max_rel_rms"] <= REL_RMS, r
+    assert r["finite"] and r["allclose"] and r["tight"] and r["max_rel_rms"] <= REL_RMS, r
     for o in outs:
         np.testing.assert_array_equal(o[True], sharded)  # the all-gather moves bits, it does not change them

@@ -1,7 +1,7 @@
 """Parity of the sm_100a kernels (called through the C ABI via the registered operator) with the
 CPU oracle on the same seeded inputs.  Tolerance: atol = rtol = 2e-2 for bf16 with fp32
-accumulation, plus max|err| <= 5e-2 * rms(expected) because on N(0,1) inputs with long contexts
-the outputs themselves are smaller than atol.  Index work (page gather, masking) is checked
+accumulation, plus |err| <= 3e-2 * rms(expected) + 1e-2 * |expected| because on N(0,1) inputs with
+long contexts the outputs themselves are smaller than atol.  Index work (page gather, masking) is checked
 bit-exactly through integer-valued cases."""
 
 import numpy as np
@@ -102,6 +102,37 @@ def test_window_invariants_of_reference_tests(rpa_lib):
     assert (o0.float() - o2.float()).abs().max().item() < 0.1
     o3 = run_cuda(base, sliding_window=7)
     assert (o0.float() - o3.float()).abs().max().item() > 1e-6
+
+
+def test_prefill_tiles_many_items_per_cta(rpa_lib):
+    """More 128-row tiles than SMs, so every persistent CTA of the tcgen05 kernel walks several items
+    (query-tile reload, O hand-over between items, ring reuse), with ragged last tiles."""
+    b = make_ragged_batch([700, 1, 333, 2, 129], [1500, 40, 333, 900, 4000], num_q_heads=8, num_kv_heads=2,
+                          head_dim=128, page_size=16, seed=51)
+    _check(b, "many prefill tiles")
+    b = make_ragged_batch([300, 260], [2100, 300], num_q_heads=16, num_kv_heads=2, head_dim=64, page_size=32,
+                          seed=52, sliding_window=700, logits_soft_cap=40.0)
+    _check(b, "prefill window+cap d64")
+    b = make_ragged_batch([200], [1000], num_q_heads=4, num_kv_heads=2, head_dim=256, page_size=8, seed=53)
+    b.softmax_aux = torch.tensor([[0.5, -1.0], [2.0, 0.0]])
+    _check(b, "prefill d256 sinks")
+
+
+def test_prefill_threshold_does_not_change_results_beyond_tolerance(rpa_lib):
+    """The same batch through 8-row split-KV tiles only (prefill_rows=0), through 128-row tensor tiles
+    for every multi-row sequence (prefill_rows=1) and with the default threshold."""
+    from ejkernel_b200 import _cabi
+    b = make_ragged_batch([1, 40, 3, 160, 1], [800, 640, 77, 1700, 9], num_q_heads=8, num_kv_heads=2, head_dim=128,
+                          page_size=16, seed=54)
+    want = oracle(b)
+    old = _cabi.get_option("prefill_rows")
+    try:
+        for rows in (0, 1, 64, 4096):
+            _cabi.set_option("prefill_rows", rows)
+            out = run_cuda(b)
+            assert_parity(out, want, b.total_tokens, what=f"prefill_rows={rows}")
+    finally:
+        _cabi.set_option("prefill_rows", old)
 
 
 def test_sinks(rpa_lib):

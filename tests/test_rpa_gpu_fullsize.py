@@ -63,7 +63,7 @@ def test_sampled_sequences_match_oracle(full):
     cu = b.query_start_loc.cpu().tolist()
     got = torch.cat([out[cu[s] : cu[s + 1]] for s in seqs])
     r = compare(got, want, atol=ATOL, rtol=RTOL)
-    assert r["finite"] and r["allclose"] and r["max_rel_rms"] <= REL_RMS, (name, r)
+    assert r["finite"] and r["allclose"] and r["tight"] and r["max_rel_rms"] <= REL_RMS, (name, r)
 
 
 def test_page_renumbering_is_bit_invariant(full):
@@ -94,7 +94,7 @@ def test_rerun_is_bitwise_equal_and_split_granularity_is_within_tolerance(full):
         _cabi.set_option("waves", old)
     T = b.total_tokens
     r = compare(out3[:T], out[:T].float().cpu().numpy(), atol=ATOL, rtol=RTOL)
-    assert r["allclose"] and r["max_rel_rms"] <= REL_RMS, (name, r)
+    assert r["allclose"] and r["tight"] and r["max_rel_rms"] <= REL_RMS, (name, r)
 
 
 def test_constant_value_rows_come_back_exactly(rpa_lib):

@@ -70,7 +70,7 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row(rpa_lib):
         assert int(status.item()) == 0
         T = b.total_tokens
         r = compare(out[:T], want[:T].float().cpu().numpy(), atol=ATOL, rtol=RTOL)
-        assert r["finite"] and r["allclose"] and r["max_rel_rms"] <= REL_RMS, r
+        assert r["finite"] and r["allclose"] and r["tight"] and r["max_rel_rms"] <= REL_RMS, r
         assert torch.count_nonzero(out[T:]) == 0
 
 
