@@ -39,7 +39,7 @@ namespace {
 constexpr int kBM = kPrefillRows;  // 128
 constexpr int kBN = kTileTokens;   // 64
 constexpr int kThreadsP = 192;
-constexpr int kRingP = 4;
+constexpr int kRingP = 16;
 constexpr float kLog2eP = 1.4426950408889634f;
 constexpr float kLazyP = 8.0f;
 
@@ -52,7 +52,7 @@ struct ItemDescP {
 
 template <int D>
 struct CfgP {
-  static constexpr int NS = (D <= 128) ? 3 : 2;   // KV stages
+  static constexpr int NS = (D == 64) ? 8 : (D == 128) ? 5 : 2;  // KV stages (as many as shared memory holds)
   static constexpr int NP = (D <= 128) ? 2 : 1;   // P buffers
   static constexpr int STAGE_BYTES = kBN * 2 * D * 2;
   static constexpr int KV_HALF = kBN * D * 2;     // bytes of the K (or V) part of a stage
@@ -184,14 +184,14 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_s_full(b), 1);
-      mbar_init(bar_s_free(b), 128);
+      mbar_init(bar_s_free(b), 4);  // one arrival per softmax warp
     }
     for (int b = 0; b < NP; ++b) {
-      mbar_init(bar_p_full(b), 128);
+      mbar_init(bar_p_full(b), 4);
       mbar_init(bar_p_free(b), 1);
     }
-    mbar_init(bar_q_full, 128);
-    mbar_init(bar_o_free, 128);
+    mbar_init(bar_q_full, 4);
+    mbar_init(bar_o_free, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     fence_async_smem();
@@ -434,7 +434,8 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           *reinterpret_cast<uint4*>(smem + C::OFF_Q + off) = v;
         }
         fence_async_smem();
-        mbar_arrive(bar_q_full);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_q_full);
       }
       const int b = gi & 1;
       if (!mbar_wait(bar_s_full(b), (gi >> 1) & 1, abort_flag, wait_ns)) break;
@@ -444,7 +445,8 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       tc_ld32(tmem_base + lane_addr + C::TMEM_S + b * kBN + 32, sr[1]);
       tc_wait_ld();
       tc_fence_before();
-      mbar_arrive(bar_s_free(b));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_s_free(b));
 
       // logits in the log2 domain, soft cap, masks (_xla_impl_fwd.py:125-138).  The common case (no
       // cap, stage entirely visible to this row) keeps the raw dot products and folds the scale into
@@ -565,7 +567,8 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       }
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(bar_p_full(pbuf));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p_full(pbuf));
 
       if (pos + kBN >= u.kv_end) {
         // ---- last stage of the item: wait for its PV, normalise, store ----
@@ -604,7 +607,8 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           }
         }
         tc_fence_before();
-        mbar_arrive(bar_o_free);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_o_free);
       }
       ++gi;
     }
