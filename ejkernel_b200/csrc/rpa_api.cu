@@ -214,6 +214,7 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
                            (long long)s.total_tokens * p.G >= g_opt.prefill_rows &&
                            s.total_tokens > s.max_num_seqs;  // more query rows than sequences: some are multi-token
   p.prefill_min_rows = use_prefill ? g_opt.prefill_rows : 0;
+  p.prefill_item_rows = prefill_rows_per_item(s.head_dim);
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool prof = g_opt.profile != 0;

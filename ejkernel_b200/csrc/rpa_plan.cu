@@ -42,7 +42,7 @@ __device__ __forceinline__ SeqInfo load_seq(const Params& p, int s, unsigned& fl
   si.kv_len = kv;
   si.rows = ql * p.G;
   si.prefill = p.prefill_min_rows > 0 && si.rows >= p.prefill_min_rows;
-  const int rpt = si.prefill ? kPrefillRows : p.rows_per_tile;
+  const int rpt = si.prefill ? p.prefill_item_rows : p.rows_per_tile;
   si.tiles = (si.rows + rpt - 1) / rpt;
   if (ql == 0) si.ok = false;  // _xla_impl_fwd.py:189-193: sequences without queries are skipped
   return si;
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
     if (si.prefill) {
       for (int t = 0; t < si.tiles; ++t) {
         int lo, hi;
-        tile_range(p, si, t, lo, hi, kPrefillRows);
+        tile_range(p, si, t, lo, hi, p.prefill_item_rows);
         atomicAdd(&s_bucket[bucket_of(lo, hi)], 1);
       }
       continue;
@@ -234,10 +234,10 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
       } else if (si.prefill) {
         for (int t = 0; t < si.tiles && n_prefill_total <= p.max_punits; ++t) {
           int lo, hi;
-          tile_range(p, si, t, lo, hi, kPrefillRows);
+          tile_range(p, si, t, lo, hi, p.prefill_item_rows);
           Unit un;
           un.seq = s;
-          un.row0 = t * kPrefillRows;
+          un.row0 = t * p.prefill_item_rows;
           un.kv_begin = lo;
           un.kv_end = hi;
           un.slot = -1;

@@ -5,21 +5,33 @@
 // contractions, exactly the two einsums of the reference's inner loop
 // (ejkernel/kernels/_xla/ragged_page_attention/_xla_impl_fwd.py:119-124,148), here as
 //     S[128 x 64]  = Q[128 x D] . K^T          tcgen05.mma kind::f16, A,B from shared memory, D in TMEM
-//     O[128 x D]  += P[128 x 64] . V           tcgen05.mma, B operand MN-major, accumulator in TMEM
+//     O[128 x D]  += P[128 x 64] . V           tcgen05.mma, A (P) from TMEM, B (V) MN-major from shared
+//                                              memory, accumulator in TMEM
 // with the online softmax (:125-151) in between done by one thread per row on values read from TMEM
 // with tcgen05.ld, so the row maximum and row sum need no shuffles at all.
 //
-// Warp roles (192 threads, one CTA per SM, persistent over a device work queue):
-//   warp 0      TMA producer: page-table driven gather of K_h / V_h, one box {64 elems, PB tokens}
-//               per (K|V, 64-element chunk of D, page block), SWIZZLE_128B, into a stage laid out
-//               [K|V][D/64][64 tokens][64] = the canonical K-major (for K) / MN-major (for V)
-//               128B-swizzled operand layout of tcgen05.mma.  No cluster multicast.
+// One CTA works on NT = 2 such tiles at once (256 consecutive rows of the same sequence and kv head;
+// NT = 1 at head_dim 256 where TMEM holds only one O accumulator): both tiles consume the same KV
+// stage, which halves the L2 -> shared-memory traffic per FLOP.  That traffic, not the tensor pipe,
+// is what bounds a 128-row tile: a stage of 32 KB feeds only 4.2 MFLOP.
+//
+// Warp roles (64 + 128*NT threads, one CTA per SM, persistent over a device work queue):
+//   warp 0      TMA producer: page-table driven gather of K_h / V_h, one box
+//               {64 elems, 8 tokens, D/64, (K_h,V_h)} per 8-token group, SWIZZLE_128B.  A box keeps
+//               the 2*D contiguous elements of a token together (512-byte runs in global memory;
+//               the TMA unit's cost is per contiguous run, so 128-byte runs are 4x slower), and lands as
+//               [group of 8 tokens][K|V][D/64][8 tokens][64]: 8-row x 128-byte swizzle atoms at a uniform
+//               stride, i.e. a canonical K-major (K) / MN-major (V) operand of tcgen05.mma with
+//               stride-byte-offset = one group.  No cluster multicast.
 //   warp 1      MMA issuer (one lane): S for stage i+1 is issued before P.V of stage i so the tensor
 //               pipe works while the softmax warps exponentiate; owns the TMEM allocation.
-//   warps 2-5   softmax: thread = TMEM lane = tile row.  Loads the tile's query rows into the
+//   warps 2-5   softmax of tile 0 (warps 6-9: tile 1): thread = TMEM lane = tile row.  Loads the tile's query rows into the
 //               K-major swizzled A layout, reads S, masks, exponentiates (log2 domain, lazy
 //               rescaling of O in TMEM only when a row maximum grows by more than 2^8), writes P
-//               (bf16) as the next A operand, and finally normalises O and stores the rows.
+//               (bf16 pairs) back into the TMEM columns S came from with tcgen05.st -- the A
+//               operand of the P.V MMA -- and finally normalises O and stores the rows.  The tensor
+//               pipe executes MMAs in issue order, so S of stage i+2 cannot overwrite those columns
+//               before P.V of stage i has read them.
 //
 // All hand-offs are mbarriers; tcgen05.commit signals MMA completion.  Every wait is bounded: on
 // expiry the warp sets the CTA abort flag, every other wait gives up when it sees the flag, the
@@ -38,7 +50,6 @@ namespace {
 
 constexpr int kBM = kPrefillRows;  // 128
 constexpr int kBN = kTileTokens;   // 64
-constexpr int kThreadsP = 192;
 constexpr int kRingP = 16;
 constexpr float kLog2eP = 1.4426950408889634f;
 constexpr float kLazyP = 8.0f;
@@ -52,26 +63,31 @@ struct ItemDescP {
 
 template <int D>
 struct CfgP {
-  static constexpr int NS = (D == 64) ? 8 : (D == 128) ? 5 : 2;  // KV stages (as many as shared memory holds)
-  static constexpr int NP = (D <= 128) ? 2 : 1;   // P buffers
+  static constexpr int NT = (D <= 128) ? 2 : 1;                    // 128-row tiles per CTA
+  static constexpr int THREADS = 64 + 128 * NT;
+  static constexpr int NS = (D == 64) ? 8 : (D == 128) ? 5 : 2;    // KV stages (as many as shared memory holds)
   static constexpr int STAGE_BYTES = kBN * 2 * D * 2;
-  static constexpr int KV_HALF = kBN * D * 2;     // bytes of the K (or V) part of a stage
-  static constexpr int Q_BYTES = kBM * D * 2;
-  static constexpr int P_BYTES = kBM * kBN * 2;
+  static constexpr int GROUP_BYTES = 8 * 2 * D * 2;   // one 8-token group: [K|V][D/64][8][64]
+  static constexpr int V_OFF = (D / 64) * 1024;       // V atoms follow the K atoms inside a group
+  static constexpr int Q_BYTES = kBM * D * 2;         // per tile
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_KV = OFF_Q + Q_BYTES;
-  static constexpr int OFF_P = OFF_KV + NS * STAGE_BYTES;
-  static constexpr int OFF_RING = OFF_P + NP * P_BYTES;
+  static constexpr int OFF_KV = OFF_Q + NT * Q_BYTES;
+  static constexpr int OFF_RING = OFF_KV + NS * STAGE_BYTES;
   static constexpr int OFF_META = OFF_RING + kRingP * (int)sizeof(ItemDescP);
   static constexpr int OFF_BAR = OFF_META + NS * 8;
-  // barriers: kv_full[NS] kv_empty[NS] s_full[2] s_free[2] p_full[NP] p_free[NP] q_full o_free
-  static constexpr int N_BAR = 2 * NS + 4 + 2 * NP + 2;
+  // barriers: kv_full[NS] kv_empty[NS], then per tile: s_full[2] p_full[2] pv_done[2] q_full o_free
+  static constexpr int BAR_PER_TILE = 8;
+  static constexpr int N_BAR = 2 * NS + NT * BAR_PER_TILE;
   static constexpr int OFF_TMEM = OFF_BAR + N_BAR * 8;
   static constexpr int OFF_ABORT = OFF_TMEM + 8;
   static constexpr int SMEM_BYTES = OFF_ABORT + 8 + 1024;
-  static constexpr uint32_t TMEM_S = 0;       // two S buffers of 64 columns
-  static constexpr uint32_t TMEM_O = 2 * kBN; // O accumulator, D columns
-  static constexpr uint32_t TMEM_COLS = (2 * kBN + D <= 256) ? 256 : 512;  // power of two >= 128 + D
+  // TMEM columns: per tile two S/P buffers of 64 columns, then per tile one O accumulator of D columns
+  static constexpr uint32_t TMEM_S = 0;
+  static constexpr uint32_t TMEM_O = NT * 2 * kBN;
+  static constexpr uint32_t TMEM_NEED = NT * (2 * kBN + D);
+  static constexpr uint32_t TMEM_COLS = TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
+  static_assert(TMEM_NEED <= 512, "TMEM holds 512 columns");
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
 // ---- PTX wrappers (mbarrier helpers live in rpa_device.cuh) ----
@@ -100,6 +116,18 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
       : "memory");
 }
+// D[tmem] (+)= A[tmem, 16-bit pairs per column] * B[smem desc]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t addr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -126,18 +154,9 @@ __device__ __forceinline__ void tc_st32(uint32_t addr, const uint32_t (&r)[32]) 
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 encoding: start>>4 at [0,14),
-// leading byte offset>>4 at [16,30), stride byte offset>>4 at [32,46), version 1 at [46,48),
-// layout type 2 (SWIZZLE_128B) at [61,64).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr >> 4) & 0x3fffu);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
+// Shared-memory matrix descriptors (128-byte swizzle, sm_100 encoding) are assembled in the MMA
+// warp: start>>4 at [0,14), leading byte offset>>4 at [16,30), stride byte offset>>4 at [32,46),
+// version 1 at [46,48), layout type 2 (SWIZZLE_128B) at [61,64).
 // Instruction descriptor of kind::f16: D fp32, A/B bf16 or f16, M = 128.
 template <typename T>
 __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
@@ -147,10 +166,10 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kThreadsP, 1)
+__global__ void __launch_bounds__(CfgP<D>::THREADS, 1)
 rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
   using C = CfgP<D>;
-  constexpr int NS = C::NS, NP = C::NP;
+  constexpr int NS = C::NS, NT = C::NT;
   constexpr int DC = D / 64;
 
   extern __shared__ uint8_t smem_raw[];
@@ -163,41 +182,40 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   const uint32_t bar0 = sb + C::OFF_BAR;
   auto bar_kv_full = [&](int s) { return bar0 + s * 8; };
   auto bar_kv_empty = [&](int s) { return bar0 + (NS + s) * 8; };
-  auto bar_s_full = [&](int b) { return bar0 + (2 * NS + b) * 8; };
-  auto bar_s_free = [&](int b) { return bar0 + (2 * NS + 2 + b) * 8; };
-  auto bar_p_full = [&](int b) { return bar0 + (2 * NS + 4 + b) * 8; };
-  auto bar_p_free = [&](int b) { return bar0 + (2 * NS + 4 + NP + b) * 8; };
-  const uint32_t bar_q_full = bar0 + (2 * NS + 4 + 2 * NP) * 8;
-  const uint32_t bar_o_free = bar_q_full + 8;
+  auto tile_bar = [&](int x, int i) { return bar0 + (2 * NS + x * C::BAR_PER_TILE + i) * 8; };
+  auto bar_s_full = [&](int x, int b) { return tile_bar(x, b); };        // S(t) complete (commit)
+  auto bar_p_full = [&](int x, int b) { return tile_bar(x, 2 + b); };    // P(t) stored to TMEM by the 4 warps
+  auto bar_pv_done = [&](int x, int b) { return tile_bar(x, 4 + b); };   // P.V(t) complete (commit)
+  auto bar_q_full = [&](int x) { return tile_bar(x, 6); };
+  auto bar_o_free = [&](int x) { return tile_bar(x, 7); };
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Hkv = p.Hkv, G = p.G;
   const int n_work = p.header[kHdrNumPrefill] * Hkv;
-  const int pb = p.tma_block_tokens, pb_shift = p.tma_block_shift;
   const unsigned long long wait_ns = (unsigned long long)p.wait_timeout_ms * 1000000ull;
   unsigned flags = 0;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(bar_kv_full(s), 1);
-      mbar_init(bar_kv_empty(s), 1);
+      // released by the MMA warp's commit and by one thread of every softmax group (after it has
+      // read the stage's metadata)
+      mbar_init(bar_kv_empty(s), 1 + NT);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar_s_full(b), 1);
-      mbar_init(bar_s_free(b), 4);  // one arrival per softmax warp
+    for (int x = 0; x < NT; ++x) {
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(bar_s_full(x, b), 1);
+        mbar_init(bar_p_full(x, b), 4);  // one arrival per softmax warp
+        mbar_init(bar_pv_done(x, b), 1);
+      }
+      mbar_init(bar_q_full(x), 4);
+      mbar_init(bar_o_free(x), 4);
     }
-    for (int b = 0; b < NP; ++b) {
-      mbar_init(bar_p_full(b), 4);
-      mbar_init(bar_p_free(b), 1);
-    }
-    mbar_init(bar_q_full, 4);
-    mbar_init(bar_o_free, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     fence_async_smem();
   }
   if (warp == 1) {
-    // TMEM: two S buffers (2 x 64 columns) + O (D columns)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(sb + C::OFF_TMEM), "r"(C::TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -209,9 +227,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
 
   if (warp == 0) {
     // =============================== TMA producer ===============================
-    const int blocks_per_stage = kBN >> pb_shift;
-    const int boxes_per_block = 2 * DC;                      // (K|V) x 64-element chunks of D
-    const uint32_t box_bytes = (uint32_t)pb * 128;
+    constexpr int kGroups = kBN / 8;                          // 8-token groups (= TMA boxes) per stage
     int gi = 0;  // global stage counter of this CTA
     int k = 0;
     int wid = 0;
@@ -245,37 +261,14 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       bool first = true;
       for (int pos = u.kv_begin; first || pos < u.kv_end; pos += kBN) {
         const int st = gi % NS;
-        if (!mbar_wait(bar_kv_empty(st), ((gi / NS) & 1) ^ 1, abort_flag, wait_ns)) {
-          alive = false;
-          break;
-        }
-        int nblk = (u.kv_end - pos + pb - 1) >> pb_shift;
-        if (nblk > blocks_per_stage) nblk = blocks_per_stage;
-        if (nblk < 0) nblk = 0;
-        if (lane == 0) {
-          if (first) {
-            // The ring slot of item k was last used by item k-4, whose stages are long consumed:
-            // the consumers are at most NS stages behind, and every item has at least one stage.
-            ItemDescP d;
-            d.u = u;
-            d.h = h;
-            d.index = k;
-            ring[ring_slot] = d;
-          }
-          metas[st] = make_int2(ring_slot, pos);
-          const uint32_t bytes = (uint32_t)nblk * boxes_per_block * box_bytes;
-          if (bytes > 0) mbar_arrive_expect_tx(bar_kv_full(st), bytes);
-          else mbar_arrive(bar_kv_full(st));
-        }
-        __syncwarp();
-        // one box per (page block j, K|V, chunk dc): lane -> (j, kv, dc)
-        const int nbox = nblk * boxes_per_block;
-        for (int bi = lane; bi < nbox; bi += 32) {
-          const int j = bi / boxes_per_block;
-          const int rem = bi - j * boxes_per_block;
-          const int kv = rem / DC, dc = rem - kv * DC;
-          const int key = pos + (j << pb_shift);
-          int pi, off;
+        int ngrp = (u.kv_end - pos + 7) >> 3;
+        if (ngrp > kGroups) ngrp = kGroups;
+        if (ngrp < 0) ngrp = 0;
+        // page id of this lane's 8-token group, fetched before the wait so its latency is hidden
+        int page = 0, off = 0;
+        if (lane < ngrp) {
+          const int key = pos + lane * 8;
+          int pi;
           if (p.page_shift >= 0) {
             pi = key >> p.page_shift;
             off = key & (p.page_size - 1);
@@ -283,14 +276,34 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
             pi = key / p.page_size;
             off = key - pi * p.page_size;
           }
-          int page = __ldg(tab + pi);
+          page = __ldg(tab + pi);
           if ((unsigned)page >= (unsigned)p.num_pages) {
             flags |= EJK_RPA_ST_PAGE_ID;
             page = 0;
           }
-          const uint32_t dst = sb + C::OFF_KV + st * C::STAGE_BYTES + (uint32_t)(kv * DC + dc) * (kBN * 128) +
-                               (uint32_t)(j << pb_shift) * 128;
-          tma_load_5d(dst, &tmap, bar_kv_full(st), 0, off, dc, 2 * h + kv, page);
+        }
+        if (!mbar_wait(bar_kv_empty(st), ((gi / NS) & 1) ^ 1, abort_flag, wait_ns)) {
+          alive = false;
+          break;
+        }
+        if (lane == 0) {
+          if (first) {
+            // the consumers are at most NS stages (hence at most NS items) behind: slot k-kRingP is free
+            ItemDescP d;
+            d.u = u;
+            d.h = h;
+            d.index = k;
+            ring[ring_slot] = d;
+          }
+          metas[st] = make_int2(ring_slot, pos);
+          const uint32_t bytes = (uint32_t)ngrp * C::GROUP_BYTES;
+          if (bytes > 0) mbar_arrive_expect_tx(bar_kv_full(st), bytes);
+          else mbar_arrive(bar_kv_full(st));
+        }
+        __syncwarp();
+        if (lane < ngrp) {
+          tma_load_5d(sb + C::OFF_KV + st * C::STAGE_BYTES + lane * C::GROUP_BYTES, &tmap, bar_kv_full(st), 0, off, 0,
+                      2 * h, page);
         }
         first = false;
         ++gi;
@@ -309,50 +322,90 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     // =============================== MMA issuer ===============================
     constexpr uint32_t idesc_s = instr_desc<T>(kBN, false);
     constexpr uint32_t idesc_pv = instr_desc<T>(D, true);
-    int gi = 0;       // stage whose S is issued next
-    int k_items = 0;  // items started
+    int gi = 0;                  // KV stage counter
+    int tcount[NT];              // stages issued per tile (drives the S / P buffer parities)
+    int items[NT];               // items started per tile
+    int prev_t[NT];
+    bool prev_act[NT];
+#pragma unroll
+    for (int x = 0; x < NT; ++x) {
+      tcount[x] = 0;
+      items[x] = 0;
+      prev_t[x] = 0;
+      prev_act[x] = false;
+    }
     bool have_prev = false, prev_first = false;
-    int prev_st = 0, prev_gi = 0;
+    int prev_st = 0;
     bool ok = true;
 
-    // S(gi) = Q . K^T of stage `st` into S buffer gi & 1
-    auto issue_s = [&](int st) -> bool {
-      const int b = gi & 1;
-      // the softmax warps must have drained the previous use of this S buffer
-      if (!mbar_wait(bar_s_free(b), ((gi >> 1) & 1) ^ 1, abort_flag, wait_ns)) return false;
+    // Descriptors are built once; per MMA only a small constant is added to the address field
+    // (the issuing thread's scalar work would otherwise cost more than the MMA itself).
+    // hi word: stride byte offset >> 4, version 1 (bit 46), SWIZZLE_128B (bits 61-63).
+    constexpr uint64_t kHiAtom1024 = ((uint64_t)((1024u >> 4) | (1u << 14) | (2u << 29))) << 32;
+    constexpr uint64_t kHiGroup = ((uint64_t)(((uint32_t)C::GROUP_BYTES >> 4) | (1u << 14) | (2u << 29))) << 32;
+    uint64_t q_desc[NT];
+#pragma unroll
+    for (int x = 0; x < NT; ++x) q_desc[x] = kHiAtom1024 | (uint64_t)(((sb + C::OFF_Q + x * C::Q_BYTES) >> 4) | (1u << 16));
+    const uint64_t k_desc0 = kHiGroup | (uint64_t)(((sb + C::OFF_KV) >> 4) | (1u << 16));
+    // V is MN-major: leading byte offset = distance between 64-element chunks of D (1024 B)
+    const uint64_t v_desc0 = kHiGroup | (uint64_t)(((sb + C::OFF_KV + C::V_OFF) >> 4) | ((1024u >> 4) << 16));
+
+    // Consecutive tcgen05.mma that accumulate into the same TMEM tile serialise on the accumulator,
+    // so the two tiles' MMAs are issued alternately: every instruction is independent of the one
+    // before it.
+    //
+    // S_x = Q_x . K^T of stage `st` into S buffer tcount[x] & 1, for every tile in `act`.  That
+    // buffer last held P of stage tcount[x]-2, which P.V of that stage -- issued earlier, and MMAs
+    // execute in issue order -- has finished reading by the time this MMA writes.
+    auto issue_s = [&](const bool (&act)[NT], int st) -> bool {
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t q_base = sb + C::OFF_Q;
-        const uint32_t k_base = sb + C::OFF_KV + st * C::STAGE_BYTES;
+        const uint64_t kd = k_desc0 + (uint64_t)((st * C::STAGE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t coff = (uint32_t)(kk >> 2), koff = (uint32_t)(kk & 3) * 32;
-          const uint64_t ad = smem_desc(q_base + coff * (kBM * 128) + koff, 16, 1024);
-          const uint64_t bd = smem_desc(k_base + coff * (kBN * 128) + koff, 16, 1024);
-          tc_mma(tmem_base + C::TMEM_S + b * kBN, ad, bd, idesc_s, kk > 0);
+          // K: 8-token atoms one group apart (SBO), the 64-element chunks of D 1024 bytes apart
+          const uint64_t bd = kd + (uint64_t)(((kk >> 2) * 1024 + (kk & 3) * 32) >> 4);
+#pragma unroll
+          for (int x = 0; x < NT; ++x) {
+            if (!act[x]) continue;
+            const uint64_t ad = q_desc[x] + (uint64_t)(((kk >> 2) * (kBM * 128) + (kk & 3) * 32) >> 4);
+            tc_mma(tmem_base + C::TMEM_S + (x * 2 + (tcount[x] & 1)) * kBN, ad, bd, idesc_s, kk > 0);
+          }
         }
-        tc_commit(bar_s_full(b));
+#pragma unroll
+        for (int x = 0; x < NT; ++x)
+          if (act[x]) tc_commit(bar_s_full(x, tcount[x] & 1));
       }
       __syncwarp();
       return true;
     };
-    // O (+)= P . V of the previous stage
+    // O_x (+)= P_x . V of the previous stage, for every tile that took part in it; P_x sits in TMEM
     auto issue_pv = [&]() -> bool {
-      const int pbuf = prev_gi % NP;
-      if (!mbar_wait(bar_p_full(pbuf), (prev_gi / NP) & 1, abort_flag, wait_ns)) return false;
+#pragma unroll
+      for (int x = 0; x < NT; ++x) {
+        if (!prev_act[x]) continue;
+        const int t = prev_t[x];
+        if (!mbar_wait(bar_p_full(x, t & 1), (t >> 1) & 1, abort_flag, wait_ns)) return false;
+      }
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t p_base = sb + C::OFF_P + pbuf * C::P_BYTES;
-        const uint32_t v_base = sb + C::OFF_KV + prev_st * C::STAGE_BYTES + C::KV_HALF;
+        const uint64_t vd = v_desc0 + (uint64_t)((prev_st * C::STAGE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
-          const uint64_t ad = smem_desc(p_base + kk * 32, 16, 1024);
-          // V: MN-major, 64-element chunks of D are kBN*128 bytes apart (LBO), 8-token groups 1024 (SBO)
-          const uint64_t bd = smem_desc(v_base + kk * (16 * 128), kBN * 128, 1024);
-          tc_mma(tmem_base + C::TMEM_O, ad, bd, idesc_pv, !(prev_first && kk == 0));
+          // V: 16 tokens = two 8-token groups per MMA
+          const uint64_t bd = vd + (uint64_t)((kk * 2 * C::GROUP_BYTES) >> 4);
+#pragma unroll
+          for (int x = 0; x < NT; ++x) {
+            if (!prev_act[x]) continue;
+            // P: 16 tokens = 8 columns of bf16 pairs
+            const uint32_t a_tmem = tmem_base + C::TMEM_S + (x * 2 + (prev_t[x] & 1)) * kBN + kk * 8;
+            tc_mma_ts(tmem_base + C::TMEM_O + x * D, a_tmem, bd, idesc_pv, !(prev_first && kk == 0));
+          }
         }
-        tc_commit(bar_p_free(pbuf));       // P buffer reusable; O holds this stage
-        tc_commit(bar_kv_empty(prev_st));  // both MMAs that read this KV stage are complete
+#pragma unroll
+        for (int x = 0; x < NT; ++x)
+          if (prev_act[x]) tc_commit(bar_pv_done(x, prev_t[x] & 1));  // O_x holds this stage
+        tc_commit(bar_kv_empty(prev_st));  // every MMA that read this KV stage is complete
       }
       __syncwarp();
       have_prev = false;
@@ -367,37 +420,56 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         if (have_prev) issue_pv();
         break;
       }
-      const bool first = (meta.y == ring[meta.x].u.kv_begin);
+      const Unit& iu = ring[meta.x].u;
+      const bool first = (meta.y == iu.kv_begin);
+      bool act[NT];
+#pragma unroll
+      for (int x = 0; x < NT; ++x) act[x] = (x == 0) || (iu.q_len * G > iu.row0 + x * kBM);
       if (!first) {
         // steady state: S of this stage goes to the tensor pipe before P.V of the previous one, so
         // the pipe has work while the softmax warps exponentiate
-        ok = issue_s(st);
+        ok = issue_s(act, st);
         if (ok && have_prev) ok = issue_pv();
       } else {
         // item boundary: finish the previous item first -- its epilogue must read O before this
-        // item's query tile is loaded and before the first P.V of this item overwrites O
+        // item's query tiles are loaded and before the first P.V of this item overwrites O
         if (have_prev) ok = issue_pv();
-        if (ok) ok = mbar_wait(bar_q_full, k_items & 1, abort_flag, wait_ns);
-        if (ok && k_items > 0) ok = mbar_wait(bar_o_free, (k_items - 1) & 1, abort_flag, wait_ns);
-        ++k_items;
-        if (ok) ok = issue_s(st);
+#pragma unroll
+        for (int x = 0; x < NT; ++x) {
+          if (!ok || !act[x]) continue;
+          ok = mbar_wait(bar_q_full(x), items[x] & 1, abort_flag, wait_ns);
+          if (ok && items[x] > 0) ok = mbar_wait(bar_o_free(x), (items[x] - 1) & 1, abort_flag, wait_ns);
+          ++items[x];
+        }
+        if (ok) ok = issue_s(act, st);
       }
       if (!ok) break;
       have_prev = true;
       prev_st = st;
-      prev_gi = gi;
       prev_first = first;
+#pragma unroll
+      for (int x = 0; x < NT; ++x) {
+        prev_act[x] = act[x];
+        prev_t[x] = tcount[x];
+        if (act[x]) ++tcount[x];
+      }
       ++gi;
     }
   } else {
     // =============================== softmax warps ===============================
-    const int row = (warp & 3) * 32 + lane;             // TMEM lane == tile row
+    const int x = (warp - 2) >> 2;                        // which tile of the CTA
+    const int row = (warp & 3) * 32 + lane;               // TMEM lane == row within the tile
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const int st_tid = tid - 64;                         // 0..127
-    int gi = 0;
+    const int grp_tid = (tid - 64) & 127;                 // 0..127 within the softmax group
+    const bool grp_leader = (grp_tid == 0);
+    const uint32_t tm_s = tmem_base + lane_addr + C::TMEM_S + x * 2 * kBN;
+    const uint32_t tm_o = tmem_base + lane_addr + C::TMEM_O + x * D;
+    uint8_t* q_smem = smem + C::OFF_Q + x * C::Q_BYTES;
+    int gi = 0;   // KV stage counter (all roles see the same stage sequence)
+    int ti = 0;   // stages this tile took part in
     float m_run = -INFINITY, l_run = 0.f;
     int pos_row = -1, lo_row = -1;
-    bool row_ok = false;
+    bool row_ok = false, active = false;
     int out_row_q = 0, out_head = 0;
     Unit u;
     u.kv_begin = u.kv_end = 0;
@@ -408,12 +480,22 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       const int2 meta = metas[st];
       if (meta.x < 0) break;
       const int pos = meta.y;
-      if (pos == ring[meta.x].u.kv_begin) {
-        // ---- new item: row bookkeeping and the query tile (K-major, 128B swizzle) ----
+      const bool first = (pos == ring[meta.x].u.kv_begin);
+      if (first) {
         u = ring[meta.x].u;
         h = ring[meta.x].h;
+        active = (x == 0) || (u.q_len * G > u.row0 + x * kBM);
+      }
+      // this group has read the stage's metadata: its share of the stage's release
+      if (grp_leader) mbar_arrive(bar_kv_empty(st));
+      if (!active) {  // the item has no rows for this tile
+        ++gi;
+        continue;
+      }
+      if (first) {
+        // ---- new item: row bookkeeping and the query tile (K-major, 128B swizzle) ----
         const int rows_total = u.q_len * G;
-        const int R = u.row0 + row;
+        const int R = u.row0 + x * kBM + row;
         row_ok = R < rows_total;
         const int qt = R / G, g = R - qt * G;
         out_row_q = u.q_start + qt;
@@ -422,8 +504,8 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         lo_row = (p.window > 0) ? pos_row - p.window : -1;
         m_run = -INFINITY;
         l_run = 0.f;
-        // all S MMAs of the previous item completed before its last s_full fired, which this
-        // thread waited for, so the Q tile may be overwritten
+        // all S MMAs of this tile's previous item completed before its last s_full fired, which
+        // this thread waited for, so the query tile may be overwritten
         const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) +
                                                           ((size_t)out_row_q * p.Hq + out_head) * D * sizeof(T));
 #pragma unroll
@@ -431,22 +513,19 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           uint4 v = make_uint4(0u, 0u, 0u, 0u);
           if (row_ok) v = __ldg(src + c);
           const uint32_t off = (uint32_t)(c >> 3) * (kBM * 128) + (uint32_t)row * 128 + (uint32_t)(((c & 7) ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(smem + C::OFF_Q + off) = v;
+          *reinterpret_cast<uint4*>(q_smem + off) = v;
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_q_full);
+        if (lane == 0) mbar_arrive(bar_q_full(x));
       }
-      const int b = gi & 1;
-      if (!mbar_wait(bar_s_full(b), (gi >> 1) & 1, abort_flag, wait_ns)) break;
+      const int b = ti & 1;
+      if (!mbar_wait(bar_s_full(x, b), (ti >> 1) & 1, abort_flag, wait_ns)) break;
       tc_fence_after();
       uint32_t sr[2][32];
-      tc_ld32(tmem_base + lane_addr + C::TMEM_S + b * kBN, sr[0]);
-      tc_ld32(tmem_base + lane_addr + C::TMEM_S + b * kBN + 32, sr[1]);
+      tc_ld32(tm_s + b * kBN, sr[0]);
+      tc_ld32(tm_s + b * kBN + 32, sr[1]);
       tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_s_free(b));
 
       // logits in the log2 domain, soft cap, masks (_xla_impl_fwd.py:125-138).  The common case (no
       // cap, stage entirely visible to this row) keeps the raw dot products and folds the scale into
@@ -457,7 +536,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       float mx;
       if (plain) {
         // max of scale*v is scale*max(v) or scale*min(v) depending on the sign of the scale
-        // (four independent chains: one warp per scheduler has nothing else to hide latency with)
+        // (four independent chains: few warps per scheduler, so latency must be hidden in-thread)
         float ext[4];
 #pragma unroll
         for (int a = 0; a < 4; ++a) ext[a] = __uint_as_float(sr[0][a]);
@@ -493,18 +572,14 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         for (int hlf = 0; hlf < 2; ++hlf)
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
-            float x = __uint_as_float(sr[hlf][c]);
+            float xv = __uint_as_float(sr[hlf][c]);
             const int key = pos + hlf * 32 + c;
-            if (!full_vis && (key > pos_row || key <= lo_row)) x = -INFINITY;
-            sr[hlf][c] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
+            if (!full_vis && (key > pos_row || key <= lo_row)) xv = -INFINITY;
+            sr[hlf][c] = __float_as_uint(xv);
+            mx = fmaxf(mx, xv);
           }
       }
-      const bool first_stage = (pos == u.kv_begin);
       const bool grow = (mx > m_run + kLazyP) || (m_run == -INFINITY && mx > -INFINITY);
-      const int pbuf = gi % NP;
-      // P buffer pbuf was last read by PV(gi - NP)
-      if (!mbar_wait(bar_p_free(pbuf), ((gi / NP) & 1) ^ 1, abort_flag, wait_ns)) break;
       if (__any_sync(0xffffffffu, grow)) {
         float alpha = 1.f;
         if (grow) {
@@ -512,67 +587,64 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           m_run = mx;
           l_run *= alpha;
         }
-        if (!first_stage) {
+        if (!first) {
           // O holds the sum over the earlier stages of this item: rescale this warp's 32 lanes.
-          // PV(gi-1) must have completed first.
-          if (NP == 2) {
-            const int pprev = (gi - 1) % NP;
-            if (!mbar_wait(bar_p_free(pprev), ((gi - 1) / NP) & 1, abort_flag, wait_ns)) break;
-          }
+          // This tile's P.V of stage ti-1 must have completed first.
+          if (!mbar_wait(bar_pv_done(x, (ti - 1) & 1), ((ti - 1) >> 1) & 1, abort_flag, wait_ns)) break;
           tc_fence_after();
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
             uint32_t o[32];
-            tc_ld32(tmem_base + lane_addr + C::TMEM_O + c0, o);
+            tc_ld32(tm_o + c0, o);
             tc_wait_ld();
 #pragma unroll
             for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-            tc_st32(tmem_base + lane_addr + C::TMEM_O + c0, o);
+            tc_st32(tm_o + c0, o);
           }
           tc_wait_st();
           tc_fence_before();
         }
       }
       const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+      // probabilities, packed as bf16 pairs, go back into the TMEM columns S came from
       float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint8_t* prow = smem + C::OFF_P + pbuf * C::P_BYTES + row * 128;
+      uint32_t pk[32];
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = c8 * 8 + e * 2;
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), e_scale, -m_use));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), e_scale, -m_use));
-          lsum4[e] += p0 + p1;
-          pk[e] = Mma<T>::pack(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      for (int j = 0; j < 32; ++j) {
+        const int c = 2 * j;
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), e_scale, -m_use));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), e_scale, -m_use));
+        lsum4[j & 3] += p0 + p1;
+        pk[j] = Mma<T>::pack(p0, p1);
       }
+      tc_st32(tm_s + b * kBN, pk);
       l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
-      if (pos + kBN > u.kv_end) {
+      if (x == 0 && pos + kBN > u.kv_end) {
         // Tail stage: V rows of keys >= kv_end were either never fetched (stale shared memory) or lie
         // past the sequence's length inside its last page (unowned, possibly NaN).  Their
-        // probabilities are exactly 0, but 0 * NaN would poison O, so the rows are cleared before
-        // the tensor core reads them.  (Zero rows are invariant under the swizzle.)
+        // probabilities are exactly 0, but 0 * NaN would poison O, so tile 0's group clears the rows
+        // before any tensor-core read: the MMA warp issues tile 1's P.V only after it has seen tile
+        // 0's p_full.  (Zero rows are invariant under the swizzle.)
         int nvalid = u.kv_end - pos;
         if (nvalid < 0) nvalid = 0;
-        uint8_t* vbase = smem + C::OFF_KV + st * C::STAGE_BYTES + C::KV_HALF;
+        uint8_t* vbase = smem + C::OFF_KV + st * C::STAGE_BYTES + C::V_OFF;
         const int n16 = (kBN - nvalid) * DC * 8;
-        for (int idx = st_tid; idx < n16; idx += 128) {
+        for (int idx = grp_tid; idx < n16; idx += 128) {
           const int t = nvalid + idx / (DC * 8);
           const int rem = idx % (DC * 8);
-          *reinterpret_cast<uint4*>(vbase + (rem >> 3) * (kBN * 128) + t * 128 + (rem & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(vbase + (t >> 3) * C::GROUP_BYTES + (rem >> 3) * 1024 + (t & 7) * 128 + (rem & 7) * 16) =
+              make_uint4(0u, 0u, 0u, 0u);
         }
       }
-      fence_async_smem();
+      if (x == 0 && pos + kBN > u.kv_end) fence_async_smem();  // the zeroed V rows are read by the async proxy
+      tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full(pbuf));
+      if (lane == 0) mbar_arrive(bar_p_full(x, b));
 
       if (pos + kBN >= u.kv_end) {
         // ---- last stage of the item: wait for its PV, normalise, store ----
-        if (!mbar_wait(bar_p_free(pbuf), (gi / NP) & 1, abort_flag, wait_ns)) break;
+        if (!mbar_wait(bar_pv_done(x, b), (ti >> 1) & 1, abort_flag, wait_ns)) break;
         tc_fence_after();
         float scl = 1.f, l_fin = l_run;
         if (p.num_sinks > 0 && row_ok) {
@@ -592,7 +664,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
           uint32_t o[32];
-          tc_ld32(tmem_base + lane_addr + C::TMEM_O + c0, o);
+          tc_ld32(tm_o + c0, o);
           tc_wait_ld();
           if (row_ok) {
 #pragma unroll
@@ -608,8 +680,9 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_o_free);
+        if (lane == 0) mbar_arrive(bar_o_free(x));
       }
+      ++ti;
       ++gi;
     }
   }
@@ -654,7 +727,7 @@ cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaSt
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  kern<<<n_sm, kThreadsP, C::SMEM_BYTES, stream>>>(map, p);
+  kern<<<n_sm, C::THREADS, C::SMEM_BYTES, stream>>>(map, p);
   return cudaGetLastError();
 }
 
@@ -670,6 +743,8 @@ cudaError_t dispatch(const Params& p, const CUtensorMap& map, int n_sm, cudaStre
 
 }  // namespace
 
+int prefill_rows_per_item(int head_dim) { return head_dim <= 128 ? 2 * kPrefillRows : kPrefillRows; }
+
 bool prefill_path_supported(const Params& p) {
   const int ps = p.page_size;
   if (ps < 8 || (ps & (ps - 1)) != 0) return false;
@@ -683,8 +758,8 @@ cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t st
   const uint64_t D = p.D, C2 = 2ull * p.Hkv;
   cuuint64_t dims[5] = {64, (cuuint64_t)p.page_size, D / 64, C2, (cuuint64_t)p.num_pages};
   cuuint64_t strides[4] = {C2 * D * esz, 64 * esz, D * esz, (cuuint64_t)p.page_size * C2 * D * esz};
-  // one box = PB tokens x 64 elements of one (K|V head, chunk of D): rows of 128 bytes
-  cuuint32_t box[5] = {64, (cuuint32_t)p.tma_block_tokens, 1, 1, 1};
+  // one box = 8 tokens x (K_h, V_h) x all of D: per token one contiguous 2*D-element run in global memory
+  cuuint32_t box[5] = {64, 8, (cuuint32_t)(D / 64), 2, 1};
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUtensorMap map;
   const CUtensorMapDataType dt = (dtype == EJK_RPA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;

@@ -65,7 +65,7 @@ struct Params {
   void* out;
   int32_t* header;
   Unit* units;
-  Unit* punits;    // prefill tiles: row0 is a multiple of kPrefillRows, slot unused
+  Unit* punits;    // prefill items: row0 is a multiple of prefill_item_rows, slot unused
   MergeItem* merge;
   float* part_o;   // [max_slots][Hkv][rows_per_tile][D]
   float2* part_ml; // [max_slots][Hkv][rows_per_tile]  (m in log2 domain, l)
@@ -74,6 +74,7 @@ struct Params {
   int32_t rows_per_tile;
   int32_t max_units, max_merge, max_slots, target_units, min_chunk;
   int32_t max_punits;
+  int32_t prefill_item_rows; // rows one prefill work item covers (128 per tile, 1 or 2 tiles per CTA)
   int32_t prefill_min_rows;  // sequences with q_len*G >= this go to the prefill-tile kernel; 0 = never
   int32_t window;      // <= 0: none
   int32_t num_sinks, sink_rows;
@@ -94,6 +95,7 @@ cudaError_t launch_splitkv(const Params& p, int dtype, int n_sm, cudaStream_t st
 bool tma_path_supported(const Params& p);
 cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 bool prefill_path_supported(const Params& p);
+int prefill_rows_per_item(int head_dim);
 cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 
