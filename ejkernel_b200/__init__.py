@@ -8,7 +8,7 @@ __version__ = "0.1.0"
 
 from . import kernels, modules  # noqa: F401
 from .kernels import Backend, Platform, kernel_registry
-from .modules import RaggedPageAttention, RaggedPageAttentionConfig, ragged_page_attention
+from .modules import RaggedPageAttention, RaggedPageAttentionConfig, ragged_page_attention, ragged_page_attention_v3
 
 __all__ = [
     "Backend",
@@ -17,4 +17,5 @@ __all__ = [
     "RaggedPageAttentionConfig",
     "kernel_registry",
     "ragged_page_attention",
+    "ragged_page_attention_v3",
 ]

@@ -38,6 +38,7 @@ EXPORTS = (
     "ejk_rpa_last_launch_count",
     "ejk_rpa_profile_read",
     "ejk_rpa_launch_static_scratch",
+    "ejk_rpa_v3_launch",
 )
 
 
@@ -119,6 +120,18 @@ def load() -> ctypes.CDLL:
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # queries .. num_seqs
         c_void_p,  # softmax_aux
         c_void_p,  # out
+        c_void_p,  # status
+        POINTER(Shape),
+        POINTER(Attrs),
+        c_void_p,  # stream
+    ]
+    lib.ejk_rpa_v3_launch.restype = c_int
+    lib.ejk_rpa_v3_launch.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p,  # queries, keys, values, kv_cache
+        c_void_p, c_void_p, c_void_p, c_void_p,  # kv_lens, block_tables, query_start_loc, distribution
+        c_void_p,  # out
+        c_void_p,  # workspace
+        c_size_t,
         c_void_p,  # status
         POINTER(Shape),
         POINTER(Attrs),

@@ -248,6 +248,26 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
   return 0;
 }
 
+int ejk_rpa_v3_launch(const void* queries, const void* keys, const void* values, void* kv_cache,
+                      const int32_t* kv_lens, const int32_t* block_tables, const int32_t* query_start_loc,
+                      const int32_t* distribution, void* out, void* workspace, size_t workspace_bytes, int32_t* status,
+                      const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
+  if (!keys || !values || !kv_cache || !distribution) return EJK_RPA_E_NULL;
+  if (int e = check_shape(shape)) return e;
+  if (shape->head_dim % 128 != 0) return EJK_RPA_E_HEAD_DIM;  // the v3 cache pads head_dim to 128: only unpadded rows are read here
+  if ((reinterpret_cast<uintptr_t>(keys) | reinterpret_cast<uintptr_t>(values)) & 15) return EJK_RPA_E_ALIGN;
+  const int32_t* num_seqs = distribution + 2;  // distribution = (decode_end, prefill_end, num_seqs), _kernel.py:211
+  cudaError_t ce = launch_kv_update(keys, values, kv_cache, kv_lens, block_tables, query_start_loc, num_seqs, status,
+                                    shape->total_tokens, shape->max_num_seqs, shape->pages_per_seq, shape->num_pages,
+                                    shape->page_size, shape->num_kv_heads, shape->head_dim, shape->head_dim,
+                                    static_cast<cudaStream_t>(stream));
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  const int rc = ejk_rpa_launch(queries, kv_cache, kv_lens, block_tables, query_start_loc, num_seqs, nullptr, out, workspace,
+                                workspace_bytes, status, shape, attrs, stream);
+  if (rc == 0) ++t_last_launches;
+  return rc;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Launch without a caller-provided workspace.
 //

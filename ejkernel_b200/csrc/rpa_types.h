@@ -98,5 +98,9 @@ bool prefill_path_supported(const Params& p);
 int prefill_rows_per_item(int head_dim);
 cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stream);
+cudaError_t launch_kv_update(const void* k_new, const void* v_new, void* cache, const int32_t* kv_lens,
+                             const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
+                             int32_t* status, int T, int S_max, int pages_per_seq, int num_pages, int page_size, int Hkv,
+                             int D, int Dalign, cudaStream_t stream);
 
 }  // namespace ejk

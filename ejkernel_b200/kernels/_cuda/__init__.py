@@ -2,5 +2,6 @@
 ejkernel/kernels/_cuda/__init__.py:1-15)."""
 
 from .ragged_page_attention import ragged_page_attention
+from .ragged_page_attention_v3 import ragged_page_attention_v3
 
-__all__ = ["ragged_page_attention"]
+__all__ = ["ragged_page_attention", "ragged_page_attention_v3"]

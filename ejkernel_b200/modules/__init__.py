@@ -1,5 +1,17 @@
-"""Public operator API, mirroring ``ejkernel.modules`` for the one operator this package covers."""
+"""Public operator API, mirroring ``ejkernel.modules`` for the operators this package covers."""
 
-from .operations import RaggedPageAttention, RaggedPageAttentionConfig, ragged_page_attention
+from .operations import (
+    RaggedPageAttention,
+    RaggedPageAttentionConfig,
+    RaggedPageAttentionv3Config,
+    ragged_page_attention,
+    ragged_page_attention_v3,
+)
 
-__all__ = ["RaggedPageAttention", "RaggedPageAttentionConfig", "ragged_page_attention"]
+__all__ = [
+    "RaggedPageAttention",
+    "RaggedPageAttentionConfig",
+    "RaggedPageAttentionv3Config",
+    "ragged_page_attention",
+    "ragged_page_attention_v3",
+]

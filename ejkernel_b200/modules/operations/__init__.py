@@ -1,4 +1,12 @@
 from .configs import BaseOperationConfig, RaggedPageAttentionConfig
 from .ragged_page_attention import RaggedPageAttention, ragged_page_attention
+from .ragged_page_attention_v3 import RaggedPageAttentionv3Config, ragged_page_attention_v3
 
-__all__ = ["BaseOperationConfig", "RaggedPageAttention", "RaggedPageAttentionConfig", "ragged_page_attention"]
+__all__ = [
+    "BaseOperationConfig",
+    "RaggedPageAttention",
+    "RaggedPageAttentionConfig",
+    "RaggedPageAttentionv3Config",
+    "ragged_page_attention",
+    "ragged_page_attention_v3",
+]

@@ -297,3 +297,39 @@ def make_workload(
     )
     b.meta["workload"] = name.lower()
     return b
+
+
+def to_v3_inputs(batch: RaggedBatch, fill: float = float("nan")):
+    """Recast a ``ragged_page_attention`` batch as inputs of ``ragged_page_attention_v3``.
+
+    The new key/value rows of the step are the last ``q_len`` tokens of every sequence, taken out of
+    the batch's (complete) pool; in the returned cache those positions hold ``fill`` so that the
+    operator's page write is observable.  Returns ``(keys, values, kv_cache_5d, block_tables_flat,
+    distribution)``; after a correct v3 call the cache equals ``batch.kv_pages`` bit for bit.
+    Layout as in the reference's ``merge_kv`` / cache (ragged_page_attention_v3/_kernel.py:45-57).
+    """
+    m = batch.meta
+    page, Hkv, D = m["page_size"], m["num_kv_heads"], m["head_dim"]
+    pool = batch.kv_pages
+    dev = pool.device
+    T = batch.queries.shape[0]
+    keys = torch.zeros((T, Hkv, D), dtype=pool.dtype, device=dev)
+    values = torch.zeros_like(keys)
+    cache = pool.clone()
+    cu = batch.query_start_loc.tolist()
+    tab = batch.block_tables
+    for s, (ql, kl) in enumerate(zip(m["q_lens"], m["kv_lens"])):
+        if ql == 0:
+            continue
+        pos = torch.arange(kl - ql, kl, device=dev)
+        pages = tab[s, (pos // page).long()].long()
+        slots = (pos % page).long()
+        rows = pool[pages, slots]  # [ql, 2Hkv, D]
+        keys[cu[s] : cu[s] + ql] = rows[:, 0::2]
+        values[cu[s] : cu[s] + ql] = rows[:, 1::2]
+        cache[pages, slots] = fill
+    pack = 32 // (pool.element_size() * 8)
+    cache5 = cache.view(pool.shape[0], page, 2 * Hkv // pack, pack, D)
+    S = len(m["q_lens"])
+    distribution = torch.tensor([S, S, S], dtype=torch.int32, device=dev)
+    return keys, values, cache5, batch.block_tables.reshape(-1).contiguous(), distribution

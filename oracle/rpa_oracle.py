@@ -266,6 +266,60 @@ def blocked_as_written(
     return out[:T].reshape(T, Hq, D)
 
 
+def v3_reference(
+    queries,
+    keys,
+    values,
+    kv_cache,
+    kv_lens,
+    block_tables,
+    query_start_loc,
+    distribution,
+    *,
+    softmax_scale: float = 1.0,
+    sliding_window: int | None = None,
+    logits_soft_cap: float | None = None,
+    k_scale: float | None = None,
+    v_scale: float | None = None,
+    precision: str = "fp64",
+):
+    """The v3 operator (ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:143-318): scatter the
+    new key/value rows into the paged cache, then attend against the updated cache.
+
+    ``kv_cache`` is ``[P, page, 2*Hkv/pack, pack, D]``; ``merge_kv`` (:45-57) interleaves K_h / V_h at
+    combined heads 2h / 2h+1.  Row r of sequence s lands at position ``kv_len - q_len + r`` (:227-229).
+    ``block_tables`` is flat, ``distribution[-1]`` the number of sequences (:211).  Returns
+    ``(out float64 [T,Hq,D], updated cache as a torch tensor of the cache dtype)``; attention is
+    ``dense_reference`` on the updated cache with scale ``softmax_scale * k_scale`` and the output
+    times ``v_scale`` (:262-263, :290-291).
+    """
+    cache = kv_cache.detach().cpu().clone()
+    P, page, hx2p, pack, D = cache.shape
+    C2 = hx2p * pack
+    flat = cache.view(P, page, C2, D)
+    ctx = _np(kv_lens, np.int64)
+    S_max = ctx.shape[0]
+    tab = _np(block_tables, np.int64).reshape(S_max, -1)
+    cu = _np(query_start_loc, np.int64)
+    S = int(_np(distribution).reshape(-1)[-1])
+    k = keys.detach().cpu()
+    v = values.detach().cpu()
+    Hkv = k.shape[1]
+    fused = torch.stack([k, v], dim=2).reshape(k.shape[0], 2 * Hkv, k.shape[2])  # merge_kv
+    for s in range(S):
+        q0, q1 = int(cu[s]), int(cu[s + 1])
+        kl = int(ctx[s])
+        for r in range(q1 - q0):
+            pos = kl - (q1 - q0) + r
+            flat[int(tab[s, pos // page]), pos % page, : 2 * Hkv, : k.shape[2]] = fused[q0 + r]
+    scale = float(softmax_scale) * (1.0 if k_scale is None else float(k_scale))
+    out = dense_reference(queries, flat, ctx, tab, cu, np.array([S]), softmax_scale=scale,
+                          sliding_window=sliding_window, logits_soft_cap=logits_soft_cap, precision=precision)
+    if v_scale is not None:
+        out = out * float(v_scale)
+    return out, cache
+
+
 def compare(got, want, *, atol=2e-2, rtol=2e-2, rows: int | None = None, rms_tol=3e-2, rel_tol=1e-2) -> dict:
     """Error summary of ``got`` against ``want`` on rows ``[0, rows)``.
 

@@ -40,7 +40,7 @@ REFERENCE_SIGNATURE = [
 
 
 def test_registered_under_the_reference_name_and_signature():
-    assert kernel_registry.list_algorithms() == ["ragged_page_attention"]
+    assert kernel_registry.list_algorithms() == ["ragged_page_attention", "ragged_page_attention_v3"]
     (spec,) = kernel_registry.list_implementations("ragged_page_attention")
     assert spec.platform is Platform.CUDA and spec.backend is Backend.GPU and spec.priority == 0
     impl = kernel_registry.get("ragged_page_attention", platform="cuda", backend="gpu")

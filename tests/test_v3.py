@@ -1,0 +1,90 @@
+"""``ragged_page_attention_v3``: the KV-cache page write fused with attention.  The CPU part pins the
+oracle restatement; the GPU part checks the CUDA path through the C ABI: the cache must come back
+bit-identical to the complete pool (the page write is pure data movement) and the output must match
+the oracle within the bf16 tolerance."""
+
+import numpy as np
+import pytest
+import torch
+
+from ejkernel_b200.utils import make_ragged_batch, make_workload, to_v3_inputs
+from oracle.rpa_oracle import dense_reference, v3_reference
+from tests.helpers import assert_parity
+
+
+def _cases():
+    yield "decode", make_ragged_batch([1, 1, 1], [300, 17, 64], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=61)
+    yield "mixed", make_ragged_batch([1, 40, 3, 130], [500, 40, 77, 900], num_q_heads=8, num_kv_heads=2, head_dim=128,
+                                     page_size=16, seed=62, sliding_window=256, logits_soft_cap=30.0)
+    yield "d256", make_ragged_batch([2, 70], [100, 300], num_q_heads=4, num_kv_heads=2, head_dim=256, page_size=32, seed=63)
+    yield "empty_seq", make_ragged_batch([1, 0, 5], [50, 20, 5], num_q_heads=4, num_kv_heads=4, head_dim=128, page_size=8,
+                                         max_num_seqs=5, pad_query_rows=3, seed=64)
+
+
+@pytest.mark.parametrize("name,b", list(_cases()), ids=[n for n, _ in _cases()])
+def test_oracle_v3_restores_the_pool_and_matches_v1(name, b):
+    keys, values, cache, tab_flat, dist = to_v3_inputs(b)
+    out, new_cache = v3_reference(b.queries, keys, values, cache, b.context_lens, tab_flat, b.query_start_loc, dist,
+                                  softmax_scale=b.softmax_scale, sliding_window=b.sliding_window,
+                                  logits_soft_cap=b.logits_soft_cap)
+    assert torch.equal(new_cache.view(b.kv_pages.shape), b.kv_pages)
+    want = dense_reference(*b.args(), **b.kwargs())
+    np.testing.assert_allclose(out, want, atol=1e-12)
+    # scales: k_scale multiplies the logits, v_scale the output (_kernel.py:262-263,290-291)
+    out2, _ = v3_reference(b.queries, keys, values, cache, b.context_lens, tab_flat, b.query_start_loc, dist,
+                           softmax_scale=b.softmax_scale / 2.0, k_scale=2.0, v_scale=3.0,
+                           sliding_window=b.sliding_window, logits_soft_cap=b.logits_soft_cap)
+    np.testing.assert_allclose(out2, 3.0 * want, atol=1e-12)
+
+
+def test_v3_is_registered_with_the_reference_signature():
+    import inspect
+
+    import ejkernel_b200 as ej
+
+    impl = ej.kernel_registry.get("ragged_page_attention_v3", platform="cuda", backend="gpu")
+    names = list(inspect.signature(impl).parameters)
+    assert names == ["queries", "keys", "values", "kv_cache", "kv_lens", "block_tables", "query_start_loc", "distribution",
+                     "softmax_scale", "sliding_window", "logits_soft_cap", "q_scale", "k_scale", "v_scale",
+                     "chunk_prefill_size", "num_kv_pages_per_block", "num_queries_per_block", "vmem_limit_bytes"]
+    assert inspect.signature(impl).parameters["softmax_scale"].default == 1.0
+    pub = list(inspect.signature(ej.ragged_page_attention_v3).parameters)
+    assert pub[:8] == names[:8] and pub[-5:] == ["platform", "cfg", "mesh", "in_specs", "out_specs"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,b", list(_cases()), ids=[n for n, _ in _cases()])
+def test_cuda_v3_matches_oracle_and_restores_the_pool(rpa_lib, name, b):
+    import ejkernel_b200 as ej
+
+    bc = b.to("cuda")
+    keys, values, cache, tab_flat, dist = to_v3_inputs(bc)
+    assert torch.isnan(cache.float()).any()
+    out, new_cache = ej.ragged_page_attention_v3(bc.queries, keys, values, cache, bc.context_lens, tab_flat,
+                                                 bc.query_start_loc, dist, softmax_scale=b.softmax_scale,
+                                                 sliding_window=b.sliding_window, logits_soft_cap=b.logits_soft_cap)
+    torch.cuda.synchronize()
+    assert new_cache.data_ptr() == cache.data_ptr(), "the cache is updated in place"
+    assert torch.equal(new_cache.view(bc.kv_pages.shape), bc.kv_pages), "page write must be bit-exact"
+    assert_parity(out, dense_reference(*b.args(), **b.kwargs()), b.total_tokens, what=f"v3 {name}")
+    assert torch.count_nonzero(out[b.total_tokens:]) == 0
+
+
+@pytest.mark.gpu
+def test_cuda_v3_scales_and_full_size_decode(rpa_lib):
+    import ejkernel_b200 as ej
+
+    b = make_workload("c2", num_seqs=64, device="cuda")
+    keys, values, cache, tab_flat, dist = to_v3_inputs(b)
+    ref = ej.ragged_page_attention(*b.args(), softmax_scale=b.softmax_scale)
+    out, new_cache = ej.ragged_page_attention_v3(b.queries, keys, values, cache, b.context_lens, tab_flat,
+                                                 b.query_start_loc, dist, softmax_scale=b.softmax_scale / 4.0,
+                                                 k_scale=4.0, v_scale=2.0)
+    torch.cuda.synchronize()
+    assert torch.equal(new_cache.view(b.kv_pages.shape), b.kv_pages)
+    # same kernels on the same bytes: v3 with folded scales reproduces v1 exactly (x2 is exact in bf16)
+    assert torch.equal(out, ref * 2.0)
+    with pytest.raises((ValueError, NotImplementedError)):  # head_dim 64 would need a cache padded to 128
+        b64 = make_ragged_batch([1], [10], num_q_heads=4, num_kv_heads=2, head_dim=64, page_size=8, seed=1).to("cuda")
+        k, v, c, t, d = to_v3_inputs(b64)
+        ej.ragged_page_attention_v3(b64.queries, k, v, c, b64.context_lens, t, b64.query_start_loc, d)
