@@ -39,6 +39,10 @@ import torch.distributed as dist  # noqa: E402
 
 METRIC = "paged_attn_query_tokens_per_s"
 UNIT = "tokens/s"
+# DRAM traffic of the attention kernel relative to its algorithmic KV bytes, from an ncu capture of a
+# reduced case of the same workload (dram__bytes_read.sum + dram__bytes_write.sum over KV bytes; traffic grows
+# in proportion to the KV bytes: every byte is read once).  Source: profiles/rpa_splitkv_tma_c2.md.
+NCU_TRAFFIC_RATIO = {"c2": (787.93 + 7.83) / 786.06}
 
 
 def parse_args():
@@ -424,7 +428,9 @@ def main():
             "bound": "hbm", "kernel": "rpa attention (gather + QK^T + softmax + PV)", "achieved": achieved,
             "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src,
             "frac_of_nominal_8tbs": achieved / 8000.0, "kernel_ms": k_ms, "plan_ms": statistics.mean(plan_ms),
-            "merge_ms": statistics.mean(merge_ms), "traffic": None,
+            "merge_ms": statistics.mean(merge_ms),
+            "traffic": (kv_bytes_rank * NCU_TRAFFIC_RATIO[args.workload]) if args.workload in NCU_TRAFFIC_RATIO else None,
+            "traffic_note": "bytes per launch, scaled by KV bytes from the ncu capture of a 48-sequence slice",
         },
         "cpu_baseline": cpu,
         "e2e": e2e,
