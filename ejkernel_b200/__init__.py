@@ -8,7 +8,7 @@ __version__ = "0.1.0"
 
 from . import kernels, modules  # noqa: F401
 from .kernels import Backend, Platform, kernel_registry
-from .modules import RaggedPageAttention, RaggedPageAttentionConfig, ragged_page_attention, ragged_page_attention_v3
+from .modules import page_attention, RaggedPageAttention, RaggedPageAttentionConfig, ragged_page_attention, ragged_page_attention_v3
 
 __all__ = [
     "Backend",
@@ -16,6 +16,7 @@ __all__ = [
     "RaggedPageAttention",
     "RaggedPageAttentionConfig",
     "kernel_registry",
+    "page_attention",
     "ragged_page_attention",
     "ragged_page_attention_v3",
 ]

@@ -39,6 +39,7 @@ EXPORTS = (
     "ejk_rpa_profile_read",
     "ejk_rpa_launch_static_scratch",
     "ejk_rpa_v3_launch",
+    "ejk_page_attention_launch",
 )
 
 
@@ -129,6 +130,17 @@ def load() -> ctypes.CDLL:
     lib.ejk_rpa_v3_launch.argtypes = [
         c_void_p, c_void_p, c_void_p, c_void_p,  # queries, keys, values, kv_cache
         c_void_p, c_void_p, c_void_p, c_void_p,  # kv_lens, block_tables, query_start_loc, distribution
+        c_void_p,  # out
+        c_void_p,  # workspace
+        c_size_t,
+        c_void_p,  # status
+        POINTER(Shape),
+        POINTER(Attrs),
+        c_void_p,  # stream
+    ]
+    lib.ejk_page_attention_launch.restype = c_int
+    lib.ejk_page_attention_launch.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,  # query, key_cache, value_cache, context_lens, block_tables
         c_void_p,  # out
         c_void_p,  # workspace
         c_size_t,

@@ -127,14 +127,17 @@ size_t ejk_rpa_workspace_bytes(const ejk_rpa_shape* shape) {
   return layout_for(*shape, d->sm_count).total;
 }
 
-int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* context_lens,
-                   const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
-                   const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
-                   int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
+// Shared body of the launch entry points.  `value_cache` != null selects the split cache layout
+// (kv_pages is then the key cache); with it, null query_start_loc / num_seqs mean "one query row per
+// sequence, all sequences".
+static int launch_impl(const void* queries, const void* kv_pages, const void* value_cache, const int32_t* context_lens,
+                       const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
+                       const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
+                       int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
   t_last_launches = 0;
-  if (!queries || !kv_pages || !context_lens || !block_tables || !query_start_loc || !num_seqs || !out ||
-      !workspace || !shape || !attrs)
+  if (!queries || !kv_pages || !context_lens || !block_tables || !out || !workspace || !shape || !attrs)
     return EJK_RPA_E_NULL;
+  if (!value_cache && (!query_start_loc || !num_seqs)) return EJK_RPA_E_NULL;
   if (int e = check_shape(shape)) return e;
   const ejk_rpa_shape& s = *shape;
   const ejk_rpa_attrs& a = *attrs;
@@ -157,6 +160,7 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
   std::memset(&p, 0, sizeof(p));
   p.q = queries;
   p.kv = kv_pages;
+  p.v_cache = value_cache;
   p.context_lens = context_lens;
   p.block_tables = block_tables;
   p.query_start_loc = query_start_loc;
@@ -206,8 +210,8 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
   p.tma_block_shift = 0;
   while ((1 << p.tma_block_shift) < p.tma_block_tokens) ++p.tma_block_shift;
   p.wait_timeout_ms = g_opt.wait_ms;
-  const bool use_tma = (g_opt.path == 2) || (g_opt.path == 0 && tma_path_supported(p));
-  if (use_tma && !tma_path_supported(p)) return EJK_RPA_E_ARG;
+  const bool use_tma = value_cache || (g_opt.path == 2) || (g_opt.path == 0 && tma_path_supported(p));
+  if (use_tma && !tma_path_supported(p)) return value_cache ? EJK_RPA_E_SHAPE : EJK_RPA_E_ARG;
   // Batches that can hold a sequence with many query rows also get the tcgen05 prefill-tile
   // kernel; whether any sequence actually qualifies is decided by the planner on the device.
   const bool use_prefill = use_tma && g_opt.prefill_rows > 0 && prefill_path_supported(p) &&
@@ -246,6 +250,25 @@ int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* con
     t_prof.recorded = true;
   }
   return 0;
+}
+
+int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* context_lens,
+                   const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
+                   const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
+                   int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
+  return launch_impl(queries, kv_pages, nullptr, context_lens, block_tables, query_start_loc, num_seqs, softmax_aux, out,
+                     workspace, workspace_bytes, status, shape, attrs, stream);
+}
+
+int ejk_page_attention_launch(const void* query, const void* key_cache, const void* value_cache,
+                              const int32_t* context_lens, const int32_t* block_tables, void* out, void* workspace,
+                              size_t workspace_bytes, int32_t* status, const ejk_rpa_shape* shape,
+                              const ejk_rpa_attrs* attrs, void* stream) {
+  if (!value_cache) return EJK_RPA_E_NULL;
+  if (shape && shape->total_tokens != shape->max_num_seqs) return EJK_RPA_E_SHAPE;  // one query row per sequence
+  if (reinterpret_cast<uintptr_t>(value_cache) & 15) return EJK_RPA_E_ALIGN;
+  return launch_impl(query, key_cache, value_cache, context_lens, block_tables, nullptr, nullptr, nullptr, out, workspace,
+                     workspace_bytes, status, shape, attrs, stream);
 }
 
 int ejk_rpa_v3_launch(const void* queries, const void* keys, const void* values, void* kv_cache,

@@ -21,8 +21,9 @@ struct SeqInfo {
 
 __device__ __forceinline__ SeqInfo load_seq(const Params& p, int s, unsigned& flags) {
   SeqInfo si;
-  int q0 = p.query_start_loc[s];
-  int q1 = p.query_start_loc[s + 1];
+  // no query_start_loc: a pure decode batch, one query row per sequence (page_attention)
+  int q0 = p.query_start_loc ? p.query_start_loc[s] : s;
+  int q1 = p.query_start_loc ? p.query_start_loc[s + 1] : s + 1;
   int kv = p.context_lens[s];
   const int kv_cap = p.pages_per_seq * p.page_size;
   if (kv < 0 || kv > kv_cap) {
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   const int tid = threadIdx.x;
   unsigned flags = 0;
 
-  int S = p.num_seqs[0];
+  int S = p.num_seqs ? p.num_seqs[0] : p.S_max;
   if (S > p.S_max) {
     flags |= EJK_RPA_ST_NUM_SEQS;
     S = p.S_max;

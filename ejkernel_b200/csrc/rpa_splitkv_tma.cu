@@ -72,7 +72,8 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
 
 template <typename T, int D, int NT, int NS>
 __global__ void __launch_bounds__(kThreadsTma, (CfgT<D, NT, NS>::SMEM_BYTES <= 112 * 1024) ? 2 : 1)
-rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
+rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_v,
+                       const Params p) {
   using C = CfgT<D, NT, NS>;
   constexpr int TK = C::TK, RT = C::RT;
   constexpr int KT = D / 16;
@@ -202,7 +203,15 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params p)
             flags |= EJK_RPA_ST_PAGE_ID;
             page = 0;
           }
-          tma_load_5d(smem_base + s * C::STAGE_BYTES + lane * box_bytes, &tmap, bar_full + s * 8, 0, off, 0, 2 * h, page);
+          const uint32_t dst = smem_base + s * C::STAGE_BYTES + lane * box_bytes;
+          if (p.v_cache == nullptr) {
+            tma_load_5d(dst, &tmap, bar_full + s * 8, 0, off, 0, 2 * h, page);
+          } else {
+            // separate caches [P, Hkv, page, D]: one box each for K and V, landing where the
+            // interleaved box would have put them ([K|V][D/64][PB tokens][64])
+            tma_load_5d(dst, &tmap, bar_full + s * 8, 0, off, 0, h, page);
+            tma_load_5d(dst + box_bytes / 2, &tmap_v, bar_full + s * 8, 0, off, 0, h, page);
+          }
         }
         first = false;
         if (++s == NS) {
@@ -570,7 +579,7 @@ EncodeFn encode_fn() {
 }
 
 template <typename T, int D, int NT, int NS>
-cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream) {
+cudaError_t launch_one(const Params& p, const CUtensorMap& map, const CUtensorMap& map_v, int n_sm, cudaStream_t stream) {
   using C = CfgT<D, NT, NS>;
   auto kern = rpa_splitkv_tma_kernel<T, D, NT, NS>;
   static bool configured[64] = {};
@@ -583,20 +592,20 @@ cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaSt
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int per_sm = (C::SMEM_BYTES <= 112 * 1024) ? 2 : 1;
-  kern<<<n_sm * per_sm, kThreadsTma, C::SMEM_BYTES, stream>>>(map, p);
+  kern<<<n_sm * per_sm, kThreadsTma, C::SMEM_BYTES, stream>>>(map, map_v, p);
   return cudaGetLastError();
 }
 
 template <typename T>
-cudaError_t dispatch(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream) {
+cudaError_t dispatch(const Params& p, const CUtensorMap& map, const CUtensorMap& map_v, int n_sm, cudaStream_t stream) {
   const bool wide = p.rows_per_tile == 16;
   switch (p.D) {
     case 64:
-      return wide ? launch_one<T, 64, 2, 4>(p, map, n_sm, stream) : launch_one<T, 64, 1, 4>(p, map, n_sm, stream);
+      return wide ? launch_one<T, 64, 2, 4>(p, map, map_v, n_sm, stream) : launch_one<T, 64, 1, 4>(p, map, map_v, n_sm, stream);
     case 128:
-      return wide ? launch_one<T, 128, 2, 3>(p, map, n_sm, stream) : launch_one<T, 128, 1, 3>(p, map, n_sm, stream);
+      return wide ? launch_one<T, 128, 2, 3>(p, map, map_v, n_sm, stream) : launch_one<T, 128, 1, 3>(p, map, map_v, n_sm, stream);
     case 256:
-      return wide ? launch_one<T, 256, 2, 2>(p, map, n_sm, stream) : launch_one<T, 256, 1, 3>(p, map, n_sm, stream);
+      return wide ? launch_one<T, 256, 2, 2>(p, map, map_v, n_sm, stream) : launch_one<T, 256, 1, 3>(p, map, map_v, n_sm, stream);
   }
   return cudaErrorInvalidValue;
 }
@@ -614,18 +623,33 @@ cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_
   if (!enc) return cudaErrorNotSupported;
   const uint64_t esz = 2;
   const uint64_t D = p.D, C2 = 2ull * p.Hkv;
-  // dims, innermost first: 64 elements | token in page | 64-element chunk of D | combined head | page
-  cuuint64_t dims[5] = {64, (cuuint64_t)p.page_size, D / 64, C2, (cuuint64_t)p.num_pages};
-  cuuint64_t strides[4] = {C2 * D * esz, 64 * esz, D * esz, (cuuint64_t)p.page_size * C2 * D * esz};
-  cuuint32_t box[5] = {64, (cuuint32_t)p.tma_block_tokens, (cuuint32_t)(D / 64), 2, 1};
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-  CUtensorMap map;
   const CUtensorMapDataType dt = (dtype == EJK_RPA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  CUresult r = enc(&map, dt, 5, const_cast<void*>(p.kv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16>(p, map, n_sm, stream);
-  return dispatch<__half>(p, map, n_sm, stream);
+  CUtensorMap map, map_v;
+  if (p.v_cache == nullptr) {
+    // dims, innermost first: 64 elements | token in page | 64-element chunk of D | combined head | page
+    cuuint64_t dims[5] = {64, (cuuint64_t)p.page_size, D / 64, C2, (cuuint64_t)p.num_pages};
+    cuuint64_t strides[4] = {C2 * D * esz, 64 * esz, D * esz, (cuuint64_t)p.page_size * C2 * D * esz};
+    cuuint32_t box[5] = {64, (cuuint32_t)p.tma_block_tokens, (cuuint32_t)(D / 64), 2, 1};
+    CUresult r = enc(&map, dt, 5, const_cast<void*>(p.kv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    map_v = map;
+  } else {
+    // key_cache / value_cache [P, Hkv, page, D]: 64 elements | token in page | chunk of D | kv head | page
+    cuuint64_t dims[5] = {64, (cuuint64_t)p.page_size, D / 64, (cuuint64_t)p.Hkv, (cuuint64_t)p.num_pages};
+    cuuint64_t strides[4] = {D * esz, 64 * esz, (cuuint64_t)p.page_size * D * esz,
+                             (cuuint64_t)p.Hkv * p.page_size * D * esz};
+    cuuint32_t box[5] = {64, (cuuint32_t)p.tma_block_tokens, (cuuint32_t)(D / 64), 1, 1};
+    CUresult r = enc(&map, dt, 5, const_cast<void*>(p.kv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    r = enc(&map_v, dt, 5, const_cast<void*>(p.v_cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  }
+  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16>(p, map, map_v, n_sm, stream);
+  return dispatch<__half>(p, map, map_v, n_sm, stream);
 }
 
 }  // namespace ejk

@@ -56,7 +56,8 @@ struct WorkspaceLayout {
 
 struct Params {
   const void* q;
-  const void* kv;
+  const void* kv;        // interleaved pool [P, page, 2*Hkv, D], or the key cache when v_cache is set
+  const void* v_cache;   // null, or the value cache of the split layout [P, Hkv, page, D] (page_attention)
   const int32_t* context_lens;
   const int32_t* block_tables;
   const int32_t* query_start_loc;
@@ -94,6 +95,8 @@ cudaError_t launch_plan(const Params& p, cudaStream_t stream);
 cudaError_t launch_splitkv(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 bool tma_path_supported(const Params& p);
 cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream);
+// Params conventions for the split layout (page_attention): query_start_loc == nullptr means one
+// query row per sequence (row s belongs to sequence s); num_seqs == nullptr means all S_max sequences.
 bool prefill_path_supported(const Params& p);
 int prefill_rows_per_item(int head_dim);
 cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t stream);

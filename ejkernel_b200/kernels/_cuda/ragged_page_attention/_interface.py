@@ -20,7 +20,9 @@ Semantics (reference lines in brackets):
   * softmax in fp32 over the visible keys; sinks add to the denominator only  [:161-172]
   * output has the dtype of ``queries``; rows past the last sequence are 0    [:197-201]
 ``compute_dtype`` below fp32 is not honoured for the carried softmax state: accumulation is
-always fp32 (the reference's bf16 carry only loses accuracy).
+always fp32 (the reference's bf16 carry only loses accuracy).  float32 operands are accepted and, as
+in the reference, cast to ``compute_dtype`` (bf16 by default) for the contractions; the result comes
+back as float32.
 """
 
 from __future__ import annotations
@@ -278,7 +280,22 @@ def ragged_page_attention(
     accepted and ignored exactly as the XLA entry ignores them (:93).  Returns a tensor with the
     shape and dtype of ``queries``.
     """
-    del mask_value, num_warps, num_stages, optimized, compute_dtype
+    del mask_value, num_warps, num_stages, optimized
+    if queries.dtype == torch.float32 and kv_pages.dtype == torch.float32 and queries.is_cuda:
+        # The reference casts float32 operands to ``compute_dtype`` before both contractions
+        # (_xla_impl_fwd.py:121-122,148) and returns the dtype of ``queries``; the same is done here.
+        # The cast walks the whole pool on every call: keep the cache in bf16/f16 for speed.
+        cd = torch.bfloat16 if compute_dtype in (None, "bfloat16") else compute_dtype
+        if cd not in _DTYPE_CODE:
+            raise NotImplementedError(f"compute_dtype={compute_dtype} is not supported by the CUDA path (bf16/f16 only)")
+        out16 = ragged_page_attention(
+            queries.to(cd), kv_pages.to(cd), context_lens, block_tables, query_start_loc, num_seqs,
+            softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap, compute_dtype=cd,
+            sliding_window=sliding_window, softmax_aux=softmax_aux, num_kv_pages_per_block=num_kv_pages_per_block,
+            num_queries_per_block=num_queries_per_block, vmem_limit_bytes=vmem_limit_bytes,
+        )
+        return out16.to(torch.float32)
+    del compute_dtype
     _validate(
         queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs,
         sliding_window=sliding_window, logits_soft_cap=logits_soft_cap, softmax_aux=softmax_aux,

@@ -1,6 +1,8 @@
 """Public operator API, mirroring ``ejkernel.modules`` for the operators this package covers."""
 
 from .operations import (
+    PageAttentionConfig,
+    page_attention,
     RaggedPageAttention,
     RaggedPageAttentionConfig,
     RaggedPageAttentionv3Config,
@@ -9,6 +11,8 @@ from .operations import (
 )
 
 __all__ = [
+    "PageAttentionConfig",
+    "page_attention",
     "RaggedPageAttention",
     "RaggedPageAttentionConfig",
     "RaggedPageAttentionv3Config",

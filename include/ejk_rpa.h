@@ -133,6 +133,20 @@ EJK_RPA_API int ejk_rpa_v3_launch(const void* queries, const void* keys, const v
                                   void* workspace, size_t workspace_bytes, int32_t* status,
                                   const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream);
 
+/* Decode-only paged attention over SEPARATE key / value caches
+ *   key_cache, value_cache [num_blocks, num_kv_heads, block_size, head_dim],  query / out [num_seqs, num_q_heads, head_dim],
+ *   context_lens [num_seqs], block_tables [num_seqs, max_blocks]
+ * -- the reference's `page_attention` operator (ejkernel/kernels/_xla/page_attention/_xla_impl_fwd.py:22-97;
+ * Triton split-KV + reduce version ejkernel/kernels/_triton/page_attention/_interface.py:88-369).  Same
+ * kernels as ejk_rpa_launch with a different tensor map: every sequence has one query row that sees all
+ * keys below its context length.  `shape`: total_tokens = max_num_seqs = num_seqs, pages_per_seq =
+ * max_blocks, num_pages = num_blocks, page_size = block_size (a power of two >= 8, else EJK_RPA_E_SHAPE).
+ * `attrs`: softmax_scale = attn_scale, logits_soft_cap = attn_logits_soft_cap (0 = none); the rest 0. */
+EJK_RPA_API int ejk_page_attention_launch(const void* query, const void* key_cache, const void* value_cache,
+                                          const int32_t* context_lens, const int32_t* block_tables, void* out,
+                                          void* workspace, size_t workspace_bytes, int32_t* status,
+                                          const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream);
+
 /* Size of the scratch buffer built into the library for ejk_rpa_launch_static_scratch. */
 #define EJK_RPA_STATIC_SCRATCH_BYTES (32u << 20)
 

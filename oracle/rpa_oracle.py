@@ -320,6 +320,41 @@ def v3_reference(
     return out, cache
 
 
+def page_attention_reference(query, key_cache, value_cache, context_lens, block_tables, *, attn_scale=None,
+                             attn_logits_soft_cap=None) -> np.ndarray:
+    """Decode attention over separate paged caches, float64
+    (ejkernel/kernels/_xla/page_attention/_xla_impl_fwd.py:22-97): ``query [S,Hq,D]``, caches
+    ``[num_blocks, Hkv, block_size, D]``, token j of sequence s in block ``block_tables[s, j // block_size]``,
+    keys ``j < context_lens[s]`` visible, logits ``(q.k) * attn_scale`` (default ``D**-0.5``), optional soft
+    cap (Triton version of the operator), softmax, weighted sum of V.  Sequences with no visible key give 0.
+    """
+    q = _np(query, np.float64)
+    kc = _np(key_cache, np.float64)
+    vc = _np(value_cache, np.float64)
+    ctx = _np(context_lens, np.int64)
+    tab = _np(block_tables, np.int64)
+    S, Hq, D = q.shape
+    _, Hkv, bs, _ = kc.shape
+    G = Hq // Hkv
+    scale = D**-0.5 if attn_scale is None else float(attn_scale)
+    out = np.zeros_like(q)
+    for s in range(S):
+        n = int(ctx[s])
+        if n <= 0:
+            continue
+        nb = -(-n // bs)
+        k = kc[tab[s, :nb]].transpose(1, 0, 2, 3).reshape(Hkv, nb * bs, D)[:, :n]
+        v = vc[tab[s, :nb]].transpose(1, 0, 2, 3).reshape(Hkv, nb * bs, D)[:, :n]
+        for h in range(Hkv):
+            logits = (q[s, h * G : (h + 1) * G] @ k[h].T) * scale
+            if attn_logits_soft_cap is not None:
+                logits = attn_logits_soft_cap * np.tanh(logits / attn_logits_soft_cap)
+            logits -= logits.max(axis=-1, keepdims=True)
+            p = np.exp(logits)
+            out[s, h * G : (h + 1) * G] = (p / p.sum(axis=-1, keepdims=True)) @ v[h]
+    return out
+
+
 def compare(got, want, *, atol=2e-2, rtol=2e-2, rows: int | None = None, rms_tol=3e-2, rel_tol=1e-2) -> dict:
     """Error summary of ``got`` against ``want`` on rows ``[0, rows)``.
 

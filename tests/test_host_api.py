@@ -40,7 +40,7 @@ REFERENCE_SIGNATURE = [
 
 
 def test_registered_under_the_reference_name_and_signature():
-    assert kernel_registry.list_algorithms() == ["ragged_page_attention", "ragged_page_attention_v3"]
+    assert kernel_registry.list_algorithms() == ["page_attention", "ragged_page_attention", "ragged_page_attention_v3"]
     (spec,) = kernel_registry.list_implementations("ragged_page_attention")
     assert spec.platform is Platform.CUDA and spec.backend is Backend.GPU and spec.priority == 0
     impl = kernel_registry.get("ragged_page_attention", platform="cuda", backend="gpu")
@@ -93,7 +93,7 @@ def test_public_operator_surface():
 
 def test_library_exports_every_declared_symbol(rpa_lib):
     header = (ROOT / "include" / "ejk_rpa.h").read_text()
-    declared = set(re.findall(r"EJK_RPA_API\s+[\w\s\*]+?\b(ejk_rpa_\w+)\s*\(", header))
+    declared = set(re.findall(r"EJK_RPA_API\s+[\w\s\*]+?\b(ejk_\w+)\s*\(", header))
     assert declared == set(_cabi.EXPORTS), (declared, set(_cabi.EXPORTS))
     for name in declared:
         assert getattr(rpa_lib, name) is not None

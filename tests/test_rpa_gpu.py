@@ -148,6 +148,17 @@ def test_sinks(rpa_lib):
         _check(b, f"sinks {rows}")
 
 
+def test_float32_operands_like_the_reference_dtype_test(rpa_lib):
+    # test/kernels/_triton/test_ragged_page_attention.py:88-103: output dtype follows the queries' dtype
+    b = make_ragged_batch([1, 2, 40], [500, 77, 300], num_q_heads=8, num_kv_heads=2, head_dim=64, page_size=16, seed=4)
+    bc = b.to("cuda")
+    out = run_cuda(bc)
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import ragged_page_attention
+    out32 = ragged_page_attention(bc.queries.float(), bc.kv_pages.float(), bc.context_lens, bc.block_tables,
+                                  bc.query_start_loc, bc.num_seqs, softmax_scale=bc.softmax_scale)
+    assert out32.dtype == torch.float32 and torch.equal(out32, out.float())
+
+
 def test_fp16(rpa_lib):
     b = make_ragged_batch([1, 2, 40], [500, 77, 300], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16,
                           seed=2, dtype=torch.float16)
@@ -280,7 +291,10 @@ def test_host_errors(rpa_lib):
     with pytest.raises(ValueError):
         ragged_page_attention(b.queries, b.kv_pages, b.context_lens.long(), b.block_tables, b.query_start_loc, b.num_seqs)
     with pytest.raises(NotImplementedError):
-        ragged_page_attention(b.queries.float(), b.kv_pages.float(), b.context_lens, b.block_tables, b.query_start_loc, b.num_seqs)
+        ragged_page_attention(b.queries.float(), b.kv_pages.float(), b.context_lens, b.block_tables, b.query_start_loc,
+                              b.num_seqs, compute_dtype=torch.float32)
+    with pytest.raises(NotImplementedError):
+        ragged_page_attention(b.queries, b.kv_pages.float(), b.context_lens, b.block_tables, b.query_start_loc, b.num_seqs)
     with pytest.raises(Exception):  # rank mismatch is a type-check error, as in the reference
         ragged_page_attention(b.queries[0], b.kv_pages, b.context_lens, b.block_tables, b.query_start_loc, b.num_seqs)
 
