@@ -295,7 +295,9 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
             d.index = k;
             ring[ring_slot] = d;
           }
-          metas[st] = make_int2(ring_slot, pos);
+          // meta.x = ring slot | 0x100 on the first stage of an item | 0x200 when the item has rows for tile 1
+          const bool two = (NT == 2) && (u.q_len * G > u.row0 + kBM);
+          metas[st] = make_int2(ring_slot | (first ? 0x100 : 0) | (two ? 0x200 : 0), pos);
           const uint32_t bytes = (uint32_t)ngrp * C::GROUP_BYTES;
           if (bytes > 0) mbar_arrive_expect_tx(bar_kv_full(st), bytes);
           else mbar_arrive(bar_kv_full(st));
@@ -352,14 +354,15 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
 
     // Consecutive tcgen05.mma that accumulate into the same TMEM tile serialise on the accumulator,
     // so the two tiles' MMAs are issued alternately: every instruction is independent of the one
-    // before it.
-    //
-    // S_x = Q_x . K^T of stage `st` into S buffer tcount[x] & 1, for every tile in `act`.  That
-    // buffer last held P of stage tcount[x]-2, which P.V of that stage -- issued earlier, and MMAs
-    // execute in issue order -- has finished reading by the time this MMA writes.
-    auto issue_s = [&](const bool (&act)[NT], int st) -> bool {
-      tc_fence_after();
-      if (lane == 0) {
+    // before it.  The whole role runs on lane 0: its scalar work between MMAs is on the critical
+    // path of every stage, so it is kept to a few instructions (no warp votes, flags ride in the
+    // stage metadata instead of being re-derived from the item descriptor).
+    if (lane == 0) {
+      // S_x = Q_x . K^T of stage `st` into S buffer tcount[x] & 1, for every tile in `act`.  That
+      // buffer last held P of stage tcount[x]-2, which P.V of that stage -- issued earlier, and MMAs
+      // execute in issue order -- has finished reading by the time this MMA writes.
+      auto issue_s = [&](const bool (&act)[NT], int st) {
+        tc_fence_after();
         const uint64_t kd = k_desc0 + (uint64_t)((st * C::STAGE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -375,20 +378,16 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
 #pragma unroll
         for (int x = 0; x < NT; ++x)
           if (act[x]) tc_commit(bar_s_full(x, tcount[x] & 1));
-      }
-      __syncwarp();
-      return true;
-    };
-    // O_x (+)= P_x . V of the previous stage, for every tile that took part in it; P_x sits in TMEM
-    auto issue_pv = [&]() -> bool {
+      };
+      // O_x (+)= P_x . V of the previous stage, for every tile that took part in it; P_x sits in TMEM
+      auto issue_pv = [&]() -> bool {
 #pragma unroll
-      for (int x = 0; x < NT; ++x) {
-        if (!prev_act[x]) continue;
-        const int t = prev_t[x];
-        if (!mbar_wait(bar_p_full(x, t & 1), (t >> 1) & 1, abort_flag, wait_ns)) return false;
-      }
-      tc_fence_after();
-      if (lane == 0) {
+        for (int x = 0; x < NT; ++x) {
+          if (!prev_act[x]) continue;
+          const int t = prev_t[x];
+          if (!mbar_wait_thread(bar_p_full(x, t & 1), (t >> 1) & 1, abort_flag, wait_ns)) return false;
+        }
+        tc_fence_after();
         const uint64_t vd = v_desc0 + (uint64_t)((prev_st * C::STAGE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
@@ -406,55 +405,54 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         for (int x = 0; x < NT; ++x)
           if (prev_act[x]) tc_commit(bar_pv_done(x, prev_t[x] & 1));  // O_x holds this stage
         tc_commit(bar_kv_empty(prev_st));  // every MMA that read this KV stage is complete
-      }
-      __syncwarp();
-      have_prev = false;
-      return true;
-    };
+        have_prev = false;
+        return true;
+      };
 
-    while (ok) {
-      const int st = gi % NS;
-      if (!mbar_wait(bar_kv_full(st), (gi / NS) & 1, abort_flag, wait_ns)) break;
-      const int2 meta = metas[st];
-      if (meta.x < 0) {
-        if (have_prev) issue_pv();
-        break;
-      }
-      const Unit& iu = ring[meta.x].u;
-      const bool first = (meta.y == iu.kv_begin);
-      bool act[NT];
+      while (ok) {
+        const int st = gi % NS;
+        if (!mbar_wait_thread(bar_kv_full(st), (gi / NS) & 1, abort_flag, wait_ns)) break;
+        const int mx = metas[st].x;
+        if (mx < 0) {
+          if (have_prev) issue_pv();
+          break;
+        }
+        const bool first = (mx & 0x100) != 0;
+        bool act[NT];
+        act[0] = true;
+        if (NT == 2) act[NT - 1] = (mx & 0x200) != 0;
+        if (!first) {
+          // steady state: S of this stage goes to the tensor pipe before P.V of the previous one, so
+          // the pipe has work while the softmax warps exponentiate
+          issue_s(act, st);
+          if (have_prev) ok = issue_pv();
+        } else {
+          // item boundary: finish the previous item first -- its epilogue must read O before this
+          // item's query tiles are loaded and before the first P.V of this item overwrites O
+          if (have_prev) ok = issue_pv();
 #pragma unroll
-      for (int x = 0; x < NT; ++x) act[x] = (x == 0) || (iu.q_len * G > iu.row0 + x * kBM);
-      if (!first) {
-        // steady state: S of this stage goes to the tensor pipe before P.V of the previous one, so
-        // the pipe has work while the softmax warps exponentiate
-        ok = issue_s(act, st);
-        if (ok && have_prev) ok = issue_pv();
-      } else {
-        // item boundary: finish the previous item first -- its epilogue must read O before this
-        // item's query tiles are loaded and before the first P.V of this item overwrites O
-        if (have_prev) ok = issue_pv();
+          for (int x = 0; x < NT; ++x) {
+            if (!ok || !act[x]) continue;
+            ok = mbar_wait_thread(bar_q_full(x), items[x] & 1, abort_flag, wait_ns);
+            if (ok && items[x] > 0) ok = mbar_wait_thread(bar_o_free(x), (items[x] - 1) & 1, abort_flag, wait_ns);
+            ++items[x];
+          }
+          if (ok) issue_s(act, st);
+        }
+        if (!ok) break;
+        have_prev = true;
+        prev_st = st;
+        prev_first = first;
 #pragma unroll
         for (int x = 0; x < NT; ++x) {
-          if (!ok || !act[x]) continue;
-          ok = mbar_wait(bar_q_full(x), items[x] & 1, abort_flag, wait_ns);
-          if (ok && items[x] > 0) ok = mbar_wait(bar_o_free(x), (items[x] - 1) & 1, abort_flag, wait_ns);
-          ++items[x];
+          prev_act[x] = act[x];
+          prev_t[x] = tcount[x];
+          if (act[x]) ++tcount[x];
         }
-        if (ok) ok = issue_s(act, st);
+        ++gi;
       }
-      if (!ok) break;
-      have_prev = true;
-      prev_st = st;
-      prev_first = first;
-#pragma unroll
-      for (int x = 0; x < NT; ++x) {
-        prev_act[x] = act[x];
-        prev_t[x] = tcount[x];
-        if (act[x]) ++tcount[x];
-      }
-      ++gi;
     }
+    __syncwarp();
   } else {
     // =============================== softmax warps ===============================
     const int x = (warp - 2) >> 2;                        // which tile of the CTA
@@ -480,11 +478,11 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       const int2 meta = metas[st];
       if (meta.x < 0) break;
       const int pos = meta.y;
-      const bool first = (pos == ring[meta.x].u.kv_begin);
+      const bool first = (meta.x & 0x100) != 0;
       if (first) {
-        u = ring[meta.x].u;
-        h = ring[meta.x].h;
-        active = (x == 0) || (u.q_len * G > u.row0 + x * kBM);
+        u = ring[meta.x & 0xff].u;
+        h = ring[meta.x & 0xff].h;
+        active = (x == 0) || (meta.x & 0x200) != 0;
       }
       // this group has read the stage's metadata: its share of the stage's release
       if (grp_leader) mbar_arrive(bar_kv_empty(st));

@@ -299,6 +299,43 @@ def test_host_errors(rpa_lib):
         ragged_page_attention(b.queries[0], b.kv_pages, b.context_lens, b.block_tables, b.query_start_loc, b.num_seqs)
 
 
+def test_enqueue_only_call_can_be_captured_in_a_cuda_graph(rpa_lib):
+    """The C-ABI launch allocates nothing, never synchronises and never reads device memory from the
+    host, so after one warm-up call (which sets per-device kernel attributes) the whole operator --
+    planner, tensor-tile kernel, split-KV kernel, merge -- records into a CUDA graph.  Replaying the
+    graph after changing the lengths in place must follow the new lengths: the work list is rebuilt on
+    the device every time."""
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import RpaWorkspace, ragged_page_attention_into
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import _shape_of
+
+    b = make_ragged_batch([1, 70, 1, 3], [900, 300, 64, 2000], num_q_heads=8, num_kv_heads=2, head_dim=128,
+                          page_size=16, seed=81).to("cuda")
+    ws = RpaWorkspace(_shape_of(b.queries, b.kv_pages, b.block_tables), b.queries.device)
+    out = torch.zeros_like(b.queries)
+    call = lambda: ragged_page_attention_into(out, ws, *b.args(), softmax_scale=b.softmax_scale)
+    call()
+    torch.cuda.synchronize()
+    eager = out.clone()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            ragged_page_attention_into(out, ws, *b.args(), softmax_scale=b.softmax_scale, stream=side)
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    # shorten every context in place and replay: the device planner must pick the new lengths up
+    new_lens = [500, 200, 10, 1200]
+    b.context_lens.copy_(torch.tensor(new_lens, dtype=torch.int32))
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    b.meta["kv_lens"] = new_lens
+    assert_parity(out, oracle(b), b.total_tokens, what="graph replay with new lengths")
+    assert int(ws.status.item()) == 0
+
+
 def test_public_module_entry(rpa_lib):
     import ejkernel_b200 as ej
     b = make_workload("c1")
