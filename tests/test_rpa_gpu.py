@@ -135,6 +135,36 @@ def test_prefill_threshold_does_not_change_results_beyond_tolerance(rpa_lib):
         _cabi.set_option("prefill_rows", old)
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_random_ragged_batches(rpa_lib, seed):
+    """Seeded random batches over the whole argument space: head layout, head_dim, page size (powers
+    of two and odd ones), decode / speculative / prefill query lengths, windows, caps, sinks, spare
+    sequence slots and padded query rows."""
+    rng = np.random.default_rng(9000 + seed)
+    hkv = int(rng.choice([1, 2, 4, 8]))
+    g = int(rng.choice([1, 2, 3, 4, 8, 16]))
+    d = int(rng.choice([64, 128, 256]))
+    page = int(rng.choice([1, 4, 8, 16, 16, 32, 64, 24]))
+    n = int(rng.integers(1, 9))
+    kinds = rng.choice(["decode", "spec", "prefill", "full"], size=n, p=[0.5, 0.2, 0.2, 0.1])
+    q_lens, kv_lens = [], []
+    for k in kinds:
+        kv = int(rng.integers(1, 2500))
+        ql = {"decode": 1, "spec": int(rng.integers(2, 6)), "prefill": int(rng.integers(17, 400)), "full": kv}[k]
+        ql = min(ql, kv)
+        q_lens.append(ql)
+        kv_lens.append(kv)
+    window = int(rng.integers(1, 1500)) if rng.random() < 0.3 else None
+    cap = float(rng.uniform(5, 60)) if rng.random() < 0.3 else None
+    b = make_ragged_batch(q_lens, kv_lens, num_q_heads=hkv * g, num_kv_heads=hkv, head_dim=d, page_size=page,
+                          max_num_seqs=n + int(rng.integers(0, 3)), pad_query_rows=int(rng.integers(0, 4)),
+                          seed=seed, sliding_window=window, logits_soft_cap=cap)
+    if rng.random() < 0.25:
+        gen = torch.Generator().manual_seed(seed)
+        b.softmax_aux = torch.randn(int(rng.choice([hkv, hkv * g])), 3, generator=gen)
+    _check(b, f"random seed {seed}: hkv{hkv} g{g} d{d} page{page} q{q_lens} kv{kv_lens} w{window} cap{cap}")
+
+
 def test_sinks(rpa_lib):
     for rows in ("q", "kv", "flat"):
         b = make_ragged_batch([1, 5, 1], [300, 70, 2000], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=21)
