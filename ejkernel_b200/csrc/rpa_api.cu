@@ -12,6 +12,7 @@ struct Options {
   int min_chunk = 256;
   int path = 0;
   int profile = 0;
+  int fused_merge = 1;     // the TMA split-KV kernel combines the chunks of a tile itself (no merge kernel)
   int wait_ms = 2000;      // bound of every in-kernel wait; expiry sets EJK_RPA_ST_TIMEOUT
   int prefill_rows = 64;  // sequences with at least this many (token, head-in-group) rows use 128-row tensor tiles
 };
@@ -83,6 +84,8 @@ WorkspaceLayout layout_for(const ejk_rpa_shape& s, int n_sm) {
   off = align_up(off + (size_t)L.max_merge * sizeof(MergeItem), 256);
   L.punits_off = off;
   off = align_up(off + (size_t)L.max_punits * sizeof(Unit), 256);
+  L.tickets_off = off;
+  off = align_up(off + (size_t)L.max_merge * s.num_kv_heads * sizeof(int32_t), 256);
   L.part_ml_off = off;
   off = align_up(off + (size_t)L.max_slots * s.num_kv_heads * L.rows_per_tile * sizeof(float2), 256);
   L.part_o_off = off;
@@ -171,6 +174,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.units = reinterpret_cast<Unit*>(ws + L.units_off);
   p.punits = reinterpret_cast<Unit*>(ws + L.punits_off);
   p.merge = reinterpret_cast<MergeItem*>(ws + L.merge_off);
+  p.tickets = reinterpret_cast<int32_t*>(ws + L.tickets_off);
   p.part_o = reinterpret_cast<float*>(ws + L.part_o_off);
   p.part_ml = reinterpret_cast<float2*>(ws + L.part_ml_off);
   p.status = status;
@@ -218,6 +222,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
                            (long long)s.total_tokens * p.G >= g_opt.prefill_rows &&
                            s.total_tokens > s.max_num_seqs;  // more query rows than sequences: some are multi-token
   p.prefill_min_rows = use_prefill ? g_opt.prefill_rows : 0;
+  p.fused_merge = (use_tma && g_opt.fused_merge) ? 1 : 0;
   p.prefill_item_rows = prefill_rows_per_item(s.head_dim);
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -242,9 +247,11 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
   if (prof) cudaEventRecord(t_prof.ev[2], st);
-  e = launch_merge(p, s.dtype, d->sm_count, st);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  ++t_last_launches;
+  if (!p.fused_merge) {
+    e = launch_merge(p, s.dtype, d->sm_count, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    ++t_last_launches;
+  }
   if (prof) {
     cudaEventRecord(t_prof.ev[3], st);
     t_prof.recorded = true;
@@ -340,6 +347,8 @@ int ejk_rpa_set_option(const char* name, int value) {
     g_opt.path = value;
   } else if (!std::strcmp(name, "profile")) {
     g_opt.profile = value ? 1 : 0;
+  } else if (!std::strcmp(name, "fused_merge")) {
+    g_opt.fused_merge = value ? 1 : 0;
   } else if (!std::strcmp(name, "wait_ms")) {
     if (value < 1) return EJK_RPA_E_ARG;
     g_opt.wait_ms = value;
@@ -358,6 +367,7 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "min_chunk")) *value = g_opt.min_chunk;
   else if (!std::strcmp(name, "path")) *value = g_opt.path;
   else if (!std::strcmp(name, "profile")) *value = g_opt.profile;
+  else if (!std::strcmp(name, "fused_merge")) *value = g_opt.fused_merge;
   else if (!std::strcmp(name, "wait_ms")) *value = g_opt.wait_ms;
   else if (!std::strcmp(name, "prefill_rows")) *value = g_opt.prefill_rows;
   else return EJK_RPA_E_ARG;

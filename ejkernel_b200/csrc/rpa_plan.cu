@@ -245,6 +245,10 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
           un.q_start = si.q_start;
           un.q_len = si.q_len;
           un.kv_len = si.kv_len;
+          un.merge_idx = -1;
+          un.chunk_idx = 0;
+          un.n_chunks = 1;
+          un.pad = 0;
           p.punits[atomicAdd(&s_bucket[bucket_of(lo, hi)], 1)] = un;
         }
         (void)pu;
@@ -253,6 +257,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
           int lo, hi, n, cs;
           tile_range(p, si, t, lo, hi, p.rows_per_tile);
           chunking(hi - lo, chunk, n, cs);
+          int this_merge = -1;
           if (n > 1) {
             MergeItem mi;
             mi.row0 = t * p.rows_per_tile;
@@ -261,6 +266,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
             mi.q_start = si.q_start;
             mi.q_len = si.q_len;
             mi.pad[0] = mi.pad[1] = mi.pad[2] = 0;
+            this_merge = m;
             p.merge[m++] = mi;
           }
           for (int c = 0; c < n; ++c) {
@@ -274,6 +280,10 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
             un.q_start = si.q_start;
             un.q_len = si.q_len;
             un.kv_len = si.kv_len;
+            un.merge_idx = this_merge;
+            un.chunk_idx = c;
+            un.n_chunks = n;
+            un.pad = 0;
             p.units[u++] = un;
           }
         }
@@ -281,6 +291,11 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
     }
 #pragma unroll
     for (int k = 0; k < kCnt; ++k) base[k] += total[k];
+  }
+  // arrival counters of the fused merge start at zero on every call
+  {
+    const int n_tickets = (base[1] <= p.max_merge ? base[1] : 0) * p.Hkv;
+    for (int i = tid; i < n_tickets; i += kPlanThreads) p.tickets[i] = 0;
   }
   if (tid == 0) {
     const bool over = base[0] > p.max_units || base[1] > p.max_merge || base[2] > p.max_slots || base[3] > p.max_punits;

@@ -36,7 +36,7 @@ constexpr float kLazyRescale = 8.0f;  // rescale the accumulators only when the 
 struct ItemDesc {
   Unit u;
   int32_t h;
-  int32_t pad[7];
+  int32_t pad[3];
 };
 
 template <int D, int NT, int NS>
@@ -140,9 +140,10 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
       Unit u;
       {
         const int4* src = reinterpret_cast<const int4*>(p.units + ui);
-        const int4 a = __ldg(src), b = __ldg(src + 1);
+        const int4 a = __ldg(src), b = __ldg(src + 1), c3 = __ldg(src + 2);
         u.seq = a.x; u.row0 = a.y; u.kv_begin = a.z; u.kv_end = a.w;
         u.slot = b.x; u.q_start = b.y; u.q_len = b.z; u.kv_len = b.w;
+        u.merge_idx = c3.x; u.chunk_idx = c3.y; u.n_chunks = c3.z; u.pad = 0;
       }
       const int ring_slot = k % kRingTma;
       int wid_next = 0;
@@ -544,6 +545,78 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
             *reinterpret_cast<float4*>(po + r * D + d) = v;
           }
           if (tid < n_rows) pml[tid] = make_float2(row_m[tid], row_l[tid]);
+          if (p.fused_merge) {
+            // Last-arriver merge: publish this chunk's partial, take a ticket for (tile, kv head); the
+            // chunk that draws the last ticket combines all of them, in chunk order, so the result
+            // does not depend on which chunk finished last.  No CTA ever waits for another.
+            __threadfence();
+            if (!consumer_sync()) break;
+            if (tid == 0) {
+              const int old = atomicAdd(&p.tickets[(size_t)u.merge_idx * Hkv + h], 1);
+              row_l[0] = (old == u.n_chunks - 1) ? 1.f : 0.f;  // row_l/row_m were consumed above
+            }
+            if (!consumer_sync()) break;
+            const bool last = row_l[0] != 0.f;
+            if (last) {
+              __threadfence();
+              constexpr int VPL = D / 32;
+              const int slot0 = u.slot - u.chunk_idx;
+              T* out = reinterpret_cast<T*>(p.out);
+              for (int r = warp; r < n_rows; r += kConsumerWarps) {
+                float m_tot = -INFINITY;
+                for (int c = lane; c < u.n_chunks; c += 32)
+                  m_tot = fmaxf(m_tot, __ldcg(&p.part_ml[((size_t)(slot0 + c) * Hkv + h) * RT + r]).x);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m_tot = fmaxf(m_tot, __shfl_xor_sync(0xffffffffu, m_tot, o));
+                const float mu = (m_tot == -INFINITY) ? 0.f : m_tot;
+                float accm[VPL];
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) accm[i] = 0.f;
+                float l_tot = 0.f;
+                for (int c = 0; c < u.n_chunks; ++c) {
+                  const size_t base = ((size_t)(slot0 + c) * Hkv + h) * RT + r;
+                  const float2 ml = __ldcg(&p.part_ml[base]);
+                  const float f = fast_exp2(ml.x - mu);
+                  l_tot += ml.y * f;
+                  const float* src = p.part_o + base * D + lane * VPL;
+                  if constexpr (VPL == 2) {
+                    const float2 v = __ldcg(reinterpret_cast<const float2*>(src));
+                    accm[0] += v.x * f;
+                    accm[1] += v.y * f;
+                  } else {
+#pragma unroll
+                    for (int i = 0; i < VPL; i += 4) {
+                      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + i));
+                      accm[i] += v.x * f;
+                      accm[i + 1] += v.y * f;
+                      accm[i + 2] += v.z * f;
+                      accm[i + 3] += v.w * f;
+                    }
+                  }
+                }
+                const int R = u.row0 + r;
+                const int qt = R / G, g = R - qt * G;
+                const int hq = h * G + g;
+                float scl = 1.f, l_fin = l_tot;
+                if (p.num_sinks > 0) {
+                  const int srow = (p.sink_rows == p.Hq) ? hq : (p.sink_rows == Hkv ? h : 0);
+                  const float* sk = p.sinks + (size_t)srow * p.num_sinks;
+                  float sm = -INFINITY;
+                  for (int i = 0; i < p.num_sinks; ++i) sm = fmaxf(sm, sk[i] * kLog2e);
+                  const float m_fin = fmaxf(m_tot, sm);
+                  const float mf = (m_fin == -INFINITY) ? 0.f : m_fin;
+                  scl = fast_exp2(m_tot - mf);
+                  l_fin = l_tot * scl;
+                  for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
+                }
+                scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
+                T* dst = out + ((size_t)(u.q_start + qt) * p.Hq + hq) * D + lane * VPL;
+#pragma unroll
+                for (int i = 0; i < VPL; i += 2)
+                  *reinterpret_cast<uint32_t*>(dst + i) = Mma<T>::pack(accm[i] * scl, accm[i + 1] * scl);
+              }
+            }
+          }
         }
         // The next item's writes to mbuf/lbuf come before its first consumer_sync, but they only
         // race with readers of mbuf/lbuf, and those finished before round 0's sync above; its

@@ -24,9 +24,14 @@ struct Unit {
   int32_t q_start;   // query_start_loc[seq]
   int32_t q_len;
   int32_t kv_len;
+  int32_t merge_idx;  // index of the tile's MergeItem (chunks > 1), else -1
+  int32_t chunk_idx;  // which chunk of the tile this is
+  int32_t n_chunks;
+  int32_t pad;
 };
+static_assert(sizeof(Unit) == 48, "Unit is read as three 16-byte words");
 
-// One row tile whose chunks must be combined by the merge kernel.
+// One row tile whose chunks must be combined (by the last chunk to finish, or by the merge kernel).
 struct MergeItem {
   int32_t row0;
   int32_t slot0;     // partial slots slot0 .. slot0+n_chunks-1
@@ -50,7 +55,7 @@ enum HeaderWord {
 };
 
 struct WorkspaceLayout {
-  size_t header_off, units_off, merge_off, part_o_off, part_ml_off, punits_off, total;
+  size_t header_off, units_off, merge_off, part_o_off, part_ml_off, punits_off, tickets_off, total;
   int32_t max_units, max_merge, max_slots, rows_per_tile, target_units, max_punits;
 };
 
@@ -68,6 +73,8 @@ struct Params {
   Unit* units;
   Unit* punits;    // prefill items: row0 is a multiple of prefill_item_rows, slot unused
   MergeItem* merge;
+  int32_t* tickets; // [max_merge][Hkv] arrival counters of the chunks of one (tile, kv head); zeroed by the planner
+  int32_t fused_merge; // 1: the split-KV kernel combines the chunks itself (last arriver), no merge kernel
   float* part_o;   // [max_slots][Hkv][rows_per_tile][D]
   float2* part_ml; // [max_slots][Hkv][rows_per_tile]  (m in log2 domain, l)
   int32_t* status; // may be null

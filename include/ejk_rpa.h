@@ -185,6 +185,8 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *   "path"       0 = auto, 1 = force the cp.async gather, 2 = force the TMA gather
  *   "prefill_rows" sequences with at least this many (query token, head-in-group) rows per kv head are
  *                served by 128-row tcgen05 tiles instead of 8-row split-KV tiles (default 64; 0 = never)
+ *   "fused_merge" 1 (default) = the split-KV kernel's last-finishing chunk combines the chunks of its tile;
+ *                0 = a separate merge kernel does
  *   "wait_ms"    wall-time bound, in milliseconds, of every wait inside a kernel (default 2000)
  *   "profile"    1 = record CUDA events around each kernel of a launch (see ejk_rpa_profile_read)
  * Returns 0, or EJK_RPA_E_ARG for an unknown name.  Counterpart of the reference's

@@ -135,6 +135,30 @@ def test_prefill_threshold_does_not_change_results_beyond_tolerance(rpa_lib):
         _cabi.set_option("prefill_rows", old)
 
 
+def test_fused_merge_equals_merge_kernel_bitwise(rpa_lib):
+    """The split-KV kernel's last-arriver merge and the separate merge kernel combine the chunks of a
+    tile in the same order with the same arithmetic: outputs are bitwise equal, run after run."""
+    from ejkernel_b200 import _cabi
+    b = make_ragged_batch([1, 1, 4, 1, 2], [6000, 37, 2900, 9000, 700], num_q_heads=16, num_kv_heads=2,
+                          head_dim=128, page_size=16, seed=61, max_num_seqs=7)
+    b.softmax_aux = torch.randn(16, 2, generator=torch.Generator().manual_seed(4))
+    want = oracle(b)
+    old = _cabi.get_option("fused_merge"), _cabi.get_option("waves")
+    try:
+        _cabi.set_option("waves", 64)  # many chunks per tile
+        _cabi.set_option("fused_merge", 1)
+        fused = [run_cuda(b) for _ in range(3)]
+        _cabi.set_option("fused_merge", 0)
+        split = run_cuda(b)
+    finally:
+        _cabi.set_option("fused_merge", old[0])
+        _cabi.set_option("waves", old[1])
+    assert_parity(fused[0], want, b.total_tokens, what="fused merge")
+    for o in fused[1:]:
+        assert torch.equal(o, fused[0])
+    assert torch.equal(split, fused[0])
+
+
 @pytest.mark.parametrize("seed", range(24))
 def test_random_ragged_batches(rpa_lib, seed):
     """Seeded random batches over the whole argument space: head layout, head_dim, page size (powers
