@@ -92,6 +92,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that lets the hardware park the thread for up to `hint_ns` while the phase is incomplete
+// (it wakes as soon as the phase completes): a waiting warp then issues almost no instructions,
+// which matters when it shares a scheduler with warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_try_wait_park(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+constexpr uint32_t kParkNs = 4000;
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
@@ -106,7 +123,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (!ok) {
     const unsigned long long t0 = global_timer_ns();
     while (true) {
-      if (mbar_try_wait(bar, parity)) {
+      if (mbar_try_wait_park(bar, parity, kParkNs)) {
         ok = true;
         break;
       }
@@ -125,7 +142,7 @@ __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, 
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_park(bar, parity, kParkNs)) return true;
     if (*abort_flag) return false;
     if (global_timer_ns() - t0 > timeout_ns) break;
   }
