@@ -13,6 +13,7 @@ struct Options {
   int path = 0;
   int profile = 0;
   int prefill_kernel = 0;  // 0 = ping-pong tiles over wide KV stages where head_dim allows, 1 = 64-token stages
+  int overlap = 1;         // programmatic dependent launches: kernels of one call overlap where they are independent
   int fused_merge = 1;     // the TMA split-KV kernel combines the chunks of a tile itself (no merge kernel)
   int wait_ms = 2000;      // bound of every in-kernel wait; expiry sets EJK_RPA_ST_TIMEOUT
   int prefill_rows = 64;  // sequences with at least this many (token, head-in-group) rows use 128-row tensor tiles
@@ -236,16 +237,23 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   }
   t_prof.recorded = false;
   if (prof) cudaEventRecord(t_prof.ev[0], st);
+  // Programmatic dependent launches (not while profiling: the event records in between would
+  // serialise the kernels anyway).  The prefill kernel starts under the planner's tail and waits for
+  // the plan on the device; the split-KV kernel starts as soon as every prefill CTA has seen the plan
+  // and takes over the SMs that prefill CTAs leave -- the two kernels write different rows.  Without
+  // a prefill kernel the split-KV kernel is the planner's dependent and waits for the plan itself.
+  const bool pdl = g_opt.overlap != 0 && !prof && use_tma;
+  p.pdl = pdl ? (use_prefill ? 1 : 2) : 0;
   cudaError_t e = launch_plan(p, st);
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
   if (prof) cudaEventRecord(t_prof.ev[1], st);
   if (use_prefill) {
-    e = launch_prefill(p, s.dtype, d->sm_count, st);
+    e = launch_prefill(p, s.dtype, d->sm_count, st, pdl);
     if (e != cudaSuccess) return static_cast<int>(e);
     ++t_last_launches;
   }
-  e = use_tma ? launch_splitkv_tma(p, s.dtype, d->sm_count, st) : launch_splitkv(p, s.dtype, d->sm_count, st);
+  e = use_tma ? launch_splitkv_tma(p, s.dtype, d->sm_count, st, pdl) : launch_splitkv(p, s.dtype, d->sm_count, st);
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
   if (prof) cudaEventRecord(t_prof.ev[2], st);
@@ -349,6 +357,8 @@ int ejk_rpa_set_option(const char* name, int value) {
     g_opt.path = value;
   } else if (!std::strcmp(name, "profile")) {
     g_opt.profile = value ? 1 : 0;
+  } else if (!std::strcmp(name, "overlap")) {
+    g_opt.overlap = value ? 1 : 0;
   } else if (!std::strcmp(name, "fused_merge")) {
     g_opt.fused_merge = value ? 1 : 0;
   } else if (!std::strcmp(name, "prefill_kernel")) {
@@ -372,6 +382,7 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "min_chunk")) *value = g_opt.min_chunk;
   else if (!std::strcmp(name, "path")) *value = g_opt.path;
   else if (!std::strcmp(name, "profile")) *value = g_opt.profile;
+  else if (!std::strcmp(name, "overlap")) *value = g_opt.overlap;
   else if (!std::strcmp(name, "fused_merge")) *value = g_opt.fused_merge;
   else if (!std::strcmp(name, "prefill_kernel")) *value = g_opt.prefill_kernel;
   else if (!std::strcmp(name, "wait_ms")) *value = g_opt.wait_ms;

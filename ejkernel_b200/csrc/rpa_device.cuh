@@ -150,6 +150,13 @@ __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, 
   return false;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while its predecessor in the stream is still running.  pdl_wait() blocks until that
+// predecessor has completed and its memory is visible; pdl_trigger() lets this kernel's own
+// dependents start (they are released once every CTA has called it or exited).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));

@@ -5,6 +5,7 @@
 // data-dependent loops (ejkernel/kernels/_xla/ragged_page_attention/_xla_impl_fwd.py:187-201).
 // Here the same iteration space is flattened into (sequence, row tile, KV chunk) items of nearly
 // equal size so that 148 SMs stay evenly loaded when lengths differ by 64x.
+#include "rpa_device.cuh"
 #include "rpa_types.h"
 
 namespace ejk {
@@ -118,6 +119,8 @@ __device__ void block_scan(int (&v)[kCnt], int (&excl)[kCnt], int (&total)[kCnt]
 }
 
 __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) {
+  // kernels launched as programmatic dependents may start their prologue now; they pdl_wait() for the plan
+  pdl_trigger();
   __shared__ int s_warp[32][kCnt];
   __shared__ unsigned long long s_keys;
   __shared__ int s_chunk;

@@ -124,7 +124,6 @@ rpa_prefill_pp_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Hkv = p.Hkv, G = p.G;
-  const int n_work = p.header[kHdrNumPrefill] * Hkv;
   const unsigned long long wait_ns = (unsigned long long)p.wait_timeout_ms * 1000000ull;
   unsigned flags = 0;
 
@@ -160,6 +159,13 @@ rpa_prefill_pp_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched as a programmatic dependent of the planner: everything above overlapped its tail.  The
+  // split-KV kernel that follows in the stream works on other rows and may start on SMs that this
+  // kernel's CTAs have left; it is released once every CTA has passed this point, i.e. after the
+  // plan is complete.
+  if (p.pdl & 1) pdl_wait();
+  pdl_trigger();
+  const int n_work = p.header[kHdrNumPrefill] * Hkv;
 
   if (warp == 0) {
     // =============================== TMA producer ===============================
@@ -624,7 +630,7 @@ rpa_prefill_pp_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
 }
 
 template <typename T, int D>
-cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream) {
+cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream, bool pdl) {
   using C = Cfg2<D>;
   auto kern = rpa_prefill_pp_kernel<T, D>;
   static bool configured[64] = {};
@@ -636,20 +642,19 @@ cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaSt
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  kern<<<n_sm, C::THREADS, C::SMEM_BYTES, stream>>>(map, p);
-  return cudaGetLastError();
+  return launch_kernel(kern, dim3(n_sm), dim3(C::THREADS), C::SMEM_BYTES, stream, pdl, map, p);
 }
 
 }  // namespace
 
 // head_dim 64 or 128; `map` is the 5-D tensor map the 64-token-stage kernel uses (same boxes).
-cudaError_t launch_prefill_pingpong(const Params& p, int dtype, const CUtensorMap& map, int n_sm, cudaStream_t stream) {
+cudaError_t launch_prefill_pingpong(const Params& p, int dtype, const CUtensorMap& map, int n_sm, cudaStream_t stream, bool pdl) {
   if (dtype == EJK_RPA_BF16) {
-    if (p.D == 64) return launch_one<__nv_bfloat16, 64>(p, map, n_sm, stream);
-    if (p.D == 128) return launch_one<__nv_bfloat16, 128>(p, map, n_sm, stream);
+    if (p.D == 64) return launch_one<__nv_bfloat16, 64>(p, map, n_sm, stream, pdl);
+    if (p.D == 128) return launch_one<__nv_bfloat16, 128>(p, map, n_sm, stream, pdl);
   } else {
-    if (p.D == 64) return launch_one<__half, 64>(p, map, n_sm, stream);
-    if (p.D == 128) return launch_one<__half, 128>(p, map, n_sm, stream);
+    if (p.D == 64) return launch_one<__half, 64>(p, map, n_sm, stream, pdl);
+    if (p.D == 128) return launch_one<__half, 128>(p, map, n_sm, stream, pdl);
   }
   return cudaErrorInvalidValue;
 }

@@ -116,7 +116,6 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Hkv = p.Hkv, G = p.G;
-  const int n_work = p.header[kHdrNumPrefill] * Hkv;
   const unsigned long long wait_ns = (unsigned long long)p.wait_timeout_ms * 1000000ull;
   unsigned flags = 0;
 
@@ -149,6 +148,10 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // programmatic dependent of the planner (see rpa_prefill_pp_sm100.cu)
+  if (p.pdl & 1) pdl_wait();
+  pdl_trigger();
+  const int n_work = p.header[kHdrNumPrefill] * Hkv;
 
   if (warp == 0) {
     // =============================== TMA producer ===============================
@@ -638,7 +641,7 @@ EncodeFn encode_fn_p() {
 }
 
 template <typename T, int D>
-cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream) {
+cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream, bool pdl) {
   using C = CfgP<D>;
   auto kern = rpa_prefill_tc_kernel<T, D>;
   static bool configured[64] = {};
@@ -650,16 +653,15 @@ cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaSt
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  kern<<<n_sm, C::THREADS, C::SMEM_BYTES, stream>>>(map, p);
-  return cudaGetLastError();
+  return launch_kernel(kern, dim3(n_sm), dim3(C::THREADS), C::SMEM_BYTES, stream, pdl, map, p);
 }
 
 template <typename T>
-cudaError_t dispatch(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream) {
+cudaError_t dispatch(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream, bool pdl) {
   switch (p.D) {
-    case 64: return launch_one<T, 64>(p, map, n_sm, stream);
-    case 128: return launch_one<T, 128>(p, map, n_sm, stream);
-    case 256: return launch_one<T, 256>(p, map, n_sm, stream);
+    case 64: return launch_one<T, 64>(p, map, n_sm, stream, pdl);
+    case 128: return launch_one<T, 128>(p, map, n_sm, stream, pdl);
+    case 256: return launch_one<T, 256>(p, map, n_sm, stream, pdl);
   }
   return cudaErrorInvalidValue;
 }
@@ -667,7 +669,7 @@ cudaError_t dispatch(const Params& p, const CUtensorMap& map, int n_sm, cudaStre
 }  // namespace
 
 // rpa_prefill_pp_sm100.cu
-cudaError_t launch_prefill_pingpong(const Params& p, int dtype, const CUtensorMap& map, int n_sm, cudaStream_t stream);
+cudaError_t launch_prefill_pingpong(const Params& p, int dtype, const CUtensorMap& map, int n_sm, cudaStream_t stream, bool pdl);
 
 int prefill_rows_per_item(int head_dim) { return head_dim <= 128 ? 2 * kPrefillRows : kPrefillRows; }
 
@@ -677,7 +679,7 @@ bool prefill_path_supported(const Params& p) {
   return encode_fn_p() != nullptr;
 }
 
-cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t stream) {
+cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t stream, bool pdl) {
   EncodeFn enc = encode_fn_p();
   if (!enc) return cudaErrorNotSupported;
   const uint64_t esz = 2;
@@ -692,9 +694,9 @@ cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t st
   CUresult r = enc(&map, dt, 5, const_cast<void*>(p.kv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-  if (p.D <= 128 && p.prefill_kernel == 0) return launch_prefill_pingpong(p, dtype, map, n_sm, stream);
-  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16>(p, map, n_sm, stream);
-  return dispatch<__half>(p, map, n_sm, stream);
+  if (p.D <= 128 && p.prefill_kernel == 0) return launch_prefill_pingpong(p, dtype, map, n_sm, stream, pdl);
+  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16>(p, map, n_sm, stream, pdl);
+  return dispatch<__half>(p, map, n_sm, stream, pdl);
 }
 
 }  // namespace ejk

@@ -96,7 +96,6 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Hkv = p.Hkv, G = p.G;
-  const int n_work = p.header[kHdrNumUnits] * Hkv;
   const int pb = p.tma_block_tokens;       // tokens per TMA box (power of two, >= 8)
   const int pb_shift = p.tma_block_shift;
   const unsigned long long wait_ns = (unsigned long long)p.wait_timeout_ms * 1000000ull;
@@ -113,6 +112,9 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   __syncthreads();
+  // launched as a programmatic dependent of the planner: everything above overlapped its tail
+  if (p.pdl & 2) pdl_wait();
+  const int n_work = p.header[kHdrNumUnits] * Hkv;
 
   if (warp == kConsumerWarps) {
     // =============================== producer warp ===============================
@@ -652,7 +654,7 @@ EncodeFn encode_fn() {
 }
 
 template <typename T, int D, int NT, int NS>
-cudaError_t launch_one(const Params& p, const CUtensorMap& map, const CUtensorMap& map_v, int n_sm, cudaStream_t stream) {
+cudaError_t launch_one(const Params& p, const CUtensorMap& map, const CUtensorMap& map_v, int n_sm, cudaStream_t stream, bool pdl) {
   using C = CfgT<D, NT, NS>;
   auto kern = rpa_splitkv_tma_kernel<T, D, NT, NS>;
   static bool configured[64] = {};
@@ -665,20 +667,19 @@ cudaError_t launch_one(const Params& p, const CUtensorMap& map, const CUtensorMa
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int per_sm = (C::SMEM_BYTES <= 112 * 1024) ? 2 : 1;
-  kern<<<n_sm * per_sm, kThreadsTma, C::SMEM_BYTES, stream>>>(map, map_v, p);
-  return cudaGetLastError();
+  return launch_kernel(kern, dim3(n_sm * per_sm), dim3(kThreadsTma), C::SMEM_BYTES, stream, pdl, map, map_v, p);
 }
 
 template <typename T>
-cudaError_t dispatch(const Params& p, const CUtensorMap& map, const CUtensorMap& map_v, int n_sm, cudaStream_t stream) {
+cudaError_t dispatch(const Params& p, const CUtensorMap& map, const CUtensorMap& map_v, int n_sm, cudaStream_t stream, bool pdl) {
   const bool wide = p.rows_per_tile == 16;
   switch (p.D) {
     case 64:
-      return wide ? launch_one<T, 64, 2, 4>(p, map, map_v, n_sm, stream) : launch_one<T, 64, 1, 4>(p, map, map_v, n_sm, stream);
+      return wide ? launch_one<T, 64, 2, 4>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 64, 1, 4>(p, map, map_v, n_sm, stream, pdl);
     case 128:
-      return wide ? launch_one<T, 128, 2, 3>(p, map, map_v, n_sm, stream) : launch_one<T, 128, 1, 3>(p, map, map_v, n_sm, stream);
+      return wide ? launch_one<T, 128, 2, 3>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 128, 1, 3>(p, map, map_v, n_sm, stream, pdl);
     case 256:
-      return wide ? launch_one<T, 256, 2, 2>(p, map, map_v, n_sm, stream) : launch_one<T, 256, 1, 3>(p, map, map_v, n_sm, stream);
+      return wide ? launch_one<T, 256, 2, 2>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 256, 1, 3>(p, map, map_v, n_sm, stream, pdl);
   }
   return cudaErrorInvalidValue;
 }
@@ -691,7 +692,7 @@ bool tma_path_supported(const Params& p) {
   return encode_fn() != nullptr;
 }
 
-cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream) {
+cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream, bool pdl) {
   EncodeFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
   const uint64_t esz = 2;
@@ -721,8 +722,8 @@ cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   }
-  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16>(p, map, map_v, n_sm, stream);
-  return dispatch<__half>(p, map, map_v, n_sm, stream);
+  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16>(p, map, map_v, n_sm, stream, pdl);
+  return dispatch<__half>(p, map, map_v, n_sm, stream, pdl);
 }
 
 }  // namespace ejk

@@ -83,6 +83,7 @@ struct Params {
   int32_t max_units, max_merge, max_slots, target_units, min_chunk;
   int32_t max_punits;
   int32_t prefill_item_rows; // rows one prefill work item covers (128 per tile, 1 or 2 tiles per CTA)
+  int32_t pdl;               // bit 0: the prefill kernel, bit 1: the split-KV kernel must pdl_wait() before reading the plan
   int32_t prefill_kernel;    // 0 = widest-stage kernel the head_dim allows, 1 = the 64-token-stage kernel
   int32_t prefill_min_rows;  // sequences with q_len*G >= this go to the prefill-tile kernel; 0 = never
   int32_t window;      // <= 0: none
@@ -102,12 +103,30 @@ struct Params {
 cudaError_t launch_plan(const Params& p, cudaStream_t stream);
 cudaError_t launch_splitkv(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 bool tma_path_supported(const Params& p);
-cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream);
+cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream, bool pdl);
 // Params conventions for the split layout (page_attention): query_start_loc == nullptr means one
 // query row per sequence (row s belongs to sequence s); num_seqs == nullptr means all S_max sequences.
 bool prefill_path_supported(const Params& p);
 int prefill_rows_per_item(int head_dim);
-cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t stream);
+cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t stream, bool pdl);
+
+// <<<>>> with, optionally, the programmatic-stream-serialization attribute: the kernel may then begin
+// while the previous kernel of the stream is still running (see pdl_wait / pdl_trigger).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 cudaError_t launch_kv_update(const void* k_new, const void* v_new, void* cache, const int32_t* kv_lens,
                              const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
