@@ -224,7 +224,15 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
                            (long long)s.total_tokens * p.G >= g_opt.prefill_rows &&
                            s.total_tokens > s.max_num_seqs;  // more query rows than sequences: some are multi-token
   p.prefill_min_rows = use_prefill ? g_opt.prefill_rows : 0;
-  p.fused_merge = (use_tma && g_opt.fused_merge) ? 1 : 0;
+  // The last-arriver merge inside the split-KV kernel saves a launch, but the chunk that arrives last
+  // combines its tile alone: with many chunks per tile (few query rows, long contexts) the separate
+  // merge kernel, which spreads the rows over the whole GPU, is faster.  Decided from static shapes:
+  // fused when a tile gets at most ~4 chunks on average.
+  // (option value 2 forces the fused merge.)
+  p.fused_merge = (use_tma && (g_opt.fused_merge == 2 ||
+                               (g_opt.fused_merge == 1 && (long long)L.target_units <= 4ll * s.total_tokens)))
+                      ? 1
+                      : 0;
   p.prefill_item_rows = prefill_rows_per_item(s.head_dim);
   p.prefill_kernel = g_opt.prefill_kernel;
 
@@ -360,7 +368,8 @@ int ejk_rpa_set_option(const char* name, int value) {
   } else if (!std::strcmp(name, "overlap")) {
     g_opt.overlap = value ? 1 : 0;
   } else if (!std::strcmp(name, "fused_merge")) {
-    g_opt.fused_merge = value ? 1 : 0;
+    if (value < 0 || value > 2) return EJK_RPA_E_ARG;
+    g_opt.fused_merge = value;
   } else if (!std::strcmp(name, "prefill_kernel")) {
     if (value < 0 || value > 1) return EJK_RPA_E_ARG;
     g_opt.prefill_kernel = value;

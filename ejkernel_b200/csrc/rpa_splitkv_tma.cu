@@ -575,24 +575,39 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
 #pragma unroll
                 for (int i = 0; i < VPL; ++i) accm[i] = 0.f;
                 float l_tot = 0.f;
-                for (int c = 0; c < u.n_chunks; ++c) {
-                  const size_t base = ((size_t)(slot0 + c) * Hkv + h) * RT + r;
-                  const float2 ml = __ldcg(&p.part_ml[base]);
-                  const float f = fast_exp2(ml.x - mu);
-                  l_tot += ml.y * f;
-                  const float* src = p.part_o + base * D + lane * VPL;
-                  if constexpr (VPL == 2) {
-                    const float2 v = __ldcg(reinterpret_cast<const float2*>(src));
-                    accm[0] += v.x * f;
-                    accm[1] += v.y * f;
-                  } else {
+                // four chunks' loads in flight at a time (each is an L2 round trip); the sums still run in
+                // chunk order
+                for (int c0 = 0; c0 < u.n_chunks; c0 += 4) {
+                  float2 ml[4];
+                  float vv[4][VPL];
 #pragma unroll
-                    for (int i = 0; i < VPL; i += 4) {
-                      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + i));
-                      accm[i] += v.x * f;
-                      accm[i + 1] += v.y * f;
-                      accm[i + 2] += v.z * f;
-                      accm[i + 3] += v.w * f;
+                  for (int j = 0; j < 4; ++j) {
+                    const int c = min(c0 + j, u.n_chunks - 1);
+                    const size_t base = ((size_t)(slot0 + c) * Hkv + h) * RT + r;
+                    ml[j] = __ldcg(&p.part_ml[base]);
+                    const float* src = p.part_o + base * D + lane * VPL;
+                    if constexpr (VPL == 2) {
+                      const float2 v = __ldcg(reinterpret_cast<const float2*>(src));
+                      vv[j][0] = v.x;
+                      vv[j][1] = v.y;
+                    } else {
+#pragma unroll
+                      for (int i = 0; i < VPL; i += 4) {
+                        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + i));
+                        vv[j][i] = v.x;
+                        vv[j][i + 1] = v.y;
+                        vv[j][i + 2] = v.z;
+                        vv[j][i + 3] = v.w;
+                      }
+                    }
+                  }
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if (c0 + j < u.n_chunks) {
+                      const float f = fast_exp2(ml[j].x - mu);
+                      l_tot += ml[j].y * f;
+#pragma unroll
+                      for (int i = 0; i < VPL; ++i) accm[i] += vv[j][i] * f;
                     }
                   }
                 }

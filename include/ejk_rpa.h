@@ -189,8 +189,9 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *                1 = always the 64-token-stage kernel (the only one for head_dim 256)
  *   "overlap"    1 (default) = the kernels of one call are launched as programmatic dependents: each starts under
  *                the tail of the one before and waits on the device for what it needs; 0 = plain stream order
- *   "fused_merge" 1 (default) = the split-KV kernel's last-finishing chunk combines the chunks of its tile;
- *                0 = a separate merge kernel does
+ *   "fused_merge" 1 (default) = where a row tile gets few KV chunks (decided from the static shapes) the split-KV
+ *                kernel's last-finishing chunk combines the chunks of its tile; 0 = always a separate merge kernel;
+ *                2 = always fused
  *   "wait_ms"    wall-time bound, in milliseconds, of every wait inside a kernel (default 2000)
  *   "profile"    1 = record CUDA events around each kernel of a launch (see ejk_rpa_profile_read)
  * Returns 0, or EJK_RPA_E_ARG for an unknown name.  Counterpart of the reference's

@@ -161,6 +161,33 @@ def test_both_prefill_tile_kernels(rpa_lib, variant):
         _cabi.set_option("prefill_kernel", old)
 
 
+def test_overlapped_launches_equal_stream_order_bitwise(rpa_lib):
+    """With programmatic dependent launches the prefill kernel starts under the planner's tail and the
+    split-KV kernel runs beside the prefill kernel's last CTAs; the kernels write different rows, so
+    the output is bitwise the same as in plain stream order -- mixed, decode-only and prefill-only batches."""
+    from ejkernel_b200 import _cabi
+    batches = [
+        make_ragged_batch([300, 1, 1, 200, 1, 3], [2000, 900, 3000, 260, 17, 640], num_q_heads=16, num_kv_heads=4,
+                          head_dim=128, page_size=16, seed=81),
+        make_ragged_batch([1] * 40, [int(x) for x in np.random.default_rng(5).integers(1, 3000, 40)], num_q_heads=8,
+                          num_kv_heads=2, head_dim=128, page_size=32, seed=82),
+        make_ragged_batch([512], [1536], num_q_heads=8, num_kv_heads=8, head_dim=64, page_size=64, seed=83),
+    ]
+    old = _cabi.get_option("overlap")
+    try:
+        for i, b in enumerate(batches):
+            want = oracle(b)
+            _cabi.set_option("overlap", 1)
+            outs = [run_cuda(b) for _ in range(3)]
+            _cabi.set_option("overlap", 0)
+            plain = run_cuda(b)
+            assert_parity(outs[0], want, b.total_tokens, what=f"overlap batch {i}")
+            for o in outs:
+                assert torch.equal(o, plain), i
+    finally:
+        _cabi.set_option("overlap", old)
+
+
 def test_fused_merge_equals_merge_kernel_bitwise(rpa_lib):
     """The split-KV kernel's last-arriver merge and the separate merge kernel combine the chunks of a
     tile in the same order with the same arithmetic: outputs are bitwise equal, run after run."""
@@ -172,7 +199,7 @@ def test_fused_merge_equals_merge_kernel_bitwise(rpa_lib):
     old = _cabi.get_option("fused_merge"), _cabi.get_option("waves")
     try:
         _cabi.set_option("waves", 64)  # many chunks per tile
-        _cabi.set_option("fused_merge", 1)
+        _cabi.set_option("fused_merge", 2)  # force it (by default such a batch gets the separate kernel)
         fused = [run_cuda(b) for _ in range(3)]
         _cabi.set_option("fused_merge", 0)
         split = run_cuda(b)
