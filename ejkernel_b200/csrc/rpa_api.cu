@@ -12,7 +12,6 @@ struct Options {
   int min_chunk = 256;
   int path = 0;
   int profile = 0;
-  int prefill_kernel = 0;  // 0 = ping-pong tiles over wide KV stages where head_dim allows, 1 = 64-token stages
   int overlap = 1;         // programmatic dependent launches: kernels of one call overlap where they are independent
   int fused_merge = 1;     // the TMA split-KV kernel combines the chunks of a tile itself (no merge kernel)
   int wait_ms = 2000;      // bound of every in-kernel wait; expiry sets EJK_RPA_ST_TIMEOUT
@@ -234,7 +233,6 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
                       ? 1
                       : 0;
   p.prefill_item_rows = prefill_rows_per_item(s.head_dim);
-  p.prefill_kernel = g_opt.prefill_kernel;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool prof = g_opt.profile != 0;
@@ -370,9 +368,6 @@ int ejk_rpa_set_option(const char* name, int value) {
   } else if (!std::strcmp(name, "fused_merge")) {
     if (value < 0 || value > 2) return EJK_RPA_E_ARG;
     g_opt.fused_merge = value;
-  } else if (!std::strcmp(name, "prefill_kernel")) {
-    if (value < 0 || value > 1) return EJK_RPA_E_ARG;
-    g_opt.prefill_kernel = value;
   } else if (!std::strcmp(name, "wait_ms")) {
     if (value < 1) return EJK_RPA_E_ARG;
     g_opt.wait_ms = value;
@@ -393,7 +388,6 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "profile")) *value = g_opt.profile;
   else if (!std::strcmp(name, "overlap")) *value = g_opt.overlap;
   else if (!std::strcmp(name, "fused_merge")) *value = g_opt.fused_merge;
-  else if (!std::strcmp(name, "prefill_kernel")) *value = g_opt.prefill_kernel;
   else if (!std::strcmp(name, "wait_ms")) *value = g_opt.wait_ms;
   else if (!std::strcmp(name, "prefill_rows")) *value = g_opt.prefill_rows;
   else return EJK_RPA_E_ARG;

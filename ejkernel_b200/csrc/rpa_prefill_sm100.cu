@@ -1,46 +1,48 @@
-// Prefill tiles of ragged paged attention on the 5th-generation tensor cores (tcgen05 + TMEM).
+// Prefill tiles of ragged paged attention on tcgen05 + TMEM: two 128-row tiles per CTA (one at
+// head_dim 256), each with its own MMA-issuing warps and softmax warps, sharing the KV stages.
 //
-// A chunked-prefill sequence contributes q_len*G (query token, head-in-group) rows per kv head;
-// 128 of them form one tile, the M of a tcgen05.mma.  Per 64-token KV stage the tile needs two dense
-// contractions, exactly the two einsums of the reference's inner loop
-// (ejkernel/kernels/_xla/ragged_page_attention/_xla_impl_fwd.py:119-124,148), here as
-//     S[128 x 64]  = Q[128 x D] . K^T          tcgen05.mma kind::f16, A,B from shared memory, D in TMEM
-//     O[128 x D]  += P[128 x 64] . V           tcgen05.mma, A (P) from TMEM, B (V) MN-major from shared
-//                                              memory, accumulator in TMEM
-// with the online softmax (:125-151) in between done by one thread per row on values read from TMEM
-// with tcgen05.ld, so the row maximum and row sum need no shuffles at all.
+// Per 64-token KV stage and per tile x (the two einsums of the reference's inner loop,
+// _xla_impl_fwd.py:119-124,148 of ejkernel/kernels/_xla/ragged_page_attention):
+//     S_x[128 x 64] = Q_x[128 x D] . K^T           D/16 tcgen05.mma, A and B from shared memory
+//     O_x[128 x D] += P_x[128 x 64] . V            4 tcgen05.mma, A = P_x from TMEM, B = V MN-major
+// What bounds such a tile is not the tensor pipe (measured: ~55 cycles per S MMA, ~77 per P.V MMA when
+// issued back to back) but latency: a softmax warp needs ~1100 cycles per stage (one warp per scheduler
+// and tile runs at a fraction of an instruction per cycle), every hand-off through an mbarrier costs
+// 100+ cycles while the tensor pipe and the TMA unit stream through shared memory, and a thread
+// that issues MMAs spends 50-150 cycles on each.  So the kernel is arranged for nobody to wait for
+// anybody longer than necessary:
+//   * S_x, P_x (two buffers) and O_x live in different TMEM columns.  As soon as the softmax warps
+//     hold S_x(j) in registers (one tcgen05.ld) they release the S columns and the tile's S issuer
+//     puts S_x(j+1) on the pipe while the exponentials of stage j are computed; P_x(j) goes to
+//     buffer j & 1, so it never waits for P_x.V(j-1) either.
+//   * S and P.V of each tile are issued by different warps (four single-thread issuing roles), so
+//     that no role's waits delay another's MMAs.
+//   * the two tiles' softmax warps share the schedulers and the MUFU unit (4 exponentials per cycle
+//     and scheduler); they take turns at the exponentials, so that one tile's waits and TMEM
+//     traffic overlap the other's MUFU phase instead of both phases running in lockstep.
+//   TMEM (512 columns at head_dim 128): S_0 S_1 (64 fp32 columns each), P_0[2] P_1[2] (32 columns
+//   of 16-bit pairs each), O_0 O_1 (D each).  At head_dim 256 one tile: S, P[2], O = 384 columns.
+// Things measured and left out: a polynomial 2^x on the FMA pipe for part of the exponentials (no gain:
+// issue slots are as scarce as MUFU slots with so few warps), two threads per row (the exchange of
+// row maxima costs more than the shorter rows save), 80/96/128-token stages with P aliased on S
+// (the tile's S -> softmax -> P.V chain then bounds the stage).
 //
-// One CTA works on NT = 2 such tiles at once (256 consecutive rows of the same sequence and kv head;
-// NT = 1 at head_dim 256 where TMEM holds only one O accumulator): both tiles consume the same KV
-// stage, which halves the L2 -> shared-memory traffic per FLOP.  That traffic, not the tensor pipe,
-// is what bounds a 128-row tile: a stage of 32 KB feeds only 4.2 MFLOP.
+// Warp roles (416 threads with two tiles, one CTA per SM, persistent over the planner's prefill queue):
+//   warp 0        TMA producer: one box {64 elems, 8 tokens, D/64, (K_h, V_h)} per 8-token group,
+//                 SWIZZLE_128B, 8 boxes per stage, page ids from the block table; publishes every
+//                 item in a ring.  No multicast.
+//   warp 1        S issuer of tile 0 (lane 0 only; the warp owns the TMEM allocation)
+//   warps 2-5     softmax of tile 0, warps 6-9 of tile 1: thread = TMEM lane = tile row; the row's
+//                 logits of the stage sit in registers; lazy rescaling of O (only when the maximum
+//                 grows by more than 2^8), normalisation, sinks, store.
+//   warps 10-12   S issuer of tile 1, P.V issuers of tiles 0 and 1 (one tile: warp 6 issues P.V)
 //
-// Warp roles (64 + 128*NT threads, one CTA per SM, persistent over a device work queue):
-//   warp 0      TMA producer: page-table driven gather of K_h / V_h, one box
-//               {64 elems, 8 tokens, D/64, (K_h,V_h)} per 8-token group, SWIZZLE_128B.  A box keeps
-//               the 2*D contiguous elements of a token together (512-byte runs in global memory;
-//               the TMA unit's cost is per contiguous run, so 128-byte runs are 4x slower), and lands as
-//               [group of 8 tokens][K|V][D/64][8 tokens][64]: 8-row x 128-byte swizzle atoms at a uniform
-//               stride, i.e. a canonical K-major (K) / MN-major (V) operand of tcgen05.mma with
-//               stride-byte-offset = one group.  No cluster multicast.
-//   warp 1      MMA issuer (one lane): S for stage i+1 is issued before P.V of stage i so the tensor
-//               pipe works while the softmax warps exponentiate; owns the TMEM allocation.
-//   warps 2-5   softmax of tile 0 (warps 6-9: tile 1): thread = TMEM lane = tile row.  Loads the tile's query rows into the
-//               K-major swizzled A layout, reads S, masks, exponentiates (log2 domain, lazy
-//               rescaling of O in TMEM only when a row maximum grows by more than 2^8), writes P
-//               (bf16 pairs) back into the TMEM columns S came from with tcgen05.st -- the A
-//               operand of the P.V MMA -- and finally normalises O and stores the rows.  The tensor
-//               pipe executes MMAs in issue order, so S of stage i+2 cannot overwrite those columns
-//               before P.V of stage i has read them.
-//
-// All hand-offs are mbarriers; tcgen05.commit signals MMA completion.  Every wait is bounded: on
-// expiry the warp sets the CTA abort flag, every other wait gives up when it sees the flag, the
-// status word gets EJK_RPA_ST_TIMEOUT, and the CTA still frees its TMEM before it returns.
+// All hand-offs are mbarriers; every wait is bounded in wall time (Params::wait_timeout_ms): on
+// expiry the warp raises the CTA's abort flag, every other wait gives up when it sees it, the status
+// word gets EJK_RPA_ST_TIMEOUT and the CTA still frees its TMEM before it returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-
-#include <type_traits>
 
 #include "rpa_tcgen05.cuh"
 #include "rpa_types.h"
@@ -48,45 +50,47 @@
 namespace ejk {
 namespace {
 
-constexpr int kBM = kPrefillRows;  // 128
-constexpr int kBN = kTileTokens;   // 64
+constexpr int kBM = kPrefillRows;  // 128 rows per tile
 constexpr int kRingP = 16;
 constexpr float kLog2eP = 1.4426950408889634f;
 constexpr float kLazyP = 8.0f;
 
+
 struct ItemDescP {
   Unit u;
   int32_t h;
-  int32_t index;  // running item number of this CTA
-  int32_t pad[6];
+  int32_t pad[3];
 };
 
 template <int D>
 struct CfgP {
-  static constexpr int NT = (D <= 128) ? 2 : 1;                    // 128-row tiles per CTA
-  static constexpr int THREADS = 64 + 128 * NT;
-  static constexpr int NS = (D == 64) ? 8 : (D == 128) ? 5 : 2;    // KV stages (as many as shared memory holds)
-  static constexpr int STAGE_BYTES = kBN * 2 * D * 2;
+  // tokens per KV stage = N of the S MMA: the largest for which TMEM holds S and two P buffers per tile
+  static constexpr int BN = 64;
+  static constexpr int NT = (D <= 128) ? 2 : 1;       // 128-row tiles per CTA (TMEM holds one 256-column O)
+  static constexpr int SM_WARPS = 4;                  // softmax warps per tile: one thread per row
+  static constexpr int THREADS = 64 + 32 * SM_WARPS * NT + 32 * (2 * NT - 1);  // producer, S issuer 0, softmax groups, the other issuers
+  static constexpr int STAGE_BYTES = BN * 2 * D * 2;
+  static constexpr int NS = (D == 64) ? 8 : (D == 128) ? 4 : 2;
   static constexpr int GROUP_BYTES = 8 * 2 * D * 2;   // one 8-token group: [K|V][D/64][8][64]
-  static constexpr int V_OFF = (D / 64) * 1024;       // V atoms follow the K atoms inside a group
-  static constexpr int Q_BYTES = kBM * D * 2;         // per tile
+  static constexpr int V_OFF = (D / 64) * 1024;
+  static constexpr int Q_BYTES = kBM * D * 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_KV = OFF_Q + NT * Q_BYTES;
   static constexpr int OFF_RING = OFF_KV + NS * STAGE_BYTES;
   static constexpr int OFF_META = OFF_RING + kRingP * (int)sizeof(ItemDescP);
   static constexpr int OFF_BAR = OFF_META + NS * 8;
-  // barriers: kv_full[NS] kv_empty[NS], then per tile: s_full[2] p_full[2] pv_done[2] q_full o_free
-  static constexpr int BAR_PER_TILE = 8;
+  // barriers: kv_full[NS] kv_empty[NS], then per tile: s_full s_free p_full[2] pv_done[2] q_full o_free skip turn
+  static constexpr int BAR_PER_TILE = 10;
   static constexpr int N_BAR = 2 * NS + NT * BAR_PER_TILE;
   static constexpr int OFF_TMEM = OFF_BAR + N_BAR * 8;
-  static constexpr int OFF_ABORT = OFF_TMEM + 8;
+  static constexpr int OFF_ABORT = OFF_TMEM + 8;   // abort flag, then the published-items counter
   static constexpr int SMEM_BYTES = OFF_ABORT + 8 + 1024;
-  // TMEM columns: per tile two S/P buffers of 64 columns, then per tile one O accumulator of D columns
-  static constexpr uint32_t TMEM_S = 0;
-  static constexpr uint32_t TMEM_O = NT * 2 * kBN;
-  static constexpr uint32_t TMEM_NEED = NT * (2 * kBN + D);
-  static constexpr uint32_t TMEM_COLS = TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
-  static_assert(TMEM_NEED <= 512, "TMEM holds 512 columns");
+  static constexpr uint32_t P_COLS = BN / 2;               // one P buffer (16-bit pairs)
+  static constexpr uint32_t TMEM_S = 0;                    // S_x at x*BN
+  static constexpr uint32_t TMEM_P = NT * BN;              // P_x[b] at 2*BN + (2x + b)*P_COLS
+  static constexpr uint32_t TMEM_O = 512 - NT * D;         // O_x at the top
+  static constexpr uint32_t TMEM_COLS = 512;
+  static_assert(BN % 16 == 0 && TMEM_P + NT * 2 * P_COLS <= TMEM_O, "TMEM holds 512 columns");
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
@@ -94,7 +98,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(CfgP<D>::THREADS, 1)
 rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) {
   using C = CfgP<D>;
-  constexpr int NS = C::NS, NT = C::NT;
+  constexpr int NS = C::NS, NT = C::NT, kBN = C::BN;
   constexpr int DC = D / 64;
 
   extern __shared__ uint8_t smem_raw[];
@@ -103,16 +107,20 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   ItemDescP* ring = reinterpret_cast<ItemDescP*>(smem + C::OFF_RING);
   int2* metas = reinterpret_cast<int2*>(smem + C::OFF_META);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT);
+  volatile int* items_pub = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT + 4);  // items in the ring so far
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_TMEM);
   const uint32_t bar0 = sb + C::OFF_BAR;
   auto bar_kv_full = [&](int s) { return bar0 + s * 8; };
   auto bar_kv_empty = [&](int s) { return bar0 + (NS + s) * 8; };
   auto tile_bar = [&](int x, int i) { return bar0 + (2 * NS + x * C::BAR_PER_TILE + i) * 8; };
-  auto bar_s_full = [&](int x, int b) { return tile_bar(x, b); };        // S(t) complete (commit)
-  auto bar_p_full = [&](int x, int b) { return tile_bar(x, 2 + b); };    // P(t) stored to TMEM by the 4 warps
-  auto bar_pv_done = [&](int x, int b) { return tile_bar(x, 4 + b); };   // P.V(t) complete (commit)
+  auto bar_s_full = [&](int x) { return tile_bar(x, 0); };    // S_x(t) complete (commit)
+  auto bar_s_free = [&](int x) { return tile_bar(x, 1); };    // S_x(t) is in the 4 warps' registers
+  auto bar_p_full = [&](int x, int b) { return tile_bar(x, 2 + b); };   // P_x(t) stored to buffer t&1 by the softmax warps
+  auto bar_pv_done = [&](int x, int b) { return tile_bar(x, 4 + b); };  // P_x.V(t) complete (commit): buffer t&1 is free
   auto bar_q_full = [&](int x) { return tile_bar(x, 6); };
   auto bar_o_free = [&](int x) { return tile_bar(x, 7); };
+  auto bar_skip = [&](int x) { return tile_bar(x, 8); };
+  auto bar_turn = [&](int x) { return tile_bar(x, 9); };      // tile x has issued the exponentials of a stage      // the 4 warps have seen an item without rows for tile x
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Hkv = p.Hkv, G = p.G;
@@ -122,20 +130,23 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(bar_kv_full(s), 1);
-      // released by the MMA warp's commit and by one thread of every softmax group (after it has
-      // read the stage's metadata)
-      mbar_init(bar_kv_empty(s), 1 + NT);
+      // released by the four MMA-issuing roles (commit, or a plain arrival when the tile is idle)
+      mbar_init(bar_kv_empty(s), 2 * NT);
     }
     for (int x = 0; x < NT; ++x) {
+      mbar_init(bar_s_full(x), 1);
+      mbar_init(bar_s_free(x), C::SM_WARPS);  // one arrival per softmax warp
       for (int b = 0; b < 2; ++b) {
-        mbar_init(bar_s_full(x, b), 1);
-        mbar_init(bar_p_full(x, b), 4);  // one arrival per softmax warp
+        mbar_init(bar_p_full(x, b), C::SM_WARPS);
         mbar_init(bar_pv_done(x, b), 1);
       }
-      mbar_init(bar_q_full(x), 4);
-      mbar_init(bar_o_free(x), 4);
+      mbar_init(bar_q_full(x), C::SM_WARPS);
+      mbar_init(bar_o_free(x), C::SM_WARPS);
+      mbar_init(bar_skip(x), C::SM_WARPS);
+      mbar_init(bar_turn(x), C::SM_WARPS);
     }
     *abort_flag = 0;
+    *items_pub = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     fence_async_smem();
   }
@@ -148,15 +159,18 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // programmatic dependent of the planner (see rpa_prefill_pp_sm100.cu)
+  // Launched as a programmatic dependent of the planner: everything above overlapped its tail.  The
+  // split-KV kernel that follows in the stream works on other rows and may start on SMs that this
+  // kernel's CTAs have left; it is released once every CTA has passed this point, i.e. after the
+  // plan is complete.
   if (p.pdl & 1) pdl_wait();
   pdl_trigger();
   const int n_work = p.header[kHdrNumPrefill] * Hkv;
 
   if (warp == 0) {
     // =============================== TMA producer ===============================
-    constexpr int kGroups = kBN / 8;                          // 8-token groups (= TMA boxes) per stage
-    int gi = 0;  // global stage counter of this CTA
+    constexpr int kGroups = kBN / 8;  // 8-token groups (= TMA boxes) per stage
+    int gi = 0;  // stage counter of this CTA
     int k = 0;
     int wid = 0;
     if (lane == 0) wid = atomicAdd(&p.header[kHdrPrefillQueue], 1);
@@ -164,11 +178,13 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     bool alive = true;
     while (alive) {
       const int s = gi % NS;
-      const uint32_t empty_parity = ((gi / NS) & 1) ^ 1;
       if (wid >= n_work) {
-        if (!mbar_wait(bar_kv_empty(s), empty_parity, abort_flag, wait_ns)) break;
+        if (!mbar_wait(bar_kv_empty(s), ((gi / NS) & 1) ^ 1, abort_flag, wait_ns)) break;
         if (lane == 0) {
           metas[s] = make_int2(-1, 0);
+          ring[k % kRingP].u.seq = -1;  // end of the item sequence, for the softmax groups
+          __threadfence_block();
+          *items_pub = k + 1;
           mbar_arrive(bar_kv_full(s));
         }
         break;
@@ -181,6 +197,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         const int4 a = __ldg(src), b = __ldg(src + 1);
         u.seq = a.x; u.row0 = a.y; u.kv_begin = a.z; u.kv_end = a.w;
         u.slot = b.x; u.q_start = b.y; u.q_len = b.z; u.kv_len = b.w;
+        u.merge_idx = -1; u.chunk_idx = 0; u.n_chunks = 1; u.pad = 0;
       }
       const int ring_slot = k % kRingP;
       int wid_next = 0;
@@ -216,15 +233,17 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         }
         if (lane == 0) {
           if (first) {
-            // the consumers are at most NS stages (hence at most NS items) behind: slot k-kRingP is free
+            // every role is within NS + 2 items of this warp (the MMA warps through the stage ring, each
+            // softmax group through q_full / skip of its MMA warp): slot k - kRingP is free
             ItemDescP d;
             d.u = u;
             d.h = h;
-            d.index = k;
             ring[ring_slot] = d;
+            __threadfence_block();
+            *items_pub = k + 1;
           }
           // meta.x = ring slot | 0x100 on the first stage of an item | 0x200 when the item has rows for tile 1
-          const bool two = (NT == 2) && (u.q_len * G > u.row0 + kBM);
+          const bool two = NT == 2 && u.q_len * G > u.row0 + kBM;
           metas[st] = make_int2(ring_slot | (first ? 0x100 : 0) | (two ? 0x200 : 0), pos);
           const uint32_t bytes = (uint32_t)ngrp * C::GROUP_BYTES;
           if (bytes > 0) mbar_arrive_expect_tx(bar_kv_full(st), bytes);
@@ -248,188 +267,157 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       if (g2 < NS) continue;  // never used
       if (!mbar_wait(bar_kv_empty(g2 % NS), ((g2 / NS) & 1) ^ 1, abort_flag, wait_ns)) break;
     }
-  } else if (warp == 1) {
-    // =============================== MMA issuer ===============================
-    constexpr uint32_t idesc_s = instr_desc<T>(kBN, false);
-    constexpr uint32_t idesc_pv = instr_desc<T>(D, true);
-    int gi = 0;                  // KV stage counter
-    int tcount[NT];              // stages issued per tile (drives the S / P buffer parities)
-    int items[NT];               // items started per tile
-    int prev_t[NT];
-    bool prev_act[NT];
-#pragma unroll
-    for (int x = 0; x < NT; ++x) {
-      tcount[x] = 0;
-      items[x] = 0;
-      prev_t[x] = 0;
-      prev_act[x] = false;
-    }
-    bool have_prev = false, prev_first = false;
-    int prev_st = 0;
-    bool ok = true;
-
-    // Descriptors are built once; per MMA only a small constant is added to the address field
-    // (the issuing thread's scalar work would otherwise cost more than the MMA itself).
-    // hi word: stride byte offset >> 4, version 1 (bit 46), SWIZZLE_128B (bits 61-63).
-    constexpr uint64_t kHiAtom1024 = ((uint64_t)((1024u >> 4) | (1u << 14) | (2u << 29))) << 32;
-    constexpr uint64_t kHiGroup = ((uint64_t)(((uint32_t)C::GROUP_BYTES >> 4) | (1u << 14) | (2u << 29))) << 32;
-    uint64_t q_desc[NT];
-#pragma unroll
-    for (int x = 0; x < NT; ++x) q_desc[x] = kHiAtom1024 | (uint64_t)(((sb + C::OFF_Q + x * C::Q_BYTES) >> 4) | (1u << 16));
-    const uint64_t k_desc0 = kHiGroup | (uint64_t)(((sb + C::OFF_KV) >> 4) | (1u << 16));
-    // V is MN-major: leading byte offset = distance between 64-element chunks of D (1024 B)
-    const uint64_t v_desc0 = kHiGroup | (uint64_t)(((sb + C::OFF_KV + C::V_OFF) >> 4) | ((1024u >> 4) << 16));
-
-    // Consecutive tcgen05.mma that accumulate into the same TMEM tile serialise on the accumulator,
-    // so the two tiles' MMAs are issued alternately: every instruction is independent of the one
-    // before it.  The whole role runs on lane 0: its scalar work between MMAs is on the critical
-    // path of every stage, so it is kept to a few instructions (no warp votes, flags ride in the
-    // stage metadata instead of being re-derived from the item descriptor).
+  } else if (warp == 1 || warp >= 2 + C::SM_WARPS * NT) {
+    // =============================== MMA issuers ===============================
+    // Four single-thread roles: S and P.V of each tile are issued by different warps.  An issuing
+    // thread spends most of a stage on latency (an mbarrier poll or a shared-memory read costs it
+    // 100+ cycles while the tensor pipe and the TMA unit stream through shared memory, a
+    // tcgen05.mma 50-150), so one thread issuing S and P.V for a tile, or worse for both tiles,
+    // becomes the bottleneck of the whole CTA.  No ordering between the roles is needed beyond the
+    // barriers: S_x(t+1) only needs the S columns back (s_free), P_x.V(t) only P_x(t) (p_full).
     if (lane == 0) {
-      // S_x = Q_x . K^T of stage `st` into S buffer tcount[x] & 1, for every tile in `act`.  That
-      // buffer last held P of stage tcount[x]-2, which P.V of that stage -- issued earlier, and MMAs
-      // execute in issue order -- has finished reading by the time this MMA writes.
-      auto issue_s = [&](const bool (&act)[NT], int st) {
-        tc_fence_after();
-        const uint64_t kd = k_desc0 + (uint64_t)((st * C::STAGE_BYTES) >> 4);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          // K: 8-token atoms one group apart (SBO), the 64-element chunks of D 1024 bytes apart
-          const uint64_t bd = kd + (uint64_t)(((kk >> 2) * 1024 + (kk & 3) * 32) >> 4);
-#pragma unroll
-          for (int x = 0; x < NT; ++x) {
-            if (!act[x]) continue;
-            const uint64_t ad = q_desc[x] + (uint64_t)(((kk >> 2) * (kBM * 128) + (kk & 3) * 32) >> 4);
-            tc_mma(tmem_base + C::TMEM_S + (x * 2 + (tcount[x] & 1)) * kBN, ad, bd, idesc_s, kk > 0);
-          }
-        }
-#pragma unroll
-        for (int x = 0; x < NT; ++x)
-          if (act[x]) tc_commit(bar_s_full(x, tcount[x] & 1));
-      };
-      // O_x (+)= P_x . V of the previous stage, for every tile that took part in it; P_x sits in TMEM
-      auto issue_pv = [&]() -> bool {
-#pragma unroll
-        for (int x = 0; x < NT; ++x) {
-          if (!prev_act[x]) continue;
-          const int t = prev_t[x];
-          if (!mbar_wait_thread(bar_p_full(x, t & 1), (t >> 1) & 1, abort_flag, wait_ns)) return false;
-        }
-        tc_fence_after();
-        const uint64_t vd = v_desc0 + (uint64_t)((prev_st * C::STAGE_BYTES) >> 4);
-#pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk) {
-          // V: 16 tokens = two 8-token groups per MMA
-          const uint64_t bd = vd + (uint64_t)((kk * 2 * C::GROUP_BYTES) >> 4);
-#pragma unroll
-          for (int x = 0; x < NT; ++x) {
-            if (!prev_act[x]) continue;
-            // P: 16 tokens = 8 columns of bf16 pairs
-            const uint32_t a_tmem = tmem_base + C::TMEM_S + (x * 2 + (prev_t[x] & 1)) * kBN + kk * 8;
-            tc_mma_ts(tmem_base + C::TMEM_O + x * D, a_tmem, bd, idesc_pv, !(prev_first && kk == 0));
-          }
-        }
-#pragma unroll
-        for (int x = 0; x < NT; ++x)
-          if (prev_act[x]) tc_commit(bar_pv_done(x, prev_t[x] & 1));  // O_x holds this stage
-        tc_commit(bar_kv_empty(prev_st));  // every MMA that read this KV stage is complete
-        have_prev = false;
-        return true;
-      };
+      // roles in the order S_0 .. S_{NT-1}, PV_0 .. PV_{NT-1}; S_0 is warp 1, the others follow the softmax warps
+      const int role = (warp == 1) ? 0 : warp - (2 + C::SM_WARPS * NT) + 1;
+      const bool is_s = role < NT;
+      const int x = is_s ? role : role - NT;
+      constexpr uint32_t idesc_s = instr_desc<T>(kBN, false);
+      constexpr uint32_t idesc_pv = instr_desc<T>(D, true);
+      // hi word of a descriptor: stride byte offset >> 4, version 1 (bit 46), SWIZZLE_128B (bits 61-63)
+      constexpr uint64_t kHiAtom1024 = ((uint64_t)((1024u >> 4) | (1u << 14) | (2u << 29))) << 32;
+      constexpr uint64_t kHiGroup = ((uint64_t)(((uint32_t)C::GROUP_BYTES >> 4) | (1u << 14) | (2u << 29))) << 32;
+      const uint64_t q_desc = kHiAtom1024 | (uint64_t)(((sb + C::OFF_Q + x * C::Q_BYTES) >> 4) | (1u << 16));
+      const uint64_t k_desc0 = kHiGroup | (uint64_t)(((sb + C::OFF_KV) >> 4) | (1u << 16));
+      // V is MN-major: leading byte offset = distance between 64-element chunks of D (1024 B)
+      const uint64_t v_desc0 = kHiGroup | (uint64_t)(((sb + C::OFF_KV + C::V_OFF) >> 4) | ((1024u >> 4) << 16));
+      const uint32_t tm_s = tmem_base + C::TMEM_S + x * kBN;
+      const uint32_t tm_p = tmem_base + C::TMEM_P + x * 2 * C::P_COLS;
+      const uint32_t tm_o = tmem_base + C::TMEM_O + x * D;
 
-      while (ok) {
+      int gi = 0;     // KV stage counter (every role sees the same stage sequence)
+      int t = 0;      // stages this tile took part in (barrier parities)
+      int items = 0;  // items this tile took part in
+      int skips = 0;  // items this tile had no rows for
+      while (true) {
         const int st = gi % NS;
         if (!mbar_wait_thread(bar_kv_full(st), (gi / NS) & 1, abort_flag, wait_ns)) break;
         const int mx = metas[st].x;
-        if (mx < 0) {
-          if (have_prev) issue_pv();
-          break;
-        }
+        if (mx < 0) break;
         const bool first = (mx & 0x100) != 0;
-        bool act[NT];
-        act[0] = true;
-        if (NT == 2) act[NT - 1] = (mx & 0x200) != 0;
-        if (!first) {
-          // steady state: S of this stage goes to the tensor pipe before P.V of the previous one, so
-          // the pipe has work while the softmax warps exponentiate
-          issue_s(act, st);
-          if (have_prev) ok = issue_pv();
-        } else {
-          // item boundary: finish the previous item first -- its epilogue must read O before this
-          // item's query tiles are loaded and before the first P.V of this item overwrites O
-          if (have_prev) ok = issue_pv();
-#pragma unroll
-          for (int x = 0; x < NT; ++x) {
-            if (!ok || !act[x]) continue;
-            ok = mbar_wait_thread(bar_q_full(x), items[x] & 1, abort_flag, wait_ns);
-            if (ok && items[x] > 0) ok = mbar_wait_thread(bar_o_free(x), (items[x] - 1) & 1, abort_flag, wait_ns);
-            ++items[x];
+        const bool act = (x == 0) || (mx & 0x200) != 0;
+        if (!act) {  // the item has no rows for this tile: only this role's share of the stage's release
+          if (first && is_s) {
+            // ... once the tile's softmax group has seen the item, so that it never falls behind
+            if (!mbar_wait_thread(bar_skip(x), skips & 1, abort_flag, wait_ns)) break;
+            ++skips;
           }
-          if (ok) issue_s(act, st);
+          mbar_arrive(bar_kv_empty(st));
+          ++gi;
+          continue;
         }
-        if (!ok) break;
-        have_prev = true;
-        prev_st = st;
-        prev_first = first;
+        if (first) ++items;
+        if (is_s) {
+          // the new query tile must be in shared memory, and S_x of the previous stage in the
+          // softmax warps' registers
+          if (first && !mbar_wait_thread(bar_q_full(x), (items - 1) & 1, abort_flag, wait_ns)) break;
+          if (t > 0 && !mbar_wait_thread(bar_s_free(x), (t - 1) & 1, abort_flag, wait_ns)) break;
+          tc_fence_after();
+          const uint64_t kd = k_desc0 + (uint64_t)((st * C::STAGE_BYTES) >> 4);
 #pragma unroll
-        for (int x = 0; x < NT; ++x) {
-          prev_act[x] = act[x];
-          prev_t[x] = tcount[x];
-          if (act[x]) ++tcount[x];
+          for (int kk = 0; kk < D / 16; ++kk) {
+            // K: 8-token atoms one group apart (SBO), the 64-element chunks of D 1024 bytes apart
+            const uint32_t koff = (uint32_t)(((kk >> 2) * 1024 + (kk & 3) * 32) >> 4);
+            const uint32_t qoff = (uint32_t)(((kk >> 2) * (kBM * 128) + (kk & 3) * 32) >> 4);
+            tc_mma(tm_s, q_desc + qoff, kd + koff, idesc_s, kk > 0);
+          }
+          tc_commit(bar_s_full(x));
+        } else {
+          // O_x (+)= P_x . V: P_x(t) must be in its TMEM buffer; the first P.V of an item overwrites
+          // O_x, which the previous item's epilogue must have read
+          if (!mbar_wait_thread(bar_p_full(x, t & 1), (t >> 1) & 1, abort_flag, wait_ns)) break;
+          if (first && items > 1 && !mbar_wait_thread(bar_o_free(x), items & 1, abort_flag, wait_ns)) break;
+          tc_fence_after();
+          const uint64_t vd = v_desc0 + (uint64_t)((st * C::STAGE_BYTES) >> 4);
+#pragma unroll
+          for (int kk = 0; kk < kBN / 16; ++kk) {
+            // V: 16 tokens = two 8-token groups per MMA; P: 16 tokens = 8 columns of 16-bit pairs
+            tc_mma_ts(tm_o, tm_p + (t & 1) * C::P_COLS + kk * 8, vd + (uint64_t)((kk * 2 * C::GROUP_BYTES) >> 4), idesc_pv,
+                      !(first && kk == 0));
+          }
+          tc_commit(bar_pv_done(x, t & 1));
         }
+        tc_commit(bar_kv_empty(st));  // this role's MMAs that read the stage have been issued
+        ++t;
         ++gi;
       }
     }
     __syncwarp();
   } else {
     // =============================== softmax warps ===============================
-    const int x = (warp - 2) >> 2;                        // which tile of the CTA
+    // One thread per tile row: warp (x, quarter) owns rows quarter*32.. of tile x (the TMEM lanes a
+    // warp may touch are fixed by warp % 4), so row maxima and sums need no shuffles.
+    constexpr int HB = kBN;
+    const int sw = warp - 2;
+    const int x = sw / C::SM_WARPS;                       // which tile of the CTA
     const int row = (warp & 3) * 32 + lane;               // TMEM lane == row within the tile
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const int grp_tid = (tid - 64) & 127;                 // 0..127 within the softmax group
-    const bool grp_leader = (grp_tid == 0);
-    const uint32_t tm_s = tmem_base + lane_addr + C::TMEM_S + x * 2 * kBN;
+    const int grp_tid = (sw % C::SM_WARPS) * 32 + lane;   // index within the tile's softmax group
+    const uint32_t tm_s = tmem_base + lane_addr + C::TMEM_S + x * kBN;
+    const uint32_t tm_p0 = tmem_base + lane_addr + C::TMEM_P + x * 2 * C::P_COLS;
     const uint32_t tm_o = tmem_base + lane_addr + C::TMEM_O + x * D;
     uint8_t* q_smem = smem + C::OFF_Q + x * C::Q_BYTES;
     int gi = 0;   // KV stage counter (all roles see the same stage sequence)
     int ti = 0;   // stages this tile took part in
-    float m_run = -INFINITY, l_run = 0.f;
-    int pos_row = -1, lo_row = -1;
-    bool row_ok = false, active = false;
-    int out_row_q = 0, out_head = 0;
-    Unit u;
-    u.kv_begin = u.kv_end = 0;
-    int h = 0;
-    while (true) {
-      const int st = gi % NS;
-      if (!mbar_wait(bar_kv_full(st), (gi / NS) & 1, abort_flag, wait_ns)) break;
-      const int2 meta = metas[st];
-      if (meta.x < 0) break;
-      const int pos = meta.y;
-      const bool first = (meta.x & 0x100) != 0;
-      if (first) {
-        u = ring[meta.x & 0xff].u;
-        h = ring[meta.x & 0xff].h;
-        active = (x == 0) || (meta.x & 0x200) != 0;
+    int k = 0;    // item counter (all roles see the same item sequence)
+    int pc = 0;   // stages in which both tiles took part (the tiles take turns at the exponentials)
+    bool alive = true;
+    // The group follows the item sequence through the producer's item ring (a counter says how many
+    // items have been published; an mbarrier parity could alias, because a group whose tile is idle
+    // skips whole items) and counts stages itself, so that per stage it waits only for S.
+    while (alive) {
+      {
+        bool have = *items_pub > k;
+        if (!have) {
+          const unsigned long long t0 = global_timer_ns();
+          while (true) {
+            __nanosleep(64);
+            if (*items_pub > k) {
+              have = true;
+              break;
+            }
+            if (*abort_flag || global_timer_ns() - t0 > wait_ns) break;
+          }
+        }
+        have = __all_sync(0xffffffffu, have);
+        if (!have) {
+          *abort_flag = 1;
+          break;
+        }
       }
-      // this group has read the stage's metadata: its share of the stage's release
-      if (grp_leader) mbar_arrive(bar_kv_empty(st));
+      const Unit u = ring[k % kRingP].u;
+      const int h = ring[k % kRingP].h;
+      ++k;
+      if (u.seq < 0) break;
+      int n_stages = (u.kv_end - u.kv_begin + kBN - 1) / kBN;
+      if (n_stages < 1) n_stages = 1;
+      const bool two = NT == 2 && u.q_len * G > u.row0 + kBM;  // the item has rows for both tiles
+      const bool active = (x == 0) || two;
       if (!active) {  // the item has no rows for this tile
-        ++gi;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_skip(x));
+        gi += n_stages;
         continue;
       }
-      if (first) {
-        // ---- new item: row bookkeeping and the query tile (K-major, 128B swizzle) ----
-        const int rows_total = u.q_len * G;
-        const int R = u.row0 + x * kBM + row;
-        row_ok = R < rows_total;
-        const int qt = R / G, g = R - qt * G;
-        out_row_q = u.q_start + qt;
-        out_head = h * G + g;
-        pos_row = row_ok ? (u.kv_len - u.q_len + qt) : -1;
-        lo_row = (p.window > 0) ? pos_row - p.window : -1;
-        m_run = -INFINITY;
-        l_run = 0.f;
+      // ---- new item: row bookkeeping and the query row (K-major, 128B swizzle) ----
+      const int rows_total = u.q_len * G;
+      const int R = u.row0 + x * kBM + row;
+      const bool row_ok = R < rows_total;
+      const int qt = R / G, g = R - qt * G;
+      const int out_row_q = u.q_start + qt;
+      const int out_head = h * G + g;
+      const int pos_row = row_ok ? (u.kv_len - u.q_len + qt) : -1;
+      const int lo_row = (p.window > 0) ? pos_row - p.window : -1;
+      float m_run = -INFINITY, l_run = 0.f;
+      {
         // all S MMAs of this tile's previous item completed before its last s_full fired, which
         // this thread waited for, so the query tile may be overwritten
         const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) +
@@ -445,66 +433,70 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_q_full(x));
       }
-      const int b = ti & 1;
-      if (!mbar_wait(bar_s_full(x, b), (ti >> 1) & 1, abort_flag, wait_ns)) break;
+     for (int js = 0; js < n_stages; ++js, ++gi, ++ti) {
+      const int st = gi % NS;
+      const int pos = u.kv_begin + js * kBN;  // first key of the stage
+      const bool first = (js == 0);
+      if (!mbar_wait(bar_s_full(x), ti & 1, abort_flag, wait_ns)) { alive = false; break; }
       tc_fence_after();
-      uint32_t sr[2][32];
-      tc_ld32(tm_s + b * kBN, sr[0]);
-      tc_ld32(tm_s + b * kBN + 32, sr[1]);
-      tc_wait_ld();
 
-      // logits in the log2 domain, soft cap, masks (_xla_impl_fwd.py:125-138).  The common case (no
-      // cap, stage entirely visible to this row) keeps the raw dot products and folds the scale into
-      // the exponent's FMA; everything else materialises the transformed logits first.
-      const bool full_vis = (pos + kBN - 1 <= pos_row) && (pos > lo_row);
+      // ---- the row's logits of the stage into registers; then the S columns are free for the
+      // tile's next S MMA, which runs while this stage's exponentials are computed
+      uint32_t sr[HB];
+#pragma unroll
+      for (int c = 0; c + 32 <= HB; c += 32) tc_ld32(tm_s + c, *reinterpret_cast<uint32_t(*)[32]>(&sr[c]));
+      static_assert(HB % 32 == 0, "S is read 32 columns at a time");
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_s_free(x));
+
+      // ---- logits in the log2 domain, soft cap, masks (_xla_impl_fwd.py:125-138).  The common case
+      // (no cap, columns entirely visible to this row) keeps the raw dot products and folds the scale
+      // into the exponent's FMA; everything else materialises the transformed, masked logits first.
+      const bool full_vis = (pos + HB - 1 <= pos_row) && (pos > lo_row);
       const bool plain = full_vis && p.cap == 0.f;
       float e_scale = p.scale_log2;  // p = exp2(v * e_scale - m)
       float mx;
       if (plain) {
         // max of scale*v is scale*max(v) or scale*min(v) depending on the sign of the scale
-        // (four independent chains: few warps per scheduler, so latency must be hidden in-thread)
         float ext[4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a) ext[a] = __uint_as_float(sr[0][a]);
+        for (int a = 0; a < 4; ++a) ext[a] = __uint_as_float(sr[a]);
         if (p.scale_log2 >= 0.f) {
 #pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf)
+          for (int i = 0; i < HB; i += 8)
 #pragma unroll
-            for (int c = 0; c < 32; ++c) ext[c & 3] = fmaxf(ext[c & 3], __uint_as_float(sr[hlf][c]));
+            for (int a = 0; a < 4; ++a)
+              ext[a] = fmax3(ext[a], __uint_as_float(sr[i + 2 * a]), __uint_as_float(sr[i + 2 * a + 1]));
           mx = fmaxf(fmaxf(ext[0], ext[1]), fmaxf(ext[2], ext[3])) * p.scale_log2;
         } else {
 #pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf)
+          for (int i = 0; i < HB; i += 8)
 #pragma unroll
-            for (int c = 0; c < 32; ++c) ext[c & 3] = fminf(ext[c & 3], __uint_as_float(sr[hlf][c]));
+            for (int a = 0; a < 4; ++a)
+              ext[a] = fmin3(ext[a], __uint_as_float(sr[i + 2 * a]), __uint_as_float(sr[i + 2 * a + 1]));
           mx = fminf(fminf(ext[0], ext[1]), fminf(ext[2], ext[3])) * p.scale_log2;
         }
       } else {
         mx = -INFINITY;
         e_scale = 1.f;
-        if (p.cap != 0.f) {
 #pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf)
-#pragma unroll
-            for (int c = 0; c < 32; ++c)
-              sr[hlf][c] = __float_as_uint(p.cap_log2 * soft_cap_tanh(__uint_as_float(sr[hlf][c]) * p.inv_cap_scale));
-        } else {
-#pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf)
-#pragma unroll
-            for (int c = 0; c < 32; ++c) sr[hlf][c] = __float_as_uint(__uint_as_float(sr[hlf][c]) * p.scale_log2);
+        for (int i = 0; i < HB; ++i) {
+          float xv = __uint_as_float(sr[i]);
+          xv = (p.cap != 0.f) ? p.cap_log2 * soft_cap_tanh(xv * p.inv_cap_scale) : xv * p.scale_log2;
+          const int key = pos + i;
+          if (!full_vis && (key > pos_row || key <= lo_row)) xv = -INFINITY;
+          sr[i] = __float_as_uint(xv);
+          mx = fmaxf(mx, xv);
         }
-#pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf)
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            float xv = __uint_as_float(sr[hlf][c]);
-            const int key = pos + hlf * 32 + c;
-            if (!full_vis && (key > pos_row || key <= lo_row)) xv = -INFINITY;
-            sr[hlf][c] = __float_as_uint(xv);
-            mx = fmaxf(mx, xv);
-          }
       }
+      // P_x has two buffers: this stage's goes where the stage before the previous one's was, whose
+      // P.V must have read it (it has, normally long ago)
+      if (ti >= 2) {
+        if (!mbar_wait(bar_pv_done(x, ti & 1), ((ti - 2) >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
+      }
+      const uint32_t tm_p = tm_p0 + (ti & 1) * C::P_COLS;
       const bool grow = (mx > m_run + kLazyP) || (m_run == -INFINITY && mx > -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
         float alpha = 1.f;
@@ -514,65 +506,81 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           l_run *= alpha;
         }
         if (!first) {
-          // O holds the sum over the earlier stages of this item: rescale this warp's 32 lanes.
-          // This tile's P.V of stage ti-1 must have completed first.
-          if (!mbar_wait(bar_pv_done(x, (ti - 1) & 1), ((ti - 1) >> 1) & 1, abort_flag, wait_ns)) break;
+          // O holds the sum over the earlier stages of this item: rescale the row, once the tile's
+          // previous P.V has completed (O is only touched between P.Vs)
+          if (!mbar_wait(bar_pv_done(x, (ti - 1) & 1), ((ti - 1) >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
           tc_fence_after();
 #pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t o[32];
-            tc_ld32(tm_o + c0, o);
+          for (int c0 = 0; c0 < D; c0 += 16) {
+            uint32_t o[16];
+            tc_ld16(tm_o + c0, o);
             tc_wait_ld();
 #pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-            tc_st32(tm_o + c0, o);
+            for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+            tc_st16(tm_o + c0, o);
           }
-          tc_wait_st();
-          tc_fence_before();
         }
       }
-      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      // probabilities, packed as bf16 pairs, go back into the TMEM columns S came from
-      float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int c = 2 * j;
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), e_scale, -m_use));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), e_scale, -m_use));
-        lsum4[j & 3] += p0 + p1;
-        pk[j] = Mma<T>::pack(p0, p1);
+      // The MUFU unit gives 4 exponentials per cycle and scheduler, and both tiles' warps sit on the
+      // same schedulers: when both tiles are at work they take turns at the exponentials (tile 0
+      // first), so that one tile's waits and TMEM traffic overlap the other's MUFU phase instead of
+      // both phases running in lockstep at half speed.
+      if (two) {
+        const bool my_turn_ok = (x == 0) ? (pc == 0 || mbar_wait(bar_turn(1), (pc - 1) & 1, abort_flag, wait_ns))
+                                         : mbar_wait(bar_turn(0), pc & 1, abort_flag, wait_ns);
+        if (!my_turn_ok) { alive = false; break; }
       }
-      tc_st32(tm_s + b * kBN, pk);
+      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+      // probabilities, packed as 16-bit pairs, into the tile's P buffer of this stage
+      float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < HB; c += 32) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c + 2 * j]), e_scale, -m_use));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 2 * j + 1]), e_scale, -m_use));
+          lsum4[j & 3] += p0 + p1;
+          pk[j] = Mma<T>::pack(p0, p1);
+        }
+        tc_st16(tm_p + (c >> 1), pk);
+      }
       l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
-      if (x == 0 && pos + kBN > u.kv_end) {
+      if (two) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_turn(x));
+        ++pc;
+      }
+      const bool tail = pos + kBN > u.kv_end;
+      if (tail) {
         // Tail stage: V rows of keys >= kv_end were either never fetched (stale shared memory) or lie
         // past the sequence's length inside its last page (unowned, possibly NaN).  Their
-        // probabilities are exactly 0, but 0 * NaN would poison O, so tile 0's group clears the rows
-        // before any tensor-core read: the MMA warp issues tile 1's P.V only after it has seen tile
-        // 0's p_full.  (Zero rows are invariant under the swizzle.)
+        // probabilities are exactly 0, but 0 * NaN would poison O, so every group clears the rows
+        // before its own tile's P.V can be issued (the two groups write the same zeros; zero rows are
+        // invariant under the swizzle).
         int nvalid = u.kv_end - pos;
         if (nvalid < 0) nvalid = 0;
         uint8_t* vbase = smem + C::OFF_KV + st * C::STAGE_BYTES + C::V_OFF;
         const int n16 = (kBN - nvalid) * DC * 8;
-        for (int idx = grp_tid; idx < n16; idx += 128) {
+        for (int idx = grp_tid; idx < n16; idx += 32 * C::SM_WARPS) {
           const int t = nvalid + idx / (DC * 8);
           const int rem = idx % (DC * 8);
           *reinterpret_cast<uint4*>(vbase + (t >> 3) * C::GROUP_BYTES + (rem >> 3) * 1024 + (t & 7) * 128 + (rem & 7) * 16) =
               make_uint4(0u, 0u, 0u, 0u);
         }
+        fence_async_smem();  // the zeroed V rows are read by the async proxy
       }
-      if (x == 0 && pos + kBN > u.kv_end) fence_async_smem();  // the zeroed V rows are read by the async proxy
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full(x, b));
+      if (lane == 0) mbar_arrive(bar_p_full(x, ti & 1));
 
       if (pos + kBN >= u.kv_end) {
-        // ---- last stage of the item: wait for its PV, normalise, store ----
-        if (!mbar_wait(bar_pv_done(x, b), (ti >> 1) & 1, abort_flag, wait_ns)) break;
+        // ---- last stage of the item: wait for its P.V, normalise, store ----
+        const float l_row = l_run;
+        if (!mbar_wait(bar_pv_done(x, ti & 1), (ti >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
         tc_fence_after();
-        float scl = 1.f, l_fin = l_run;
+        float scl = 1.f, l_fin = l_row;
         if (p.num_sinks > 0 && row_ok) {
           // attention sinks join the denominator only (_xla_impl_fwd.py:161-172)
           const int srow = (p.sink_rows == p.Hq) ? out_head : (p.sink_rows == Hkv ? h : 0);
@@ -582,7 +590,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           const float m_fin = fmaxf(m_run, sm);
           const float mf = (m_fin == -INFINITY) ? 0.f : m_fin;
           scl = fast_exp2(m_run - mf);
-          l_fin = l_run * scl;
+          l_fin = l_row * scl;
           for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2eP - mf);
         }
         scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
@@ -608,8 +616,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_o_free(x));
       }
-      ++ti;
-      ++gi;
+     }
     }
   }
   if (*abort_flag) flags |= EJK_RPA_ST_TIMEOUT;
@@ -656,20 +663,20 @@ cudaError_t launch_one(const Params& p, const CUtensorMap& map, int n_sm, cudaSt
   return launch_kernel(kern, dim3(n_sm), dim3(C::THREADS), C::SMEM_BYTES, stream, pdl, map, p);
 }
 
-template <typename T>
-cudaError_t dispatch(const Params& p, const CUtensorMap& map, int n_sm, cudaStream_t stream, bool pdl) {
-  switch (p.D) {
-    case 64: return launch_one<T, 64>(p, map, n_sm, stream, pdl);
-    case 128: return launch_one<T, 128>(p, map, n_sm, stream, pdl);
-    case 256: return launch_one<T, 256>(p, map, n_sm, stream, pdl);
+cudaError_t dispatch(const Params& p, int dtype, const CUtensorMap& map, int n_sm, cudaStream_t stream, bool pdl) {
+  if (dtype == EJK_RPA_BF16) {
+    if (p.D == 64) return launch_one<__nv_bfloat16, 64>(p, map, n_sm, stream, pdl);
+    if (p.D == 128) return launch_one<__nv_bfloat16, 128>(p, map, n_sm, stream, pdl);
+    if (p.D == 256) return launch_one<__nv_bfloat16, 256>(p, map, n_sm, stream, pdl);
+  } else {
+    if (p.D == 64) return launch_one<__half, 64>(p, map, n_sm, stream, pdl);
+    if (p.D == 128) return launch_one<__half, 128>(p, map, n_sm, stream, pdl);
+    if (p.D == 256) return launch_one<__half, 256>(p, map, n_sm, stream, pdl);
   }
   return cudaErrorInvalidValue;
 }
 
 }  // namespace
-
-// rpa_prefill_pp_sm100.cu
-cudaError_t launch_prefill_pingpong(const Params& p, int dtype, const CUtensorMap& map, int n_sm, cudaStream_t stream, bool pdl);
 
 int prefill_rows_per_item(int head_dim) { return head_dim <= 128 ? 2 * kPrefillRows : kPrefillRows; }
 
@@ -694,9 +701,7 @@ cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t st
   CUresult r = enc(&map, dt, 5, const_cast<void*>(p.kv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-  if (p.D <= 128 && p.prefill_kernel == 0) return launch_prefill_pingpong(p, dtype, map, n_sm, stream, pdl);
-  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16>(p, map, n_sm, stream, pdl);
-  return dispatch<__half>(p, map, n_sm, stream, pdl);
+  return dispatch(p, dtype, map, n_sm, stream, pdl);
 }
 
 }  // namespace ejk

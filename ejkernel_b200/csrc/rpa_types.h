@@ -84,7 +84,6 @@ struct Params {
   int32_t max_punits;
   int32_t prefill_item_rows; // rows one prefill work item covers (128 per tile, 1 or 2 tiles per CTA)
   int32_t pdl;               // bit 0: the prefill kernel, bit 1: the split-KV kernel must pdl_wait() before reading the plan
-  int32_t prefill_kernel;    // 0 = widest-stage kernel the head_dim allows, 1 = the 64-token-stage kernel
   int32_t prefill_min_rows;  // sequences with q_len*G >= this go to the prefill-tile kernel; 0 = never
   int32_t window;      // <= 0: none
   int32_t num_sinks, sink_rows;

@@ -185,8 +185,6 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *   "path"       0 = auto, 1 = force the cp.async gather, 2 = force the TMA gather
  *   "prefill_rows" sequences with at least this many (query token, head-in-group) rows per kv head are
  *                served by 128-row tcgen05 tiles instead of 8-row split-KV tiles (default 64; 0 = never)
- *   "prefill_kernel" 0 (default) = prefill tiles run the ping-pong kernel (96/128-token stages) at head_dim <= 128,
- *                1 = always the 64-token-stage kernel (the only one for head_dim 256)
  *   "overlap"    1 (default) = the kernels of one call are launched as programmatic dependents: each starts under
  *                the tail of the one before and waits on the device for what it needs; 0 = plain stream order
  *   "fused_merge" 1 (default) = where a row tile gets few KV chunks (decided from the static shapes) the split-KV

@@ -135,30 +135,25 @@ def test_prefill_threshold_does_not_change_results_beyond_tolerance(rpa_lib):
         _cabi.set_option("prefill_rows", old)
 
 
-@pytest.mark.parametrize("variant", [0, 1])
-def test_both_prefill_tile_kernels(rpa_lib, variant):
-    """The ping-pong kernel (96/128-token stages, head_dim <= 128) and the 64-token-stage kernel serve
-    the same items; both must match the oracle on ragged tiles, windows, caps, sinks, one-tile items
-    and sequences whose length is not a multiple of the stage."""
-    from ejkernel_b200 import _cabi
-    old = _cabi.get_option("prefill_kernel")
-    try:
-        _cabi.set_option("prefill_kernel", variant)
-        b = make_ragged_batch([700, 1, 333, 2, 129], [1500, 40, 333, 900, 4000], num_q_heads=8, num_kv_heads=2,
-                              head_dim=128, page_size=16, seed=71)
-        _check(b, f"variant {variant}: many tiles")
-        b = make_ragged_batch([300, 260, 17], [2100, 300, 97], num_q_heads=16, num_kv_heads=2, head_dim=64,
-                              page_size=32, seed=72, sliding_window=700, logits_soft_cap=40.0)
-        _check(b, f"variant {variant}: window+cap d64")
-        b = make_ragged_batch([96, 33, 64], [96, 1000, 191], num_q_heads=4, num_kv_heads=4, head_dim=128, page_size=8,
-                              seed=73)
-        b.softmax_aux = torch.randn(4, 2, generator=torch.Generator().manual_seed(5))
-        _check(b, f"variant {variant}: g1 sinks page8")
-        b = make_ragged_batch([512, 512], [4096, 513], num_q_heads=32, num_kv_heads=8, head_dim=128, page_size=64,
-                              seed=74, dtype=torch.float16)
-        _check(b, f"variant {variant}: fp16 chunked prefill")
-    finally:
-        _cabi.set_option("prefill_kernel", old)
+def test_prefill_tile_kernel_shapes(rpa_lib):
+    """The tcgen05 tile kernel on ragged tiles, windows, caps, sinks, one-tile items, sequences whose length
+    is not a multiple of the 64-token stage, every head_dim, and fp16."""
+    b = make_ragged_batch([700, 1, 333, 2, 129], [1500, 40, 333, 900, 4000], num_q_heads=8, num_kv_heads=2,
+                          head_dim=128, page_size=16, seed=71)
+    _check(b, "many tiles")
+    b = make_ragged_batch([300, 260, 17], [2100, 300, 97], num_q_heads=16, num_kv_heads=2, head_dim=64,
+                          page_size=32, seed=72, sliding_window=700, logits_soft_cap=40.0)
+    _check(b, "window+cap d64")
+    b = make_ragged_batch([96, 33, 64], [96, 1000, 191], num_q_heads=4, num_kv_heads=4, head_dim=128, page_size=8,
+                          seed=73)
+    b.softmax_aux = torch.randn(4, 2, generator=torch.Generator().manual_seed(5))
+    _check(b, "g1 sinks page8")
+    b = make_ragged_batch([512, 512], [4096, 513], num_q_heads=32, num_kv_heads=8, head_dim=128, page_size=64,
+                          seed=74, dtype=torch.float16)
+    _check(b, "fp16 chunked prefill")
+    b = make_ragged_batch([130, 400, 1], [1000, 450, 77], num_q_heads=8, num_kv_heads=4, head_dim=256, page_size=16,
+                          seed=75, sliding_window=300)
+    _check(b, "d256 one tile per CTA, window")
 
 
 def test_overlapped_launches_equal_stream_order_bitwise(rpa_lib):
