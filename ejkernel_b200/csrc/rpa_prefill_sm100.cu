@@ -68,7 +68,8 @@ struct CfgP {
   static constexpr int BN = 64;
   static constexpr int NT = (D <= 128) ? 2 : 1;       // 128-row tiles per CTA (TMEM holds one 256-column O)
   static constexpr int SM_WARPS = 4;                  // softmax warps per tile: one thread per row
-  static constexpr int THREADS = 64 + 32 * SM_WARPS * NT + 32 * (2 * NT - 1);  // producer, S issuer 0, softmax groups, the other issuers
+  // producer, S issuer of tile 0, softmax groups, the other issuers
+  static constexpr int THREADS = 64 + 32 * SM_WARPS * NT + 32 * (2 * NT - 1);
   static constexpr int STAGE_BYTES = BN * 2 * D * 2;
   static constexpr int NS = (D == 64) ? 8 : (D == 128) ? 4 : 2;
   static constexpr int GROUP_BYTES = 8 * 2 * D * 2;   // one 8-token group: [K|V][D/64][8][64]
@@ -119,8 +120,8 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   auto bar_pv_done = [&](int x, int b) { return tile_bar(x, 4 + b); };  // P_x.V(t) complete (commit): buffer t&1 is free
   auto bar_q_full = [&](int x) { return tile_bar(x, 6); };
   auto bar_o_free = [&](int x) { return tile_bar(x, 7); };
-  auto bar_skip = [&](int x) { return tile_bar(x, 8); };
-  auto bar_turn = [&](int x) { return tile_bar(x, 9); };      // tile x has issued the exponentials of a stage      // the 4 warps have seen an item without rows for tile x
+  auto bar_skip = [&](int x) { return tile_bar(x, 8); };      // the 4 warps have seen an item without rows for tile x
+  auto bar_turn = [&](int x) { return tile_bar(x, 9); };      // tile x has issued the exponentials of a stage
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Hkv = p.Hkv, G = p.G;
@@ -433,190 +434,190 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_q_full(x));
       }
-     for (int js = 0; js < n_stages; ++js, ++gi, ++ti) {
-      const int st = gi % NS;
-      const int pos = u.kv_begin + js * kBN;  // first key of the stage
-      const bool first = (js == 0);
-      if (!mbar_wait(bar_s_full(x), ti & 1, abort_flag, wait_ns)) { alive = false; break; }
-      tc_fence_after();
+      for (int js = 0; js < n_stages; ++js, ++gi, ++ti) {
+        const int st = gi % NS;
+        const int pos = u.kv_begin + js * kBN;  // first key of the stage
+        const bool first = (js == 0);
+        if (!mbar_wait(bar_s_full(x), ti & 1, abort_flag, wait_ns)) { alive = false; break; }
+        tc_fence_after();
 
-      // ---- the row's logits of the stage into registers; then the S columns are free for the
-      // tile's next S MMA, which runs while this stage's exponentials are computed
-      uint32_t sr[HB];
-#pragma unroll
-      for (int c = 0; c + 32 <= HB; c += 32) tc_ld32(tm_s + c, *reinterpret_cast<uint32_t(*)[32]>(&sr[c]));
-      static_assert(HB % 32 == 0, "S is read 32 columns at a time");
-      tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_s_free(x));
+        // ---- the row's logits of the stage into registers; then the S columns are free for the
+        // tile's next S MMA, which runs while this stage's exponentials are computed
+        uint32_t sr[HB];
+  #pragma unroll
+        for (int c = 0; c + 32 <= HB; c += 32) tc_ld32(tm_s + c, *reinterpret_cast<uint32_t(*)[32]>(&sr[c]));
+        static_assert(HB % 32 == 0, "S is read 32 columns at a time");
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_s_free(x));
 
-      // ---- logits in the log2 domain, soft cap, masks (_xla_impl_fwd.py:125-138).  The common case
-      // (no cap, columns entirely visible to this row) keeps the raw dot products and folds the scale
-      // into the exponent's FMA; everything else materialises the transformed, masked logits first.
-      const bool full_vis = (pos + HB - 1 <= pos_row) && (pos > lo_row);
-      const bool plain = full_vis && p.cap == 0.f;
-      float e_scale = p.scale_log2;  // p = exp2(v * e_scale - m)
-      float mx;
-      if (plain) {
-        // max of scale*v is scale*max(v) or scale*min(v) depending on the sign of the scale
-        float ext[4];
-#pragma unroll
-        for (int a = 0; a < 4; ++a) ext[a] = __uint_as_float(sr[a]);
-        if (p.scale_log2 >= 0.f) {
-#pragma unroll
-          for (int i = 0; i < HB; i += 8)
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-              ext[a] = fmax3(ext[a], __uint_as_float(sr[i + 2 * a]), __uint_as_float(sr[i + 2 * a + 1]));
-          mx = fmaxf(fmaxf(ext[0], ext[1]), fmaxf(ext[2], ext[3])) * p.scale_log2;
+        // ---- logits in the log2 domain, soft cap, masks (_xla_impl_fwd.py:125-138).  The common case
+        // (no cap, columns entirely visible to this row) keeps the raw dot products and folds the scale
+        // into the exponent's FMA; everything else materialises the transformed, masked logits first.
+        const bool full_vis = (pos + HB - 1 <= pos_row) && (pos > lo_row);
+        const bool plain = full_vis && p.cap == 0.f;
+        float e_scale = p.scale_log2;  // p = exp2(v * e_scale - m)
+        float mx;
+        if (plain) {
+          // max of scale*v is scale*max(v) or scale*min(v) depending on the sign of the scale
+          float ext[4];
+  #pragma unroll
+          for (int a = 0; a < 4; ++a) ext[a] = __uint_as_float(sr[a]);
+          if (p.scale_log2 >= 0.f) {
+  #pragma unroll
+            for (int i = 0; i < HB; i += 8)
+  #pragma unroll
+              for (int a = 0; a < 4; ++a)
+                ext[a] = fmax3(ext[a], __uint_as_float(sr[i + 2 * a]), __uint_as_float(sr[i + 2 * a + 1]));
+            mx = fmaxf(fmaxf(ext[0], ext[1]), fmaxf(ext[2], ext[3])) * p.scale_log2;
+          } else {
+  #pragma unroll
+            for (int i = 0; i < HB; i += 8)
+  #pragma unroll
+              for (int a = 0; a < 4; ++a)
+                ext[a] = fmin3(ext[a], __uint_as_float(sr[i + 2 * a]), __uint_as_float(sr[i + 2 * a + 1]));
+            mx = fminf(fminf(ext[0], ext[1]), fminf(ext[2], ext[3])) * p.scale_log2;
+          }
         } else {
-#pragma unroll
-          for (int i = 0; i < HB; i += 8)
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-              ext[a] = fmin3(ext[a], __uint_as_float(sr[i + 2 * a]), __uint_as_float(sr[i + 2 * a + 1]));
-          mx = fminf(fminf(ext[0], ext[1]), fminf(ext[2], ext[3])) * p.scale_log2;
-        }
-      } else {
-        mx = -INFINITY;
-        e_scale = 1.f;
-#pragma unroll
-        for (int i = 0; i < HB; ++i) {
-          float xv = __uint_as_float(sr[i]);
-          xv = (p.cap != 0.f) ? p.cap_log2 * soft_cap_tanh(xv * p.inv_cap_scale) : xv * p.scale_log2;
-          const int key = pos + i;
-          if (!full_vis && (key > pos_row || key <= lo_row)) xv = -INFINITY;
-          sr[i] = __float_as_uint(xv);
-          mx = fmaxf(mx, xv);
-        }
-      }
-      // P_x has two buffers: this stage's goes where the stage before the previous one's was, whose
-      // P.V must have read it (it has, normally long ago)
-      if (ti >= 2) {
-        if (!mbar_wait(bar_pv_done(x, ti & 1), ((ti - 2) >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
-      }
-      const uint32_t tm_p = tm_p0 + (ti & 1) * C::P_COLS;
-      const bool grow = (mx > m_run + kLazyP) || (m_run == -INFINITY && mx > -INFINITY);
-      if (__any_sync(0xffffffffu, grow)) {
-        float alpha = 1.f;
-        if (grow) {
-          alpha = fast_exp2(m_run - mx);  // 0 on the first finite maximum
-          m_run = mx;
-          l_run *= alpha;
-        }
-        if (!first) {
-          // O holds the sum over the earlier stages of this item: rescale the row, once the tile's
-          // previous P.V has completed (O is only touched between P.Vs)
-          if (!mbar_wait(bar_pv_done(x, (ti - 1) & 1), ((ti - 1) >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
-          tc_fence_after();
-#pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 16) {
-            uint32_t o[16];
-            tc_ld16(tm_o + c0, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-            tc_st16(tm_o + c0, o);
+          mx = -INFINITY;
+          e_scale = 1.f;
+  #pragma unroll
+          for (int i = 0; i < HB; ++i) {
+            float xv = __uint_as_float(sr[i]);
+            xv = (p.cap != 0.f) ? p.cap_log2 * soft_cap_tanh(xv * p.inv_cap_scale) : xv * p.scale_log2;
+            const int key = pos + i;
+            if (!full_vis && (key > pos_row || key <= lo_row)) xv = -INFINITY;
+            sr[i] = __float_as_uint(xv);
+            mx = fmaxf(mx, xv);
           }
         }
-      }
-      // The MUFU unit gives 4 exponentials per cycle and scheduler, and both tiles' warps sit on the
-      // same schedulers: when both tiles are at work they take turns at the exponentials (tile 0
-      // first), so that one tile's waits and TMEM traffic overlap the other's MUFU phase instead of
-      // both phases running in lockstep at half speed.
-      if (two) {
-        const bool my_turn_ok = (x == 0) ? (pc == 0 || mbar_wait(bar_turn(1), (pc - 1) & 1, abort_flag, wait_ns))
-                                         : mbar_wait(bar_turn(0), pc & 1, abort_flag, wait_ns);
-        if (!my_turn_ok) { alive = false; break; }
-      }
-      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      // probabilities, packed as 16-bit pairs, into the tile's P buffer of this stage
-      float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < HB; c += 32) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c + 2 * j]), e_scale, -m_use));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 2 * j + 1]), e_scale, -m_use));
-          lsum4[j & 3] += p0 + p1;
-          pk[j] = Mma<T>::pack(p0, p1);
+        // P_x has two buffers: this stage's goes where the stage before the previous one's was, whose
+        // P.V must have read it (it has, normally long ago)
+        if (ti >= 2) {
+          if (!mbar_wait(bar_pv_done(x, ti & 1), ((ti - 2) >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
         }
-        tc_st16(tm_p + (c >> 1), pk);
-      }
-      l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
-      if (two) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_turn(x));
-        ++pc;
-      }
-      const bool tail = pos + kBN > u.kv_end;
-      if (tail) {
-        // Tail stage: V rows of keys >= kv_end were either never fetched (stale shared memory) or lie
-        // past the sequence's length inside its last page (unowned, possibly NaN).  Their
-        // probabilities are exactly 0, but 0 * NaN would poison O, so every group clears the rows
-        // before its own tile's P.V can be issued (the two groups write the same zeros; zero rows are
-        // invariant under the swizzle).
-        int nvalid = u.kv_end - pos;
-        if (nvalid < 0) nvalid = 0;
-        uint8_t* vbase = smem + C::OFF_KV + st * C::STAGE_BYTES + C::V_OFF;
-        const int n16 = (kBN - nvalid) * DC * 8;
-        for (int idx = grp_tid; idx < n16; idx += 32 * C::SM_WARPS) {
-          const int t = nvalid + idx / (DC * 8);
-          const int rem = idx % (DC * 8);
-          *reinterpret_cast<uint4*>(vbase + (t >> 3) * C::GROUP_BYTES + (rem >> 3) * 1024 + (t & 7) * 128 + (rem & 7) * 16) =
-              make_uint4(0u, 0u, 0u, 0u);
-        }
-        fence_async_smem();  // the zeroed V rows are read by the async proxy
-      }
-      tc_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p_full(x, ti & 1));
-
-      if (pos + kBN >= u.kv_end) {
-        // ---- last stage of the item: wait for its P.V, normalise, store ----
-        const float l_row = l_run;
-        if (!mbar_wait(bar_pv_done(x, ti & 1), (ti >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
-        tc_fence_after();
-        float scl = 1.f, l_fin = l_row;
-        if (p.num_sinks > 0 && row_ok) {
-          // attention sinks join the denominator only (_xla_impl_fwd.py:161-172)
-          const int srow = (p.sink_rows == p.Hq) ? out_head : (p.sink_rows == Hkv ? h : 0);
-          const float* sk = p.sinks + (size_t)srow * p.num_sinks;
-          float sm = -INFINITY;
-          for (int i = 0; i < p.num_sinks; ++i) sm = fmaxf(sm, sk[i] * kLog2eP);
-          const float m_fin = fmaxf(m_run, sm);
-          const float mf = (m_fin == -INFINITY) ? 0.f : m_fin;
-          scl = fast_exp2(m_run - mf);
-          l_fin = l_row * scl;
-          for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2eP - mf);
-        }
-        scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
-        T* orow = reinterpret_cast<T*>(p.out) + ((size_t)out_row_q * p.Hq + out_head) * D;
-#pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t o[32];
-          tc_ld32(tm_o + c0, o);
-          tc_wait_ld();
-          if (row_ok) {
-#pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-              uint4 v;
-              v.x = Mma<T>::pack(__uint_as_float(o[c]) * scl, __uint_as_float(o[c + 1]) * scl);
-              v.y = Mma<T>::pack(__uint_as_float(o[c + 2]) * scl, __uint_as_float(o[c + 3]) * scl);
-              v.z = Mma<T>::pack(__uint_as_float(o[c + 4]) * scl, __uint_as_float(o[c + 5]) * scl);
-              v.w = Mma<T>::pack(__uint_as_float(o[c + 6]) * scl, __uint_as_float(o[c + 7]) * scl);
-              *reinterpret_cast<uint4*>(orow + c0 + c) = v;
+        const uint32_t tm_p = tm_p0 + (ti & 1) * C::P_COLS;
+        const bool grow = (mx > m_run + kLazyP) || (m_run == -INFINITY && mx > -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          float alpha = 1.f;
+          if (grow) {
+            alpha = fast_exp2(m_run - mx);  // 0 on the first finite maximum
+            m_run = mx;
+            l_run *= alpha;
+          }
+          if (!first) {
+            // O holds the sum over the earlier stages of this item: rescale the row, once the tile's
+            // previous P.V has completed (O is only touched between P.Vs)
+            if (!mbar_wait(bar_pv_done(x, (ti - 1) & 1), ((ti - 1) >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
+            tc_fence_after();
+  #pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 16) {
+              uint32_t o[16];
+              tc_ld16(tm_o + c0, o);
+              tc_wait_ld();
+  #pragma unroll
+              for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+              tc_st16(tm_o + c0, o);
             }
           }
         }
+        // The MUFU unit gives 4 exponentials per cycle and scheduler, and both tiles' warps sit on the
+        // same schedulers: when both tiles are at work they take turns at the exponentials (tile 0
+        // first), so that one tile's waits and TMEM traffic overlap the other's MUFU phase instead of
+        // both phases running in lockstep at half speed.
+        if (two) {
+          const bool my_turn_ok = (x == 0) ? (pc == 0 || mbar_wait(bar_turn(1), (pc - 1) & 1, abort_flag, wait_ns))
+                                           : mbar_wait(bar_turn(0), pc & 1, abort_flag, wait_ns);
+          if (!my_turn_ok) { alive = false; break; }
+        }
+        const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+        // probabilities, packed as 16-bit pairs, into the tile's P buffer of this stage
+        float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
+  #pragma unroll
+        for (int c = 0; c < HB; c += 32) {
+          uint32_t pk[16];
+  #pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c + 2 * j]), e_scale, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 2 * j + 1]), e_scale, -m_use));
+            lsum4[j & 3] += p0 + p1;
+            pk[j] = Mma<T>::pack(p0, p1);
+          }
+          tc_st16(tm_p + (c >> 1), pk);
+        }
+        l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
+        if (two) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_turn(x));
+          ++pc;
+        }
+        const bool tail = pos + kBN > u.kv_end;
+        if (tail) {
+          // Tail stage: V rows of keys >= kv_end were either never fetched (stale shared memory) or lie
+          // past the sequence's length inside its last page (unowned, possibly NaN).  Their
+          // probabilities are exactly 0, but 0 * NaN would poison O, so every group clears the rows
+          // before its own tile's P.V can be issued (the two groups write the same zeros; zero rows are
+          // invariant under the swizzle).
+          int nvalid = u.kv_end - pos;
+          if (nvalid < 0) nvalid = 0;
+          uint8_t* vbase = smem + C::OFF_KV + st * C::STAGE_BYTES + C::V_OFF;
+          const int n16 = (kBN - nvalid) * DC * 8;
+          for (int idx = grp_tid; idx < n16; idx += 32 * C::SM_WARPS) {
+            const int t = nvalid + idx / (DC * 8);
+            const int rem = idx % (DC * 8);
+            *reinterpret_cast<uint4*>(vbase + (t >> 3) * C::GROUP_BYTES + (rem >> 3) * 1024 + (t & 7) * 128 + (rem & 7) * 16) =
+                make_uint4(0u, 0u, 0u, 0u);
+          }
+          fence_async_smem();  // the zeroed V rows are read by the async proxy
+        }
+        tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_o_free(x));
+        if (lane == 0) mbar_arrive(bar_p_full(x, ti & 1));
+
+        if (pos + kBN >= u.kv_end) {
+          // ---- last stage of the item: wait for its P.V, normalise, store ----
+          const float l_row = l_run;
+          if (!mbar_wait(bar_pv_done(x, ti & 1), (ti >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
+          tc_fence_after();
+          float scl = 1.f, l_fin = l_row;
+          if (p.num_sinks > 0 && row_ok) {
+            // attention sinks join the denominator only (_xla_impl_fwd.py:161-172)
+            const int srow = (p.sink_rows == p.Hq) ? out_head : (p.sink_rows == Hkv ? h : 0);
+            const float* sk = p.sinks + (size_t)srow * p.num_sinks;
+            float sm = -INFINITY;
+            for (int i = 0; i < p.num_sinks; ++i) sm = fmaxf(sm, sk[i] * kLog2eP);
+            const float m_fin = fmaxf(m_run, sm);
+            const float mf = (m_fin == -INFINITY) ? 0.f : m_fin;
+            scl = fast_exp2(m_run - mf);
+            l_fin = l_row * scl;
+            for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2eP - mf);
+          }
+          scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
+          T* orow = reinterpret_cast<T*>(p.out) + ((size_t)out_row_q * p.Hq + out_head) * D;
+  #pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t o[32];
+            tc_ld32(tm_o + c0, o);
+            tc_wait_ld();
+            if (row_ok) {
+  #pragma unroll
+              for (int c = 0; c < 32; c += 8) {
+                uint4 v;
+                v.x = Mma<T>::pack(__uint_as_float(o[c]) * scl, __uint_as_float(o[c + 1]) * scl);
+                v.y = Mma<T>::pack(__uint_as_float(o[c + 2]) * scl, __uint_as_float(o[c + 3]) * scl);
+                v.z = Mma<T>::pack(__uint_as_float(o[c + 4]) * scl, __uint_as_float(o[c + 5]) * scl);
+                v.w = Mma<T>::pack(__uint_as_float(o[c + 6]) * scl, __uint_as_float(o[c + 7]) * scl);
+                *reinterpret_cast<uint4*>(orow + c0 + c) = v;
+              }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_o_free(x));
+        }
       }
-     }
     }
   }
   if (*abort_flag) flags |= EJK_RPA_ST_TIMEOUT;
