@@ -194,7 +194,22 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.max_slots = L.max_slots;
   p.max_punits = L.max_punits;
   p.target_units = L.target_units;
+  // Per-call tile hints of the reference's RaggedPageAttentionConfig (configs.py:242-258) override
+  // the process-wide options: num_kv_pages_per_block = smallest KV chunk a row tile is split into
+  // (in pages; rounded up to whole 64-token stages), num_queries_per_block = query tokens from
+  // which on a sequence is served by 128-row tensor tiles.
   p.min_chunk = g_opt.min_chunk;
+  if (a.num_kv_pages_per_block > 0) {
+    long long c = (long long)a.num_kv_pages_per_block * s.page_size;
+    c = ((c + kTileTokens - 1) / kTileTokens) * kTileTokens;
+    if (c > 0x40000000ll) c = 0x40000000ll;
+    p.min_chunk = (int)c;
+  }
+  int prefill_rows = g_opt.prefill_rows;
+  if (a.num_queries_per_block > 0) {
+    const long long r = (long long)a.num_queries_per_block * (s.num_q_heads / s.num_kv_heads);
+    prefill_rows = r > 0x40000000ll ? 0x40000000 : (int)r;
+  }
   p.window = a.sliding_window > 0 ? a.sliding_window : 0;
   p.num_sinks = a.num_sinks;
   p.sink_rows = a.sink_rows;
@@ -219,10 +234,10 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   if (use_tma && !tma_path_supported(p)) return value_cache ? EJK_RPA_E_SHAPE : EJK_RPA_E_ARG;
   // Batches that can hold a sequence with many query rows also get the tcgen05 prefill-tile
   // kernel; whether any sequence actually qualifies is decided by the planner on the device.
-  const bool use_prefill = use_tma && g_opt.prefill_rows > 0 && prefill_path_supported(p) &&
-                           (long long)s.total_tokens * p.G >= g_opt.prefill_rows &&
+  const bool use_prefill = use_tma && prefill_rows > 0 && prefill_path_supported(p) &&
+                           (long long)s.total_tokens * p.G >= prefill_rows &&
                            s.total_tokens > s.max_num_seqs;  // more query rows than sequences: some are multi-token
-  p.prefill_min_rows = use_prefill ? g_opt.prefill_rows : 0;
+  p.prefill_min_rows = use_prefill ? prefill_rows : 0;
   // The last-arriver merge inside the split-KV kernel saves a launch, but the chunk that arrives last
   // combines its tile alone: with many chunks per tile (few query rows, long contexts) the separate
   // merge kernel, which spreads the rows over the whole GPU, is faster.  Decided from static shapes:

@@ -17,6 +17,7 @@ import torch
 from ...kernels._registry import Backend, Platform, kernel_registry
 from ...sharding import Mesh1D, PartitionSpec, all_gather_heads
 from .configs import RaggedPageAttentionConfig
+from .tuning import PersistentCache, call_key, cuda_event_timer, device_fingerprint, pick_best
 
 Array = torch.Tensor
 OP_ID = "ragged_page_attention"
@@ -40,6 +41,14 @@ class RaggedPageAttention:
     op_id = OP_ID
     version = OP_VERSION
 
+    def __init__(self, cache: PersistentCache | None = None):
+        # tuned configurations, looked up when a call gives no ``cfg``; None = always the heuristic
+        self.cache = cache
+
+    @property
+    def op_id_v(self) -> str:
+        return f"{self.op_id}@v{self.version}"
+
     def get_impl(self, cfg: RaggedPageAttentionConfig):
         platform = _resolve_platform(cfg.platform)
         backend = Backend.GPU if cfg.backend in (None, "any", Backend.ANY) else cfg.backend
@@ -51,10 +60,53 @@ class RaggedPageAttention:
             platform="cuda", backend="gpu",
         )
 
-    def candidate_cfgs(self, inv=None) -> list[RaggedPageAttentionConfig]:
-        """The device planner sizes KV chunks from the lengths at run time, so there is a single
-        candidate (the reference's GPU candidate list also collapses to one entry, :478-499)."""
-        return [self.heuristic_cfg(inv)]
+    def candidate_cfgs(self, inv=None, page_size: int | None = None) -> list[RaggedPageAttentionConfig]:
+        """The heuristic (the device planner sizes KV chunks from the lengths at run time) plus, when
+        the page size is known, a few floors for the KV chunk and thresholds for the tensor tiles.
+        The reference's GPU candidate list is a single entry (:478-499)."""
+        out = [self.heuristic_cfg(inv)]
+        if page_size:
+            for chunk_tokens in (128, 512, 1024, 2048):
+                out.append(RaggedPageAttentionConfig(
+                    num_kv_pages_per_block=max(1, chunk_tokens // page_size), num_queries_per_block=None,
+                    platform="cuda", backend="gpu"))
+            for q_tokens in (4, 64):
+                out.append(RaggedPageAttentionConfig(
+                    num_kv_pages_per_block=None, num_queries_per_block=q_tokens, platform="cuda", backend="gpu"))
+        return out
+
+    def lookup_cfg(self, queries, kv_pages, block_tables, *, sliding_window=None, logits_soft_cap=None,
+                   softmax_aux=None) -> RaggedPageAttentionConfig:
+        """The tuned configuration of this call signature on this device, else the heuristic."""
+        if self.cache is not None:
+            hit = self.cache.get(device_fingerprint(queries.device), self.op_id_v,
+                                 call_key(queries, kv_pages, block_tables, sliding_window=sliding_window,
+                                          logits_soft_cap=logits_soft_cap, softmax_aux=softmax_aux))
+            if hit is not None:
+                return hit
+        return self.heuristic_cfg()
+
+    def autotune(self, queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, *,
+                 softmax_scale=None, logits_soft_cap=None, sliding_window=None, softmax_aux=None,
+                 candidates=None, timer=cuda_event_timer) -> RaggedPageAttentionConfig:
+        """Measures every candidate on the given operands (reference: ``Tuner.measure``,
+        ejkernel/ops/config/selection.py:226-245), stores the fastest under
+        ``device|ragged_page_attention@v0|call_key`` if a cache is attached, and returns it."""
+        cands = list(candidates) if candidates is not None else self.candidate_cfgs(page_size=kv_pages.shape[1])
+        pages_per_seq = block_tables.shape[1]
+        cands = [c for c in cands if c.num_kv_pages_per_block is None or c.num_kv_pages_per_block <= pages_per_seq]
+
+        def run_with(cfg):
+            return lambda: self.run(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs,
+                                    softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap,
+                                    sliding_window=sliding_window, softmax_aux=softmax_aux, cfg=cfg)
+
+        best, _ = pick_best(cands, run_with, timer)
+        if self.cache is not None:
+            self.cache.put(device_fingerprint(queries.device), self.op_id_v,
+                           call_key(queries, kv_pages, block_tables, sliding_window=sliding_window,
+                                    logits_soft_cap=logits_soft_cap, softmax_aux=softmax_aux), best)
+        return best
 
     candidate_cfgs_gpu = candidate_cfgs
     candidate_cfgs_shard_map_gpu = candidate_cfgs
@@ -168,7 +220,17 @@ class RaggedPageAttention:
         return fn, call_args
 
 
-_kernel = RaggedPageAttention()
+def _cache_from_env() -> PersistentCache | None:
+    """``EJKERNEL_B200_TUNING_CACHE=<file.json>`` attaches a persistent cache to the module-level
+    operator (the reference reads its cache location from the environment too,
+    ejkernel/ops/config/selection.py:328)."""
+    import os
+
+    path = os.environ.get("EJKERNEL_B200_TUNING_CACHE")
+    return PersistentCache(OP_ID, path, cfg_type=RaggedPageAttentionConfig) if path else None
+
+
+_kernel = RaggedPageAttention(cache=_cache_from_env())
 
 
 def ragged_page_attention(
@@ -201,7 +263,8 @@ def ragged_page_attention(
     ``softmax_aux`` sinks.  With ``mesh``, ``in_specs`` and ``out_specs`` all given the call runs in
     shard-map mode on this process's local shards (see ``create_shard_map_wrapper``).
     """
-    cfg = cfg or _kernel.heuristic_cfg()
+    cfg = cfg or _kernel.lookup_cfg(queries, kv_pages, block_tables, sliding_window=sliding_window,
+                                    logits_soft_cap=logits_soft_cap, softmax_aux=softmax_aux)
     common = dict(
         softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap, compute_dtype=compute_dtype,
         optimized=optimized, sliding_window=sliding_window, softmax_aux=softmax_aux, mask_value=mask_value,

@@ -88,8 +88,11 @@ typedef struct ejk_rpa_attrs {
   int32_t sliding_window;/* <= 0 = none; W keeps keys (pos-W, pos] (_xla_impl_fwd.py:128-134) */
   int32_t num_sinks;     /* 0 = no softmax_aux */
   int32_t sink_rows;     /* rows of softmax_aux: num_q_heads, num_kv_heads, or 1 (_xla_impl_fwd.py:60-77) */
-  int32_t num_kv_pages_per_block; /* tile hint, 0 = auto (RaggedPageAttentionConfig, configs.py:242-258) */
-  int32_t num_queries_per_block;  /* tile hint, 0 = auto */
+  int32_t num_kv_pages_per_block; /* tile hint of RaggedPageAttentionConfig (configs.py:242-258), 0 = auto: the
+                                     smallest KV chunk, in pages, a row tile is split into (overrides option
+                                     "min_chunk" for this call) */
+  int32_t num_queries_per_block;  /* tile hint, 0 = auto: sequences with at least this many query tokens are served
+                                     by 128-row tensor tiles (overrides option "prefill_rows" for this call) */
 } ejk_rpa_attrs;
 
 /* Library version (EJK_RPA_VERSION of the build).  No reference counterpart; the reference

@@ -156,6 +156,28 @@ def test_prefill_tile_kernel_shapes(rpa_lib):
     _check(b, "d256 one tile per CTA, window")
 
 
+def test_tile_hints_change_the_partition_not_the_result(rpa_lib, tmp_path):
+    """``num_kv_pages_per_block`` (KV-chunk floor) and ``num_queries_per_block`` (threshold of the tensor
+    tiles) of RaggedPageAttentionConfig reach the planner per call; every setting must match the oracle,
+    and the autotuner must return one of its candidates and persist it."""
+    from ejkernel_b200.modules.operations import RaggedPageAttention, RaggedPageAttentionConfig
+    from ejkernel_b200.modules.operations.tuning import PersistentCache
+    b = make_ragged_batch([1, 40, 3, 160, 1], [2800, 640, 77, 1700, 900], num_q_heads=8, num_kv_heads=2, head_dim=128,
+                          page_size=16, seed=91)
+    want = oracle(b)
+    bc = b.to("cuda")
+    kern = RaggedPageAttention(cache=PersistentCache("ragged_page_attention", str(tmp_path / "t.json"),
+                                                     cfg_type=RaggedPageAttentionConfig))
+    for kvp, nq in ((None, None), (4, None), (128, None), (None, 1), (None, 100), (8, 3)):
+        cfg = RaggedPageAttentionConfig(num_kv_pages_per_block=kvp, num_queries_per_block=nq, platform="cuda", backend="gpu")
+        out = kern.run(*bc.args(), **bc.kwargs(), cfg=cfg)
+        assert_parity(out, want, b.total_tokens, what=f"hints kv_pages={kvp} queries={nq}")
+    best = kern.autotune(*bc.args(), softmax_scale=bc.softmax_scale)
+    assert best in kern.candidate_cfgs(page_size=16)
+    assert kern.lookup_cfg(bc.queries, bc.kv_pages, bc.block_tables) == best
+    assert_parity(kern.run(*bc.args(), **bc.kwargs(), cfg=best), want, b.total_tokens, what="tuned cfg")
+
+
 def test_overlapped_launches_equal_stream_order_bitwise(rpa_lib):
     """With programmatic dependent launches the prefill kernel starts under the planner's tail and the
     split-KV kernel runs beside the prefill kernel's last CTAs; the kernels write different rows, so
