@@ -12,6 +12,7 @@ struct Options {
   int min_chunk = 256;
   int path = 0;
   int profile = 0;
+  int test_withhold = 0;   // test hook, see Params::test_withhold
   int overlap = 1;         // programmatic dependent launches: kernels of one call overlap where they are independent
   int fused_merge = 1;     // the TMA split-KV kernel combines the chunks of a tile itself (no merge kernel)
   int wait_ms = 2000;      // bound of every in-kernel wait; expiry sets EJK_RPA_ST_TIMEOUT
@@ -230,6 +231,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.tma_block_shift = 0;
   while ((1 << p.tma_block_shift) < p.tma_block_tokens) ++p.tma_block_shift;
   p.wait_timeout_ms = g_opt.wait_ms;
+  p.test_withhold = g_opt.test_withhold;
   const bool use_tma = value_cache || (g_opt.path == 2) || (g_opt.path == 0 && tma_path_supported(p));
   if (use_tma && !tma_path_supported(p)) return value_cache ? EJK_RPA_E_SHAPE : EJK_RPA_E_ARG;
   // Batches that can hold a sequence with many query rows also get the tcgen05 prefill-tile
@@ -380,6 +382,9 @@ int ejk_rpa_set_option(const char* name, int value) {
     g_opt.profile = value ? 1 : 0;
   } else if (!std::strcmp(name, "overlap")) {
     g_opt.overlap = value ? 1 : 0;
+  } else if (!std::strcmp(name, "test_withhold")) {
+    if (value < 0 || value > 3) return EJK_RPA_E_ARG;
+    g_opt.test_withhold = value;
   } else if (!std::strcmp(name, "fused_merge")) {
     if (value < 0 || value > 2) return EJK_RPA_E_ARG;
     g_opt.fused_merge = value;
@@ -402,6 +407,7 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "path")) *value = g_opt.path;
   else if (!std::strcmp(name, "profile")) *value = g_opt.profile;
   else if (!std::strcmp(name, "overlap")) *value = g_opt.overlap;
+  else if (!std::strcmp(name, "test_withhold")) *value = g_opt.test_withhold;
   else if (!std::strcmp(name, "fused_merge")) *value = g_opt.fused_merge;
   else if (!std::strcmp(name, "wait_ms")) *value = g_opt.wait_ms;
   else if (!std::strcmp(name, "prefill_rows")) *value = g_opt.prefill_rows;

@@ -136,6 +136,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return ok;
 }
 
+// Bounded wait that ignores the abort flag: used on the way out of a kernel, to give bulk copies that
+// are still in flight time to land before the CTA's shared memory is released.
+__device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity, unsigned long long timeout_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  while (global_timer_ns() - t0 <= timeout_ns)
+    if (mbar_try_wait_park(bar, parity, kParkNs)) return true;
+  return false;
+}
+
 // Same bounded wait for a role that runs on a single thread (no warp vote).
 __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                  unsigned long long timeout_ns) {

@@ -232,7 +232,10 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           alive = false;
           break;
         }
-        if (lane == 0) {
+        // test hook: the stage is never announced, the waits for it must run out
+        const bool withhold = (p.test_withhold & 2) && wid == 0 && first;
+        if (withhold) ngrp = 0;
+        if (lane == 0 && !withhold) {
           if (first) {
             // every role is within NS + 2 items of this warp (the MMA warps through the stage ring, each
             // softmax group through q_full / skip of its MMA warp): slot k - kRingP is free
@@ -267,6 +270,14 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       const int g2 = gi + i;
       if (g2 < NS) continue;  // never used
       if (!mbar_wait(bar_kv_empty(g2 % NS), ((g2 / NS) & 1) ^ 1, abort_flag, wait_ns)) break;
+    }
+    if (*abort_flag) {
+      // giving up: nobody releases stages any more, so wait (bounded, 2 ms per stage) for the copies
+      // themselves -- the "full" phase of each of the last NS announced stages
+      for (int i = 1; i <= NS && i <= gi; ++i) {
+        const int f = gi - i;
+        mbar_wait_quiet(bar_kv_full(f % NS), (uint32_t)((f / NS) & 1), 2000000ull);
+      }
     }
   } else if (warp == 1 || warp >= 2 + C::SM_WARPS * NT) {
     // =============================== MMA issuers ===============================

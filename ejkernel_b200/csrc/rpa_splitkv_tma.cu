@@ -123,6 +123,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
     int s = 0;
     uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1: all stages start empty
     int k = 0;
+    int fills = 0;  // stages announced so far
     int wid = 0;
     if (lane == 0) wid = atomicAdd(&p.header[kHdrQueue], 1);
     wid = __shfl_sync(0xffffffffu, wid, 0);
@@ -135,6 +136,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
           metas[s] = make_int2(-1, 0);
           mbar_arrive(bar_full + s * 8);
         }
+        ++fills;
         break;
       }
       const int ui = wid / Hkv;
@@ -185,7 +187,11 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
         if (nblk > blocks_per_stage) nblk = blocks_per_stage;
         if (nblk < 0) nblk = 0;
         __syncwarp();
-        if (lane == 0) {
+        // test hook: the stage is never announced, the consumers' wait for it must run out
+        const bool withhold = (p.test_withhold & 1) && wid == 0 && first;
+        ++fills;
+        if (withhold) nblk = 0;
+        if (lane == 0 && !withhold) {
           metas[s] = make_int2(ring_slot, pos);
           if (nblk > 0) mbar_arrive_expect_tx(bar_full + s * 8, (uint32_t)nblk * box_bytes);
           else mbar_arrive(bar_full + s * 8);
@@ -234,7 +240,16 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
         empty_parity ^= 1u;
       }
     }
-    if (*abort_flag) flags |= EJK_RPA_ST_TIMEOUT;
+    if (*abort_flag) {
+      // Giving up: the consumers no longer release stages, so wait (bounded, 2 ms per stage) for the
+      // copies themselves -- the "full" phase of each of the last NS announced stages -- before this
+      // CTA's shared memory can go to another CTA.
+      flags |= EJK_RPA_ST_TIMEOUT;
+      for (int i = 1; i <= NS && i <= fills; ++i) {
+        const int f = fills - i;
+        mbar_wait_quiet(bar_full + (f % NS) * 8, (uint32_t)((f / NS) & 1), 2000000ull);
+      }
+    }
   } else {
     // =============================== consumer warps ===============================
     // per-thread shared-memory offsets of the ldmatrix rows (constant for the whole kernel)

@@ -83,6 +83,9 @@ struct Params {
   int32_t max_units, max_merge, max_slots, target_units, min_chunk;
   int32_t max_punits;
   int32_t prefill_item_rows; // rows one prefill work item covers (128 per tile, 1 or 2 tiles per CTA)
+  int32_t test_withhold;     // test hook: bit 0 / bit 1 = the CTA of the split-KV / prefill kernel that takes work item 0
+                             // never announces the item's first KV stage, so that the waits on it run out
+                             // (EJK_RPA_ST_TIMEOUT); 0 in production
   int32_t pdl;               // bit 0: the prefill kernel, bit 1: the split-KV kernel must pdl_wait() before reading the plan
   int32_t prefill_min_rows;  // sequences with q_len*G >= this go to the prefill-tile kernel; 0 = never
   int32_t window;      // <= 0: none

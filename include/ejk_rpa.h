@@ -193,6 +193,9 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *   "fused_merge" 1 (default) = where a row tile gets few KV chunks (decided from the static shapes) the split-KV
  *                kernel's last-finishing chunk combines the chunks of its tile; 0 = always a separate merge kernel;
  *                2 = always fused
+ *   "test_withhold" test hook, 0 in production: bit 0 / bit 1 make the CTA of the split-KV / prefill kernel that takes
+ *                work item 0 never announce the item's first KV stage, so that the waits on it run out and the call reports
+ *                EJK_RPA_ST_TIMEOUT (no fault, no hang; the context stays usable)
  *   "wait_ms"    wall-time bound, in milliseconds, of every wait inside a kernel (default 2000)
  *   "profile"    1 = record CUDA events around each kernel of a launch (see ejk_rpa_profile_read)
  * Returns 0, or EJK_RPA_E_ARG for an unknown name.  Counterpart of the reference's

@@ -156,6 +156,36 @@ def test_prefill_tile_kernel_shapes(rpa_lib):
     _check(b, "d256 one tile per CTA, window")
 
 
+@pytest.mark.parametrize("which", ["split-KV kernel", "prefill kernel"])
+def test_a_wait_that_runs_out_sets_the_timeout_bit_and_leaves_the_context_usable(rpa_lib, which):
+    """Every in-kernel wait is bounded.  The test hook makes CTA 0 never announce its first KV stage
+    (nothing faults, nothing hangs): the waits on it expire after ``wait_ms``, the CTA gives up, frees
+    what it holds and returns, the status word carries EJK_RPA_ST_TIMEOUT, and the next call on the same
+    context is correct again."""
+    from ejkernel_b200 import _cabi
+    if which == "prefill kernel":
+        b = make_ragged_batch([200, 1], [900, 300], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=95)
+    else:
+        b = make_ragged_batch([1, 1, 2], [700, 64, 1500], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=96)
+    want = oracle(b)
+    bc = b.to("cuda")
+    old = _cabi.get_option("wait_ms")
+    try:
+        _cabi.set_option("wait_ms", 50)
+        _cabi.set_option("test_withhold", 2 if which == "prefill kernel" else 1)
+        run_cuda(bc)
+        torch.cuda.synchronize()
+        word = status_word(bc)
+        assert word & _cabi.ST_TIMEOUT, (which, word)
+        assert "wait" in " ".join(_cabi.decode_status(word)).lower() or "time" in " ".join(_cabi.decode_status(word)).lower()
+    finally:
+        _cabi.set_option("test_withhold", 0)
+        _cabi.set_option("wait_ms", old)
+    out = run_cuda(bc)
+    assert status_word(bc) == 0
+    assert_parity(out, want, b.total_tokens, what=f"after a timed-out {which}")
+
+
 def test_tile_hints_change_the_partition_not_the_result(rpa_lib, tmp_path):
     """``num_kv_pages_per_block`` (KV-chunk floor) and ``num_queries_per_block`` (threshold of the tensor
     tiles) of RaggedPageAttentionConfig reach the planner per call; every setting must match the oracle,
