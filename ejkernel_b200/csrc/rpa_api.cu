@@ -8,10 +8,11 @@ namespace ejk {
 namespace {
 
 struct Options {
-  int waves = 8;
+  int waves = 4;           // split-KV work items per CTA (with longest-first queueing, fewer and longer items win)
   int min_chunk = 256;
   int path = 0;
   int profile = 0;
+  int sort_items = 1;      // split-KV work items longest first
   int test_withhold = 0;   // test hook, see Params::test_withhold
   int overlap = 1;         // programmatic dependent launches: kernels of one call overlap where they are independent
   int fused_merge = 1;     // the TMA split-KV kernel combines the chunks of a tile itself (no merge kernel)
@@ -232,6 +233,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   while ((1 << p.tma_block_shift) < p.tma_block_tokens) ++p.tma_block_shift;
   p.wait_timeout_ms = g_opt.wait_ms;
   p.test_withhold = g_opt.test_withhold;
+  p.sort_items = g_opt.sort_items;
   const bool use_tma = value_cache || (g_opt.path == 2) || (g_opt.path == 0 && tma_path_supported(p));
   if (use_tma && !tma_path_supported(p)) return value_cache ? EJK_RPA_E_SHAPE : EJK_RPA_E_ARG;
   // Batches that can hold a sequence with many query rows also get the tcgen05 prefill-tile
@@ -243,12 +245,14 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   // The last-arriver merge inside the split-KV kernel saves a launch, but the chunk that arrives last
   // combines its tile alone: with many chunks per tile (few query rows, long contexts) the separate
   // merge kernel, which spreads the rows over the whole GPU, is faster.  Decided from static shapes:
-  // fused when a tile gets at most ~4 chunks on average.
-  // (option value 2 forces the fused merge.)
-  p.fused_merge = (use_tma && (g_opt.fused_merge == 2 ||
-                               (g_opt.fused_merge == 1 && (long long)L.target_units <= 4ll * s.total_tokens)))
-                      ? 1
-                      : 0;
+  // fused when a tile can get at most ~2 chunks -- on average over the batch (work items per query
+  // token) or because the longest possible context is that short.  (Option value 2 forces it.)
+  {
+    const long long max_kv = (long long)s.pages_per_seq * s.page_size;
+    const long long by_len = (max_kv + p.min_chunk - 1) / p.min_chunk;
+    const bool few = (long long)L.target_units <= 2ll * s.total_tokens || by_len <= 2;
+    p.fused_merge = (use_tma && (g_opt.fused_merge == 2 || (g_opt.fused_merge == 1 && few))) ? 1 : 0;
+  }
   p.prefill_item_rows = prefill_rows_per_item(s.head_dim);
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -382,6 +386,8 @@ int ejk_rpa_set_option(const char* name, int value) {
     g_opt.profile = value ? 1 : 0;
   } else if (!std::strcmp(name, "overlap")) {
     g_opt.overlap = value ? 1 : 0;
+  } else if (!std::strcmp(name, "sort_items")) {
+    g_opt.sort_items = value ? 1 : 0;
   } else if (!std::strcmp(name, "test_withhold")) {
     if (value < 0 || value > 3) return EJK_RPA_E_ARG;
     g_opt.test_withhold = value;
@@ -407,6 +413,7 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "path")) *value = g_opt.path;
   else if (!std::strcmp(name, "profile")) *value = g_opt.profile;
   else if (!std::strcmp(name, "overlap")) *value = g_opt.overlap;
+  else if (!std::strcmp(name, "sort_items")) *value = g_opt.sort_items;
   else if (!std::strcmp(name, "test_withhold")) *value = g_opt.test_withhold;
   else if (!std::strcmp(name, "fused_merge")) *value = g_opt.fused_merge;
   else if (!std::strcmp(name, "wait_ms")) *value = g_opt.wait_ms;

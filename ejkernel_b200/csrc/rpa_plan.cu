@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   __shared__ unsigned long long s_keys;
   __shared__ int s_chunk;
   __shared__ int s_bucket[kLenBuckets];  // histogram, then write cursor, of prefill tiles per length bucket
+  __shared__ int s_bdec[kLenBuckets];    // the same for the split-KV work items
   const int tid = threadIdx.x;
   unsigned flags = 0;
 
@@ -135,7 +136,10 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   }
   if (S < 0) S = 0;
   if (tid == 0) s_keys = 0ull;
-  for (int i = tid; i < kLenBuckets; i += kPlanThreads) s_bucket[i] = 0;
+  for (int i = tid; i < kLenBuckets; i += kPlanThreads) {
+    s_bucket[i] = 0;
+    s_bdec[i] = 0;
+  }
   // bucket = stages >> bshift, sized so the longest possible tile lands in the last bucket
   int bshift = 0;
   {
@@ -190,15 +194,32 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   __syncthreads();
   const int chunk = s_chunk;
 
-  // histogram -> descending exclusive offsets: the longest tiles get the lowest queue positions, so
-  // the persistent CTAs of the tensor-tile kernel take them first (longest-processing-time order)
+  // ---- pass 1b: histogram of the split-KV work items by length (the chunk size is known now)
+  for (int s = tid; s < S && p.sort_items; s += kPlanThreads) {
+    unsigned f = 0;
+    SeqInfo si = load_seq(p, s, f);
+    if (!si.ok || si.prefill) continue;
+    for (int t = 0; t < si.tiles; ++t) {
+      int lo, hi, n, cs;
+      tile_range(p, si, t, lo, hi, p.rows_per_tile);
+      chunking(hi - lo, chunk, n, cs);
+      if (n > 1) atomicAdd(&s_bdec[bucket_of(lo, lo + cs)], n - 1);
+      atomicAdd(&s_bdec[bucket_of(lo + (n - 1) * cs, hi)], 1);
+    }
+  }
+  __syncthreads();
+
+  // histograms -> descending exclusive offsets: the longest items get the lowest queue positions, so the
+  // persistent CTAs take them first (longest-processing-time order) and the kernels end on short
+  // items instead of on whatever the sequence order happens to leave for last
   int n_prefill_total = 0;
   {
     static_assert(kLenBuckets == kPlanThreads, "one bucket per planner thread");
-    int v[kCnt] = {s_bucket[kLenBuckets - 1 - tid], 0, 0, 0};
+    int v[kCnt] = {s_bucket[kLenBuckets - 1 - tid], s_bdec[kLenBuckets - 1 - tid], 0, 0};
     int excl[kCnt], total[kCnt];
     block_scan(v, excl, total, s_warp);
     s_bucket[kLenBuckets - 1 - tid] = excl[0];
+    s_bdec[kLenBuckets - 1 - tid] = excl[1];
     n_prefill_total = total[0];
     __syncthreads();
   }
@@ -287,8 +308,9 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
             un.chunk_idx = c;
             un.n_chunks = n;
             un.pad = 0;
-            p.units[u++] = un;
+            p.units[p.sort_items ? atomicAdd(&s_bdec[bucket_of(un.kv_begin, un.kv_end)], 1) : u + c] = un;
           }
+          u += n;
         }
       }
     }

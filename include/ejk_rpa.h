@@ -183,11 +183,12 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
                                               const ejk_rpa_attrs* attrs, void* stream);
 
 /* Process-wide tuning knobs (host side, not thread safe against concurrent launches):
- *   "waves"      work items per resident CTA the device planner aims for (default 8)
+ *   "waves"      work items per resident CTA the device planner aims for (default 4)
  *   "min_chunk"  smallest KV chunk, in tokens, a split may have (default 256)
  *   "path"       0 = auto, 1 = force the cp.async gather, 2 = force the TMA gather
  *   "prefill_rows" sequences with at least this many (query token, head-in-group) rows per kv head are
  *                served by 128-row tcgen05 tiles instead of 8-row split-KV tiles (default 64; 0 = never)
+ *   "sort_items" 1 (default) = the planner queues split-KV work items longest first, 0 = in sequence order
  *   "overlap"    1 (default) = the kernels of one call are launched as programmatic dependents: each starts under
  *                the tail of the one before and waits on the device for what it needs; 0 = plain stream order
  *   "fused_merge" 1 (default) = where a row tile gets few KV chunks (decided from the static shapes) the split-KV

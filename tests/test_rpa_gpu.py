@@ -235,6 +235,28 @@ def test_overlapped_launches_equal_stream_order_bitwise(rpa_lib):
         _cabi.set_option("overlap", old)
 
 
+def test_queue_order_does_not_change_results(rpa_lib):
+    """The planner queues split-KV work items longest first (option ``sort_items``); inside a length
+    bucket the order depends on atomics.  Every item writes its own rows or its own partial slot and
+    partials are combined in chunk order, so the output is bitwise the same as in sequence order, run
+    after run."""
+    from ejkernel_b200 import _cabi
+    b = make_ragged_batch([1, 2, 1, 5, 1, 1, 3], [5000, 37, 2900, 9000, 700, 64, 1300], num_q_heads=16, num_kv_heads=4,
+                          head_dim=128, page_size=16, seed=97, sliding_window=6000)
+    want = oracle(b)
+    old = _cabi.get_option("sort_items")
+    try:
+        _cabi.set_option("sort_items", 0)
+        plain = run_cuda(b)
+        _cabi.set_option("sort_items", 1)
+        outs = [run_cuda(b) for _ in range(4)]
+    finally:
+        _cabi.set_option("sort_items", old)
+    assert_parity(plain, want, b.total_tokens, what="sequence order")
+    for o in outs:
+        assert torch.equal(o, plain)
+
+
 def test_fused_merge_equals_merge_kernel_bitwise(rpa_lib):
     """The split-KV kernel's last-arriver merge and the separate merge kernel combine the chunks of a
     tile in the same order with the same arithmetic: outputs are bitwise equal, run after run."""
