@@ -404,6 +404,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           *abort_flag = 1;
           break;
         }
+        __threadfence_block();  // the ring entry was written before the counter moved; read it after
       }
       const Unit u = ring[k % kRingP].u;
       const int h = ring[k % kRingP].h;
