@@ -42,7 +42,7 @@ UNIT = "tokens/s"
 # DRAM traffic of the attention kernel relative to its algorithmic KV bytes, from an ncu capture of a
 # reduced case of the same workload (dram__bytes_read.sum + dram__bytes_write.sum over KV bytes; traffic grows
 # in proportion to the KV bytes: every byte is read once).  Source: profiles/rpa_splitkv_tma_c2.md.
-NCU_TRAFFIC_RATIO = {"c2": (787.95 + 7.75) / 786.06}
+NCU_TRAFFIC_RATIO = {"c2": (788.25 + 5.55) / 786.06}
 
 
 def parse_args():
