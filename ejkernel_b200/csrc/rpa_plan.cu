@@ -13,6 +13,7 @@ namespace {
 
 constexpr int kPlanThreads = 1024;
 constexpr int kLenBuckets = 1024;  // prefill tiles are queued longest first (bucketed by stage count)
+constexpr int kSeqCache = 2048;    // sequences whose lengths stay in shared memory between the passes
 
 struct SeqInfo {
   int q_start, q_len, kv_len, rows, tiles;
@@ -20,12 +21,28 @@ struct SeqInfo {
   bool prefill;  // many query rows: 128-row tiles for the tcgen05 kernel, no KV split
 };
 
-__device__ __forceinline__ SeqInfo load_seq(const Params& p, int s, unsigned& flags) {
+// The three passes of the planner need every sequence's (query start, query end, kv length); the
+// first pass reads them from global memory and parks them in shared memory (`cache`, three rows of
+// kSeqCache), the later passes take them from there: a global round trip per pass is most of a
+// pass's latency.
+__device__ __forceinline__ SeqInfo load_seq(const Params& p, int s, unsigned& flags, int (*cache)[kSeqCache], bool fill) {
   SeqInfo si;
-  // no query_start_loc: a pure decode batch, one query row per sequence (page_attention)
-  int q0 = p.query_start_loc ? p.query_start_loc[s] : s;
-  int q1 = p.query_start_loc ? p.query_start_loc[s + 1] : s + 1;
-  int kv = p.context_lens[s];
+  int q0, q1, kv;
+  if (!fill && s < kSeqCache) {
+    q0 = cache[0][s];
+    q1 = cache[1][s];
+    kv = cache[2][s];
+  } else {
+    // no query_start_loc: a pure decode batch, one query row per sequence (page_attention)
+    q0 = p.query_start_loc ? p.query_start_loc[s] : s;
+    q1 = p.query_start_loc ? p.query_start_loc[s + 1] : s + 1;
+    kv = p.context_lens[s];
+    if (fill && s < kSeqCache) {
+      cache[0][s] = q0;
+      cache[1][s] = q1;
+      cache[2][s] = kv;
+    }
+  }
   const int kv_cap = p.pages_per_seq * p.page_size;
   if (kv < 0 || kv > kv_cap) {
     flags |= EJK_RPA_ST_KVLEN;
@@ -79,6 +96,22 @@ __device__ __forceinline__ void chunking(int len, int chunk, int& n, int& csize)
   if (csize < kTileTokens) csize = kTileTokens;
 }
 
+// Work items go to scattered queue positions: three 16-byte stores per item instead of twelve 4-byte
+// ones (with one item per lane every store instruction touches 32 sectors, and that store traffic was most
+// of the planner's time at 2048 sequences).
+__device__ __forceinline__ void store_unit(Unit* dst, const Unit& u) {
+  int4* d = reinterpret_cast<int4*>(dst);
+  d[0] = make_int4(u.seq, u.row0, u.kv_begin, u.kv_end);
+  d[1] = make_int4(u.slot, u.q_start, u.q_len, u.kv_len);
+  d[2] = make_int4(u.merge_idx, u.chunk_idx, u.n_chunks, u.pad);
+}
+__device__ __forceinline__ void store_merge(MergeItem* dst, const MergeItem& m) {
+  static_assert(sizeof(MergeItem) == 32, "two 16-byte words");
+  int4* d = reinterpret_cast<int4*>(dst);
+  d[0] = make_int4(m.row0, m.slot0, m.n_chunks, m.q_start);
+  d[1] = make_int4(m.q_len, m.pad[0], m.pad[1], m.pad[2]);
+}
+
 // inclusive block scan of kCnt counters; returns this thread's exclusive prefix and the block total
 constexpr int kCnt = 4;
 __device__ void block_scan(int (&v)[kCnt], int (&excl)[kCnt], int (&total)[kCnt], int (*s_warp)[kCnt]) {
@@ -126,6 +159,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   __shared__ int s_chunk;
   __shared__ int s_bucket[kLenBuckets];  // histogram, then write cursor, of prefill tiles per length bucket
   __shared__ int s_bdec[kLenBuckets];    // the same for the split-KV work items
+  __shared__ int s_seq[3][kSeqCache];    // see load_seq
   const int tid = threadIdx.x;
   unsigned flags = 0;
 
@@ -157,7 +191,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   unsigned long long keys = 0;
   for (int s = tid; s < S; s += kPlanThreads) {
     unsigned f = 0;
-    SeqInfo si = load_seq(p, s, f);
+    SeqInfo si = load_seq(p, s, f, s_seq, true);
     if (!si.ok) continue;
     if (si.prefill) {
       for (int t = 0; t < si.tiles; ++t) {
@@ -197,7 +231,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   // ---- pass 1b: histogram of the split-KV work items by length (the chunk size is known now)
   for (int s = tid; s < S && p.sort_items; s += kPlanThreads) {
     unsigned f = 0;
-    SeqInfo si = load_seq(p, s, f);
+    SeqInfo si = load_seq(p, s, f, s_seq, false);
     if (!si.ok || si.prefill) continue;
     for (int t = 0; t < si.tiles; ++t) {
       int lo, hi, n, cs;
@@ -233,7 +267,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
     si.ok = false;
     si.prefill = false;
     if (s < S) {
-      si = load_seq(p, s, flags);
+      si = load_seq(p, s, flags, s_seq, false);
       if (si.ok && si.prefill) {
         cnt[3] = si.tiles;
       } else if (si.ok) {
@@ -273,7 +307,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
           un.chunk_idx = 0;
           un.n_chunks = 1;
           un.pad = 0;
-          p.punits[atomicAdd(&s_bucket[bucket_of(lo, hi)], 1)] = un;
+          store_unit(&p.punits[atomicAdd(&s_bucket[bucket_of(lo, hi)], 1)], un);
         }
         (void)pu;
       } else {
@@ -291,7 +325,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
             mi.q_len = si.q_len;
             mi.pad[0] = mi.pad[1] = mi.pad[2] = 0;
             this_merge = m;
-            p.merge[m++] = mi;
+            store_merge(&p.merge[m++], mi);
           }
           for (int c = 0; c < n; ++c) {
             Unit un;
@@ -308,7 +342,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
             un.chunk_idx = c;
             un.n_chunks = n;
             un.pad = 0;
-            p.units[p.sort_items ? atomicAdd(&s_bdec[bucket_of(un.kv_begin, un.kv_end)], 1) : u + c] = un;
+            store_unit(&p.units[p.sort_items ? atomicAdd(&s_bdec[bucket_of(un.kv_begin, un.kv_end)], 1) : u + c], un);
           }
           u += n;
         }
