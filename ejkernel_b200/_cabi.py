@@ -32,6 +32,7 @@ EXPORTS = (
     "ejk_rpa_version",
     "ejk_rpa_error_string",
     "ejk_rpa_workspace_bytes",
+    "ejk_rpa_workspace_bytes_min",
     "ejk_rpa_launch",
     "ejk_rpa_set_option",
     "ejk_rpa_get_option",
@@ -93,6 +94,8 @@ def load() -> ctypes.CDLL:
     lib.ejk_rpa_error_string.argtypes = [c_int]
     lib.ejk_rpa_workspace_bytes.restype = c_size_t
     lib.ejk_rpa_workspace_bytes.argtypes = [POINTER(Shape)]
+    lib.ejk_rpa_workspace_bytes_min.restype = c_size_t
+    lib.ejk_rpa_workspace_bytes_min.argtypes = [POINTER(Shape)]
     lib.ejk_rpa_launch.restype = c_int
     lib.ejk_rpa_launch.argtypes = [
         c_void_p,  # queries

@@ -12,6 +12,7 @@ struct Options {
   int min_chunk = 256;
   int path = 0;
   int profile = 0;
+  int prefill_split = 1;   // prefill items are cut along KV at CTA-quota boundaries (needs the larger workspace)
   int sort_items = 1;      // split-KV work items longest first
   int test_withhold = 0;   // test hook, see Params::test_withhold
   int overlap = 1;         // programmatic dependent launches: kernels of one call overlap where they are independent
@@ -94,6 +95,19 @@ WorkspaceLayout layout_for(const ejk_rpa_shape& s, int n_sm) {
   L.part_o_off = off;
   off = align_up(off + (size_t)L.max_slots * s.num_kv_heads * L.rows_per_tile * s.head_dim * sizeof(float), 256);
   L.total = off;
+  {
+    const int nt = prefill_rows_per_item(s.head_dim) / kPrefillRows;
+    L.ppart_slots = 2 * n_sm;
+    L.pprefix_off = off;
+    off = align_up(off + ((size_t)L.max_punits + 1) * sizeof(int32_t), 256);
+    L.ptickets_off = off;
+    off = align_up(off + (size_t)L.max_punits * s.num_kv_heads * nt * 4 * sizeof(int32_t), 256);
+    L.ppart_ml_off = off;
+    off = align_up(off + (size_t)L.ppart_slots * nt * kPrefillRows * sizeof(float2), 256);
+    L.ppart_o_off = off;
+    off = align_up(off + (size_t)L.ppart_slots * nt * kPrefillRows * s.head_dim * sizeof(float), 256);
+    L.total_split = off;
+  }
   return L;
 }
 
@@ -130,7 +144,12 @@ size_t ejk_rpa_workspace_bytes(const ejk_rpa_shape* shape) {
   if (check_shape(shape) != 0) return 0;
   const DeviceInfo* d = device_info();
   if (!d) return 0;
-  return layout_for(*shape, d->sm_count).total;
+  const WorkspaceLayout L = layout_for(*shape, d->sm_count);
+  // shapes that can hold a multi-token sequence also get room for the KV split of prefill items; a
+  // launch with only L.total bytes still works, without that split
+  const bool multi = shape->total_tokens > shape->max_num_seqs;
+  const int ps = shape->page_size;
+  return (multi && ps >= 8 && (ps & (ps - 1)) == 0) ? L.total_split : L.total;
 }
 
 // Shared body of the launch entry points.  `value_cache` != null selects the split cache layout
@@ -178,6 +197,13 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.punits = reinterpret_cast<Unit*>(ws + L.punits_off);
   p.merge = reinterpret_cast<MergeItem*>(ws + L.merge_off);
   p.tickets = reinterpret_cast<int32_t*>(ws + L.tickets_off);
+  if (workspace_bytes >= L.total_split && g_opt.prefill_split) {
+    p.pprefix = reinterpret_cast<int32_t*>(ws + L.pprefix_off);
+    p.ptickets = reinterpret_cast<int32_t*>(ws + L.ptickets_off);
+    p.ppart_ml = reinterpret_cast<float2*>(ws + L.ppart_ml_off);
+    p.ppart_o = reinterpret_cast<float*>(ws + L.ppart_o_off);
+    p.prefill_split = 1;
+  }
   p.part_o = reinterpret_cast<float*>(ws + L.part_o_off);
   p.part_ml = reinterpret_cast<float2*>(ws + L.part_ml_off);
   p.status = status;
@@ -296,6 +322,13 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   return 0;
 }
 
+size_t ejk_rpa_workspace_bytes_min(const ejk_rpa_shape* shape) {
+  if (check_shape(shape) != 0) return 0;
+  const DeviceInfo* d = device_info();
+  if (!d) return 0;
+  return layout_for(*shape, d->sm_count).total;
+}
+
 int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* context_lens,
                    const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                    const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
@@ -386,6 +419,8 @@ int ejk_rpa_set_option(const char* name, int value) {
     g_opt.profile = value ? 1 : 0;
   } else if (!std::strcmp(name, "overlap")) {
     g_opt.overlap = value ? 1 : 0;
+  } else if (!std::strcmp(name, "prefill_split")) {
+    g_opt.prefill_split = value ? 1 : 0;
   } else if (!std::strcmp(name, "sort_items")) {
     g_opt.sort_items = value ? 1 : 0;
   } else if (!std::strcmp(name, "test_withhold")) {
@@ -413,6 +448,7 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "path")) *value = g_opt.path;
   else if (!std::strcmp(name, "profile")) *value = g_opt.profile;
   else if (!std::strcmp(name, "overlap")) *value = g_opt.overlap;
+  else if (!std::strcmp(name, "prefill_split")) *value = g_opt.prefill_split;
   else if (!std::strcmp(name, "sort_items")) *value = g_opt.sort_items;
   else if (!std::strcmp(name, "test_withhold")) *value = g_opt.test_withhold;
   else if (!std::strcmp(name, "fused_merge")) *value = g_opt.fused_merge;

@@ -356,12 +356,39 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
     const int n_tickets = (base[1] <= p.max_merge ? base[1] : 0) * p.Hkv;
     for (int i = tid; i < n_tickets; i += kPlanThreads) p.tickets[i] = 0;
   }
+  // KV split of prefill items: exclusive prefix of their stage counts in queue order (the tile kernel
+  // cuts the concatenated stage sequence of all (item, kv head) pairs into equal CTA quotas), and the
+  // arrival counters of the parts
+  int prefill_stages = 0;
+  if (p.prefill_split) {
+    const int n_items = base[3] <= p.max_punits ? base[3] : 0;
+    __syncthreads();  // the items scattered above by other threads
+    int running = 0;
+    for (int i0 = 0; i0 < n_items; i0 += kPlanThreads) {
+      const int i = i0 + tid;
+      int v[kCnt] = {0, 0, 0, 0};
+      if (i < n_items) {
+        const int len = p.punits[i].kv_end - p.punits[i].kv_begin;
+        v[0] = len > 0 ? (len + kTileTokens - 1) / kTileTokens : 1;
+      }
+      int excl[kCnt], total[kCnt];
+      block_scan(v, excl, total, s_warp);
+      if (i < n_items) p.pprefix[i] = running + excl[0];
+      running += total[0];
+    }
+    if (tid == 0) p.pprefix[n_items] = running;
+    prefill_stages = running;
+    const int nt = p.prefill_item_rows / kPrefillRows;
+    const int n_pt = n_items * p.Hkv * nt * 4;
+    for (int i = tid; i < n_pt; i += kPlanThreads) p.ptickets[i] = 0;
+  }
   if (tid == 0) {
     const bool over = base[0] > p.max_units || base[1] > p.max_merge || base[2] > p.max_slots || base[3] > p.max_punits;
     p.header[kHdrNumUnits] = over ? 0 : base[0];
     p.header[kHdrNumMerge] = over ? 0 : base[1];
     p.header[kHdrNumSlots] = over ? 0 : base[2];
     p.header[kHdrNumPrefill] = over ? 0 : base[3];
+    p.header[kHdrPrefillStages] = over ? 0 : prefill_stages;
     if (over) flags |= EJK_RPA_ST_INTERNAL;
   }
   if (flags && p.status) atomicOr(reinterpret_cast<unsigned*>(p.status), flags);

@@ -56,10 +56,16 @@ constexpr float kLog2eP = 1.4426950408889634f;
 constexpr float kLazyP = 8.0f;
 
 
+// One piece of work of a CTA: an item (256 or 128 query rows of one sequence) of one kv head, or, with
+// the KV split, the part of it that falls into the CTA's quota of KV stages.  For a part, u.kv_begin /
+// u.kv_end are the part's range, u.n_chunks the number of parts of the item, u.chunk_idx this part's
+// number and u.merge_idx the (item, head) index.
 struct ItemDescP {
   Unit u;
   int32_t h;
-  int32_t pad[3];
+  int32_t first_stage;  // index of the (item, head)'s first stage in the global stage sequence
+  int32_t quota;        // stages per CTA
+  int32_t pad;
 };
 
 template <int D>
@@ -173,13 +179,45 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     constexpr int kGroups = kBN / 8;  // 8-token groups (= TMA boxes) per stage
     int gi = 0;  // stage counter of this CTA
     int k = 0;
+    // Two ways to hand out work.  Dynamic: whole (item, head) pairs from the planner's longest-first
+    // queue.  KV split (when the workspace has room for the parts): the stages of all (item, head)
+    // pairs, in queue order, form one sequence that is cut into equal quotas, one per CTA, so that
+    // every SM is busy to the end however few items there are; an item that straddles a quota
+    // boundary is finished by several CTAs, whose parts the last one to arrive combines.
+    // A part costs a pipeline restart, a 64-128 KB round trip of its unnormalised O through the
+    // workspace and the combine (measured: 15-25 stages' worth per CTA), so the split is used only where
+    // the dynamic schedule is clearly worse: rounds * average item > 1.15 * (quota + 16 stages), e.g. 160
+    // equal items on 148 CTAs (0.289 -> 0.203 ms), not 128 or 256 of them, nor short items.
+    const int n_items = p.header[kHdrNumPrefill];
+    const long long W = (long long)p.header[kHdrPrefillStages] * Hkv;
+    bool split = p.prefill_split && W > 0 && W < (1ll << 30);
+    if (split) {
+      const long long U = (long long)n_items * Hkv, Cn = gridDim.x;
+      const long long rounds = (U + Cn - 1) / Cn;
+      split = rounds * W * Cn * 20 >= 23 * U * (W + 16 * Cn);
+    }
+    const int quota = split ? (int)((W + gridDim.x - 1) / gridDim.x) : 0;
+    long long g = (long long)blockIdx.x * quota;                 // next global stage of this CTA
+    const long long g_end = (g + quota < W) ? g + quota : W;
+    int it = 0;                                                  // item that contains stage g
+    if (split && g < g_end) {
+      int lo = 0, hi = n_items;  // Hkv * pprefix[lo] <= g < Hkv * pprefix[hi]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if ((long long)Hkv * __ldg(p.pprefix + mid) <= g) lo = mid;
+        else hi = mid;
+      }
+      it = lo;
+    }
     int wid = 0;
-    if (lane == 0) wid = atomicAdd(&p.header[kHdrPrefillQueue], 1);
-    wid = __shfl_sync(0xffffffffu, wid, 0);
+    if (!split) {
+      if (lane == 0) wid = atomicAdd(&p.header[kHdrPrefillQueue], 1);
+      wid = __shfl_sync(0xffffffffu, wid, 0);
+    }
     bool alive = true;
     while (alive) {
       const int s = gi % NS;
-      if (wid >= n_work) {
+      if (split ? (g >= g_end) : (wid >= n_work)) {
         if (!mbar_wait(bar_kv_empty(s), ((gi / NS) & 1) ^ 1, abort_flag, wait_ns)) break;
         if (lane == 0) {
           metas[s] = make_int2(-1, 0);
@@ -190,19 +228,43 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         }
         break;
       }
-      const int ui = wid / Hkv;
-      const int h = wid - ui * Hkv;
+      int ui, h, first_stage = 0;
+      int st_b = 0, st_e = -1;  // the piece's stage range inside the item (st_e < 0: the whole item)
+      int n_parts = 1, part_idx = 0;
+      if (split) {
+        const int p0 = __ldg(p.pprefix + it), p1 = __ldg(p.pprefix + it + 1);
+        const int n_i = p1 - p0;                                  // stages of the item (per head)
+        const long long rel = g - (long long)Hkv * p0;
+        ui = it;
+        h = (int)(rel / n_i);
+        st_b = (int)(rel - (long long)h * n_i);
+        const long long left = g_end - g;
+        const int take = (n_i - st_b < left) ? n_i - st_b : (int)left;
+        st_e = st_b + take;
+        first_stage = (int)((long long)Hkv * p0 + (long long)h * n_i);
+        const int c0 = first_stage / quota, c1 = (first_stage + n_i - 1) / quota;
+        n_parts = c1 - c0 + 1;
+        part_idx = (int)blockIdx.x - c0;
+        g += take;
+        if (st_e == n_i && h == Hkv - 1) ++it;
+        if (st_e == n_i) st_e = -1;  // up to the item's real end (its last stage may be ragged)
+      } else {
+        ui = wid / Hkv;
+        h = wid - ui * Hkv;
+      }
       Unit u;
       {
         const int4* src = reinterpret_cast<const int4*>(p.punits + ui);
         const int4 a = __ldg(src), b = __ldg(src + 1);
         u.seq = a.x; u.row0 = a.y; u.kv_begin = a.z; u.kv_end = a.w;
         u.slot = b.x; u.q_start = b.y; u.q_len = b.z; u.kv_len = b.w;
-        u.merge_idx = -1; u.chunk_idx = 0; u.n_chunks = 1; u.pad = 0;
+        u.merge_idx = ui * Hkv + h; u.chunk_idx = part_idx; u.n_chunks = n_parts; u.pad = 0;
+        if (st_e >= 0) u.kv_end = u.kv_begin + st_e * kBN;
+        u.kv_begin += st_b * kBN;
       }
       const int ring_slot = k % kRingP;
       int wid_next = 0;
-      if (lane == 0) wid_next = atomicAdd(&p.header[kHdrPrefillQueue], 1);
+      if (!split && lane == 0) wid_next = atomicAdd(&p.header[kHdrPrefillQueue], 1);
       const int32_t* tab = p.block_tables + (size_t)u.seq * p.pages_per_seq;
       bool first = true;
       for (int pos = u.kv_begin; first || pos < u.kv_end; pos += kBN) {
@@ -232,16 +294,20 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           alive = false;
           break;
         }
-        // test hook: the stage is never announced, the waits for it must run out
-        const bool withhold = (p.test_withhold & 2) && wid == 0 && first;
+        // test hook: the stage's data is never announced (no arrival, no copies), so the waits for it must
+        // run out; the item itself is published as usual, so that every role sees a valid descriptor
+        const bool withhold = (p.test_withhold & 2) && first && (split ? (blockIdx.x == 0 && k == 0) : (wid == 0));
         if (withhold) ngrp = 0;
-        if (lane == 0 && !withhold) {
+        if (lane == 0) {
           if (first) {
             // every role is within NS + 2 items of this warp (the MMA warps through the stage ring, each
             // softmax group through q_full / skip of its MMA warp): slot k - kRingP is free
             ItemDescP d;
             d.u = u;
             d.h = h;
+            d.first_stage = first_stage;
+            d.quota = quota;
+            d.pad = 0;
             ring[ring_slot] = d;
             __threadfence_block();
             *items_pub = k + 1;
@@ -250,8 +316,12 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           const bool two = NT == 2 && u.q_len * G > u.row0 + kBM;
           metas[st] = make_int2(ring_slot | (first ? 0x100 : 0) | (two ? 0x200 : 0), pos);
           const uint32_t bytes = (uint32_t)ngrp * C::GROUP_BYTES;
-          if (bytes > 0) mbar_arrive_expect_tx(bar_kv_full(st), bytes);
-          else mbar_arrive(bar_kv_full(st));
+          if (withhold) {
+          } else if (bytes > 0) {
+            mbar_arrive_expect_tx(bar_kv_full(st), bytes);
+          } else {
+            mbar_arrive(bar_kv_full(st));
+          }
         }
         __syncwarp();
         if (lane < ngrp) {
@@ -262,7 +332,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         ++gi;
       }
       ++k;
-      wid = __shfl_sync(0xffffffffu, wid_next, 0);
+      if (!split) wid = __shfl_sync(0xffffffffu, wid_next, 0);
     }
     // wait (bounded) until every stage this warp filled has been released, i.e. all its bulk
     // copies have landed and been consumed
@@ -408,6 +478,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       }
       const Unit u = ring[k % kRingP].u;
       const int h = ring[k % kRingP].h;
+      const int first_stage = ring[k % kRingP].first_stage, quota = ring[k % kRingP].quota;
       ++k;
       if (u.seq < 0) break;
       int n_stages = (u.kv_end - u.kv_begin + kBN - 1) / kBN;
@@ -456,7 +527,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         // ---- the row's logits of the stage into registers; then the S columns are free for the
         // tile's next S MMA, which runs while this stage's exponentials are computed
         uint32_t sr[HB];
-  #pragma unroll
+#pragma unroll
         for (int c = 0; c + 32 <= HB; c += 32) tc_ld32(tm_s + c, *reinterpret_cast<uint32_t(*)[32]>(&sr[c]));
         static_assert(HB % 32 == 0, "S is read 32 columns at a time");
         tc_wait_ld();
@@ -474,19 +545,19 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         if (plain) {
           // max of scale*v is scale*max(v) or scale*min(v) depending on the sign of the scale
           float ext[4];
-  #pragma unroll
+#pragma unroll
           for (int a = 0; a < 4; ++a) ext[a] = __uint_as_float(sr[a]);
           if (p.scale_log2 >= 0.f) {
-  #pragma unroll
+#pragma unroll
             for (int i = 0; i < HB; i += 8)
-  #pragma unroll
+#pragma unroll
               for (int a = 0; a < 4; ++a)
                 ext[a] = fmax3(ext[a], __uint_as_float(sr[i + 2 * a]), __uint_as_float(sr[i + 2 * a + 1]));
             mx = fmaxf(fmaxf(ext[0], ext[1]), fmaxf(ext[2], ext[3])) * p.scale_log2;
           } else {
-  #pragma unroll
+#pragma unroll
             for (int i = 0; i < HB; i += 8)
-  #pragma unroll
+#pragma unroll
               for (int a = 0; a < 4; ++a)
                 ext[a] = fmin3(ext[a], __uint_as_float(sr[i + 2 * a]), __uint_as_float(sr[i + 2 * a + 1]));
             mx = fminf(fminf(ext[0], ext[1]), fminf(ext[2], ext[3])) * p.scale_log2;
@@ -494,7 +565,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         } else {
           mx = -INFINITY;
           e_scale = 1.f;
-  #pragma unroll
+#pragma unroll
           for (int i = 0; i < HB; ++i) {
             float xv = __uint_as_float(sr[i]);
             xv = (p.cap != 0.f) ? p.cap_log2 * soft_cap_tanh(xv * p.inv_cap_scale) : xv * p.scale_log2;
@@ -523,12 +594,12 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
             // previous P.V has completed (O is only touched between P.Vs)
             if (!mbar_wait(bar_pv_done(x, (ti - 1) & 1), ((ti - 1) >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
             tc_fence_after();
-  #pragma unroll 1
+#pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 16) {
               uint32_t o[16];
               tc_ld16(tm_o + c0, o);
               tc_wait_ld();
-  #pragma unroll
+#pragma unroll
               for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
               tc_st16(tm_o + c0, o);
             }
@@ -546,10 +617,10 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
         // probabilities, packed as 16-bit pairs, into the tile's P buffer of this stage
         float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
-  #pragma unroll
+#pragma unroll
         for (int c = 0; c < HB; c += 32) {
           uint32_t pk[16];
-  #pragma unroll
+#pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c + 2 * j]), e_scale, -m_use));
             const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 2 * j + 1]), e_scale, -m_use));
@@ -589,10 +660,99 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         if (lane == 0) mbar_arrive(bar_p_full(x, ti & 1));
 
         if (pos + kBN >= u.kv_end) {
-          // ---- last stage of the item: wait for its P.V, normalise, store ----
-          const float l_row = l_run;
+          // ---- last stage of the piece: wait for its P.V, then normalise and store, or (a part of a
+          // split item) publish the unnormalised part and, if it is the last to arrive, combine ----
           if (!mbar_wait(bar_pv_done(x, ti & 1), (ti >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
           tc_fence_after();
+          if (u.n_chunks > 1) {
+            // Slot of the part CTA c holds of this (item, head): a CTA has at most two parts, the item
+            // its quota begins in (slot 2c) and the item its quota ends in (slot 2c + 1).
+            auto slot_of = [&](int c) { return ((long long)first_stage <= (long long)c * quota) ? 2 * c : 2 * c + 1; };
+            const size_t mine = ((size_t)slot_of((int)blockIdx.x) * NT + x) * kBM + row;
+            if (row_ok) p.ppart_ml[mine] = make_float2(m_run, l_run);
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t o[32];
+              tc_ld32(tm_o + c0, o);
+              tc_wait_ld();
+              if (row_ok) {
+                float4* dst = reinterpret_cast<float4*>(p.ppart_o + mine * D + c0);
+#pragma unroll
+                for (int c = 0; c < 32; c += 4)
+                  dst[c >> 2] = make_float4(__uint_as_float(o[c]), __uint_as_float(o[c + 1]), __uint_as_float(o[c + 2]),
+                                            __uint_as_float(o[c + 3]));
+              }
+            }
+            tc_fence_before();
+            __threadfence();
+            __syncwarp();
+            int old = 0;
+            if (lane == 0) {
+              mbar_arrive(bar_o_free(x));
+              // one counter per 32-row quarter of the tile: the warps of a group never wait for each other
+              old = atomicAdd(&p.ptickets[((size_t)u.merge_idx * NT + x) * 4 + (warp & 3)], 1);
+            }
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == u.n_chunks - 1 && row_ok) {
+              // last part to arrive: combine the parts of this row, in part order (so the result does not
+              // depend on which part arrived last)
+              __threadfence();
+              const int c_first = first_stage / quota;
+              float m_tot = -INFINITY;
+              for (int pi = 0; pi < u.n_chunks; ++pi)
+                m_tot = fmaxf(m_tot, __ldcg(&p.ppart_ml[((size_t)slot_of(c_first + pi) * NT + x) * kBM + row]).x);
+              const float mu = (m_tot == -INFINITY) ? 0.f : m_tot;
+              float l_tot = 0.f;
+              for (int pi = 0; pi < u.n_chunks; ++pi) {
+                const float2 ml = __ldcg(&p.ppart_ml[((size_t)slot_of(c_first + pi) * NT + x) * kBM + row]);
+                l_tot += ml.y * fast_exp2(ml.x - mu);
+              }
+              float scl = 1.f, l_fin = l_tot;
+              if (p.num_sinks > 0) {
+                const int srow = (p.sink_rows == p.Hq) ? out_head : (p.sink_rows == Hkv ? h : 0);
+                const float* sk = p.sinks + (size_t)srow * p.num_sinks;
+                float sm = -INFINITY;
+                for (int i = 0; i < p.num_sinks; ++i) sm = fmaxf(sm, sk[i] * kLog2eP);
+                const float m_fin = fmaxf(m_tot, sm);
+                const float mf = (m_fin == -INFINITY) ? 0.f : m_fin;
+                scl = fast_exp2(m_tot - mf);
+                l_fin = l_tot * scl;
+                for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2eP - mf);
+              }
+              scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
+              T* orow = reinterpret_cast<T*>(p.out) + ((size_t)out_row_q * p.Hq + out_head) * D;
+#pragma unroll 1
+              for (int c0 = 0; c0 < D; c0 += 32) {
+                float acc[32];
+#pragma unroll
+                for (int c = 0; c < 32; ++c) acc[c] = 0.f;
+                for (int pi = 0; pi < u.n_chunks; ++pi) {
+                  const size_t at = ((size_t)slot_of(c_first + pi) * NT + x) * kBM + row;
+                  const float f = fast_exp2(__ldcg(&p.ppart_ml[at]).x - mu);
+                  const float4* src = reinterpret_cast<const float4*>(p.ppart_o + at * D + c0);
+#pragma unroll
+                  for (int c = 0; c < 32; c += 4) {
+                    const float4 v = __ldcg(src + (c >> 2));
+                    acc[c] += v.x * f;
+                    acc[c + 1] += v.y * f;
+                    acc[c + 2] += v.z * f;
+                    acc[c + 3] += v.w * f;
+                  }
+                }
+#pragma unroll
+                for (int c = 0; c < 32; c += 8) {
+                  uint4 v;
+                  v.x = Mma<T>::pack(acc[c] * scl, acc[c + 1] * scl);
+                  v.y = Mma<T>::pack(acc[c + 2] * scl, acc[c + 3] * scl);
+                  v.z = Mma<T>::pack(acc[c + 4] * scl, acc[c + 5] * scl);
+                  v.w = Mma<T>::pack(acc[c + 6] * scl, acc[c + 7] * scl);
+                  *reinterpret_cast<uint4*>(orow + c0 + c) = v;
+                }
+              }
+            }
+            continue;  // next stage = first stage of the next piece
+          }
+          const float l_row = l_run;
           float scl = 1.f, l_fin = l_row;
           if (p.num_sinks > 0 && row_ok) {
             // attention sinks join the denominator only (_xla_impl_fwd.py:161-172)
@@ -608,13 +768,13 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           }
           scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
           T* orow = reinterpret_cast<T*>(p.out) + ((size_t)out_row_q * p.Hq + out_head) * D;
-  #pragma unroll 1
+#pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {
             uint32_t o[32];
             tc_ld32(tm_o + c0, o);
             tc_wait_ld();
             if (row_ok) {
-  #pragma unroll
+#pragma unroll
               for (int c = 0; c < 32; c += 8) {
                 uint4 v;
                 v.x = Mma<T>::pack(__uint_as_float(o[c]) * scl, __uint_as_float(o[c + 1]) * scl);

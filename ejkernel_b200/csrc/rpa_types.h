@@ -51,11 +51,16 @@ enum HeaderWord {
   kHdrTotalKeys = 5,
   kHdrNumPrefill = 6,     // work items of the tcgen05 prefill-tile kernel
   kHdrPrefillQueue = 7,   // its work queue head
+  kHdrPrefillStages = 8,  // sum of the items' 64-token KV stages (per kv head)
   kHdrWords = 64,
 };
 
 struct WorkspaceLayout {
   size_t header_off, units_off, merge_off, part_o_off, part_ml_off, punits_off, tickets_off, total;
+  // optional tail, used when the caller's workspace has room for it (total_split bytes): prefill items are
+  // then cut along KV at CTA-quota boundaries and their parts combined by the part that finishes last
+  size_t pprefix_off, ptickets_off, ppart_ml_off, ppart_o_off, total_split;
+  int32_t ppart_slots;
   int32_t max_units, max_merge, max_slots, rows_per_tile, target_units, max_punits;
 };
 
@@ -73,6 +78,12 @@ struct Params {
   Unit* units;
   Unit* punits;    // prefill items: row0 is a multiple of prefill_item_rows, slot unused
   MergeItem* merge;
+  // KV split of prefill items (all null / 0 when off)
+  int32_t* pprefix;   // [num prefill items + 1] exclusive prefix of the items' stage counts, queue order
+  int32_t* ptickets;  // [items][Hkv][tiles][4 row quarters] arrival counters, zeroed by the planner
+  float2* ppart_ml;   // [2 * CTAs][tiles][128] (m, l) of a part
+  float* ppart_o;     // [2 * CTAs][tiles][128][D] unnormalised O of a part
+  int32_t prefill_split;
   int32_t* tickets; // [max_merge][Hkv] arrival counters of the chunks of one (tile, kv head); zeroed by the planner
   int32_t fused_merge; // 1: the split-KV kernel combines the chunks itself (last arriver), no merge kernel
   float* part_o;   // [max_slots][Hkv][rows_per_tile][D]

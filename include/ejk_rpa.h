@@ -51,7 +51,7 @@ extern "C" {
 #define EJK_RPA_E_SHAPE (-2)     /* a dimension is <= 0, Hq % Hkv != 0, ... */
 #define EJK_RPA_E_HEAD_DIM (-3)  /* head_dim not in {64, 128, 256} */
 #define EJK_RPA_E_DTYPE (-4)     /* unknown dtype code */
-#define EJK_RPA_E_WORKSPACE (-5) /* workspace smaller than ejk_rpa_workspace_bytes() / misaligned */
+#define EJK_RPA_E_WORKSPACE (-5) /* workspace smaller than ejk_rpa_workspace_bytes_min() / misaligned */
 #define EJK_RPA_E_ARG (-6)       /* sliding_window / logits_soft_cap / sinks out of contract */
 #define EJK_RPA_E_DEVICE (-7)    /* current device is not sm_100 class */
 #define EJK_RPA_E_ALIGN (-8)     /* a tensor base pointer is not 16-byte aligned */
@@ -109,6 +109,12 @@ EJK_RPA_API const char* ejk_rpa_error_string(int code);
  * (_xla_impl_fwd.py:113-114). */
 EJK_RPA_API size_t ejk_rpa_workspace_bytes(const ejk_rpa_shape* shape);
 
+/* The smallest workspace a launch accepts for this shape.  It is smaller than
+ * ejk_rpa_workspace_bytes() for shapes that can hold multi-token sequences: the difference is the
+ * room in which prefill items cut along KV park their parts (option "prefill_split"); with the
+ * smaller workspace those items are scheduled whole.  No reference counterpart. */
+EJK_RPA_API size_t ejk_rpa_workspace_bytes_min(const ejk_rpa_shape* shape);
+
 /* Enqueue one ragged paged attention call on `stream` (a cudaStream_t).
  * Replaces _ragged_paged_attention (_xla_impl_fwd.py:25-201) / ragged_paged_attention_triton_call
  * (_triton_impl_fwd.py:485-613).  `workspace` must be 256-byte aligned and hold
@@ -165,7 +171,7 @@ EJK_RPA_API int ejk_page_attention_launch(const void* query, const void* key_cac
  * the process exits.  The caller still passes every input, `out` and `status` exactly as for
  * ejk_rpa_launch.  The call itself performs no cudaMalloc / cudaFree and calls no allocating
  * library routine.
- *   - A shape whose ejk_rpa_workspace_bytes() exceeds the array is refused with
+ *   - A shape whose ejk_rpa_workspace_bytes_min() exceeds the array is refused with
  *     EJK_RPA_E_SCRATCH (roughly: decode batches up to a few hundred sequences fit, batches with
  *     thousands of prefill rows do not); nothing is launched in that case.
  *   - The first call on each device looks up the array's device address (a one-time set-up with
@@ -188,6 +194,9 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *   "path"       0 = auto, 1 = force the cp.async gather, 2 = force the TMA gather
  *   "prefill_rows" sequences with at least this many (query token, head-in-group) rows per kv head are
  *                served by 128-row tcgen05 tiles instead of 8-row split-KV tiles (default 64; 0 = never)
+ *   "prefill_split" 1 (default) = when the workspace has the size ejk_rpa_workspace_bytes reports, prefill items are
+ *                cut along KV at per-CTA quota boundaries and their parts combined by the last one to finish;
+ *                0 = whole items from a longest-first queue (also what a smaller workspace gets)
  *   "sort_items" 1 (default) = the planner queues split-KV work items longest first, 0 = in sequence order
  *   "overlap"    1 (default) = the kernels of one call are launched as programmatic dependents: each starts under
  *                the tail of the one before and waits on the device for what it needs; 0 = plain stream order

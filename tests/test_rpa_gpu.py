@@ -208,6 +208,40 @@ def test_tile_hints_change_the_partition_not_the_result(rpa_lib, tmp_path):
     assert_parity(kern.run(*bc.args(), **bc.kwargs(), cfg=best), want, b.total_tokens, what="tuned cfg")
 
 
+def test_prefill_items_split_along_kv(rpa_lib):
+    """With room in the workspace the tile kernel cuts the stage sequence of all (item, kv head) pairs
+    into one quota per CTA; items that straddle a quota boundary are finished by several CTAs and
+    combined by the part that arrives last, in part order.  Few long items (every one is split many
+    ways), many short ones, one-tile items, windows, sinks: all must match the oracle, repeat bitwise,
+    and agree with the unsplit schedule within the tolerance."""
+    from ejkernel_b200 import _cabi
+    cases = [
+        dict(q=[256], kv=[6000], hq=4, hkv=1, d=128, page=16, kw={}),                       # 4 long items -> 148 CTAs
+        dict(q=[512, 300], kv=[2048, 5000], hq=8, hkv=2, d=128, page=32, kw=dict(sliding_window=3000)),
+        dict(q=[40] * 12 + [1, 1], kv=[700 + 37 * i for i in range(12)] + [900, 50], hq=16, hkv=2, d=64, page=16, kw={}),
+        dict(q=[129, 500], kv=[129, 3100], hq=8, hkv=4, d=256, page=16, kw=dict(logits_soft_cap=30.0)),
+    ]
+    old = _cabi.get_option("prefill_split")
+    try:
+        for i, c in enumerate(cases):
+            b = make_ragged_batch(c["q"], c["kv"], num_q_heads=c["hq"], num_kv_heads=c["hkv"], head_dim=c["d"],
+                                  page_size=c["page"], seed=110 + i, **c["kw"])
+            if i == 1:
+                b.softmax_aux = torch.randn(c["hq"], 2, generator=torch.Generator().manual_seed(6))
+            want = oracle(b)
+            _cabi.set_option("prefill_split", 1)
+            outs = [run_cuda(b) for _ in range(3)]
+            assert status_word(b.to("cuda")) == 0
+            _cabi.set_option("prefill_split", 0)
+            whole = run_cuda(b)
+            assert_parity(outs[0], want, b.total_tokens, what=f"split case {i}")
+            assert_parity(whole, want, b.total_tokens, what=f"unsplit case {i}")
+            for o in outs[1:]:
+                assert torch.equal(o, outs[0]), i
+    finally:
+        _cabi.set_option("prefill_split", old)
+
+
 def test_overlapped_launches_equal_stream_order_bitwise(rpa_lib):
     """With programmatic dependent launches the prefill kernel starts under the planner's tail and the
     split-KV kernel runs beside the prefill kernel's last CTAs; the kernels write different rows, so

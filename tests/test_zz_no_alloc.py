@@ -59,7 +59,7 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row(rpa_lib):
     second = make_ragged_batch([1, 9, 1, 30, 1], [3000, 700, 64, 1500, 5], num_q_heads=8, num_kv_heads=2, head_dim=128,
                                page_size=16, seed=41, sliding_window=512, logits_soft_cap=30.0).to("cuda")
     for b in (first, second):
-        assert _cabi.load().ejk_rpa_workspace_bytes(ctypes.byref(_shape_of(b.queries, b.kv_pages, b.block_tables))) \
+        assert _cabi.load().ejk_rpa_workspace_bytes_min(ctypes.byref(_shape_of(b.queries, b.kv_pages, b.block_tables))) \
             <= _cabi.STATIC_SCRATCH_BYTES
         want = _reference_run(b)
         out = torch.zeros_like(b.queries)
@@ -77,7 +77,7 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row(rpa_lib):
 def test_static_scratch_refuses_shapes_beyond_its_maximum(rpa_lib):
     # thousands of query rows need far more partial slots than 32 MiB holds
     b = make_ragged_batch([3000], [3000], num_q_heads=32, num_kv_heads=8, head_dim=128, page_size=16, seed=1).to("cuda")
-    need = rpa_lib.ejk_rpa_workspace_bytes(ctypes.byref(_shape_of(b.queries, b.kv_pages, b.block_tables)))
+    need = rpa_lib.ejk_rpa_workspace_bytes_min(ctypes.byref(_shape_of(b.queries, b.kv_pages, b.block_tables)))
     assert need > _cabi.STATIC_SCRATCH_BYTES
     out = torch.full_like(b.queries, 7.0)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
