@@ -269,6 +269,20 @@ def test_overlapped_launches_equal_stream_order_bitwise(rpa_lib):
         _cabi.set_option("overlap", old)
 
 
+def test_more_sequences_than_the_planner_caches(rpa_lib):
+    """The planner keeps the lengths of the first 2048 sequences in shared memory between its passes
+    and re-reads the others from global memory; 2500 short sequences (a few of them multi-token, some
+    slots unused) go through both routes."""
+    rng = np.random.default_rng(77)
+    n = 2500
+    kv = [int(x) for x in rng.integers(1, 200, n)]
+    ql = [1] * n
+    for i in (3, 700, 2047, 2048, 2499):
+        ql[i] = min(kv[i], 5)
+    b = make_ragged_batch(ql, kv, num_q_heads=4, num_kv_heads=2, head_dim=64, page_size=16, seed=98, max_num_seqs=n + 7)
+    _check(b, "2500 sequences")
+
+
 def test_queue_order_does_not_change_results(rpa_lib):
     """The planner queues split-KV work items longest first (option ``sort_items``); inside a length
     bucket the order depends on atomics.  Every item writes its own rows or its own partial slot and
