@@ -539,10 +539,22 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         // (no cap, columns entirely visible to this row) keeps the raw dot products and folds the scale
         // into the exponent's FMA; everything else materialises the transformed, masked logits first.
         const bool full_vis = (pos + HB - 1 <= pos_row) && (pos > lo_row);
-        const bool plain = full_vis && p.cap == 0.f;
+        // Without a soft cap the raw dot products stay in the registers and the scale is folded into the
+        // exponent's FMA; keys the row must not see are replaced by the infinity that scales to -inf
+        // (stages on the causal diagonal, window edges, the tail of the last page: common in the first
+        // chunk of a prompt, where every stage is such a stage for some rows).
+        const bool raw = p.cap == 0.f && p.scale_log2 != 0.f;
         float e_scale = p.scale_log2;  // p = exp2(v * e_scale - m)
         float mx;
-        if (plain) {
+        if (raw) {
+          if (!full_vis) {
+            const uint32_t gone = __float_as_uint(p.scale_log2 > 0.f ? -INFINITY : INFINITY);
+            const int hi_i = pos_row - pos;  // last visible column of the stage
+            const int lo_i = lo_row - pos;   // columns up to here are left of the window
+#pragma unroll
+            for (int i = 0; i < HB; ++i)
+              if (i > hi_i || i <= lo_i) sr[i] = gone;
+          }
           // max of scale*v is scale*max(v) or scale*min(v) depending on the sign of the scale
           float ext[4];
 #pragma unroll
