@@ -115,7 +115,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 // Bounded wait, executed by all 32 lanes of a warp.  Gives up when `timeout_ns` of wall time have
-// passed or when another warp of the CTA has raised `abort_flag`; the verdict is made
+// passed or when another warp of the CTA has raised `abort_flag`; the outcome is made
 // warp-uniform so the lanes never part ways on it.  false = gave up (the flag is then set).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned long long timeout_ns) {

@@ -651,7 +651,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
           }
         }
         // The next item's writes to mbuf/lbuf come before its first consumer_sync, but they only
-        // race with readers of mbuf/lbuf, and those finished before round 0's sync above; its
+        // race with readers of mbuf/lbuf, and those finished before the first combine step's sync above; its
         // writes to obuf/row_* come after its first consumer_sync, which every warp reaches only
         // after finishing the loops above.
       }
