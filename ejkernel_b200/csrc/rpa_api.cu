@@ -158,7 +158,8 @@ size_t ejk_rpa_workspace_bytes(const ejk_rpa_shape* shape) {
 static int launch_impl(const void* queries, const void* kv_pages, const void* value_cache, const int32_t* context_lens,
                        const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                        const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
-                       int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
+                       int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream,
+                       int kv_dim = 0) {
   t_last_launches = 0;
   if (!queries || !kv_pages || !context_lens || !block_tables || !out || !workspace || !shape || !attrs)
     return EJK_RPA_E_NULL;
@@ -216,6 +217,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.Hkv = s.num_kv_heads;
   p.G = s.num_q_heads / s.num_kv_heads;
   p.D = s.head_dim;
+  p.Dkv = kv_dim > 0 ? kv_dim : s.head_dim;
   p.rows_per_tile = L.rows_per_tile;
   p.max_units = L.max_units;
   p.max_merge = L.max_merge;
@@ -354,16 +356,18 @@ int ejk_rpa_v3_launch(const void* queries, const void* keys, const void* values,
                       const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
   if (!keys || !values || !kv_cache || !distribution) return EJK_RPA_E_NULL;
   if (int e = check_shape(shape)) return e;
-  if (shape->head_dim % 128 != 0) return EJK_RPA_E_HEAD_DIM;  // the v3 cache pads head_dim to 128: only unpadded rows are read here
+  // the v3 cache pads head_dim to a multiple of 128 (align_to(D, 128), _kernel.py:45-57); the page write
+  // zero-fills the padding like merge_kv does and the attention kernels step over it
+  const int d_align = (shape->head_dim + 127) / 128 * 128;
   if ((reinterpret_cast<uintptr_t>(keys) | reinterpret_cast<uintptr_t>(values)) & 15) return EJK_RPA_E_ALIGN;
   const int32_t* num_seqs = distribution + 2;  // distribution = (decode_end, prefill_end, num_seqs), _kernel.py:211
   cudaError_t ce = launch_kv_update(keys, values, kv_cache, kv_lens, block_tables, query_start_loc, num_seqs, status,
                                     shape->total_tokens, shape->max_num_seqs, shape->pages_per_seq, shape->num_pages,
-                                    shape->page_size, shape->num_kv_heads, shape->head_dim, shape->head_dim,
+                                    shape->page_size, shape->num_kv_heads, shape->head_dim, d_align,
                                     static_cast<cudaStream_t>(stream));
   if (ce != cudaSuccess) return static_cast<int>(ce);
-  const int rc = ejk_rpa_launch(queries, kv_cache, kv_lens, block_tables, query_start_loc, num_seqs, nullptr, out, workspace,
-                                workspace_bytes, status, shape, attrs, stream);
+  const int rc = launch_impl(queries, kv_cache, nullptr, kv_lens, block_tables, query_start_loc, num_seqs, nullptr, out,
+                             workspace, workspace_bytes, status, shape, attrs, stream, d_align);
   if (rc == 0) ++t_last_launches;
   return rc;
 }

@@ -121,8 +121,9 @@ rpa_splitkv_kernel(const Params p) {
     constexpr int ITERS = TK * CPT / kThreads;
     const uint32_t sbase = smem_base + slot * C::STAGE_BYTES;
     const int32_t* tab = p.block_tables + (size_t)c.u.seq * p.pages_per_seq;
-    const size_t tok_stride = (size_t)2 * Hkv * D * sizeof(T);
-    const uint8_t* kvb = reinterpret_cast<const uint8_t*>(p.kv) + (size_t)(2 * c.h) * D * sizeof(T);
+    const size_t head_stride = (size_t)p.Dkv * sizeof(T);  // K_h and V_h are one (possibly padded) row apart
+    const size_t tok_stride = (size_t)2 * Hkv * head_stride;
+    const uint8_t* kvb = reinterpret_cast<const uint8_t*>(p.kv) + (size_t)(2 * c.h) * head_stride;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       const int cidx = tid + i * kThreads;
@@ -144,7 +145,8 @@ rpa_splitkv_kernel(const Params p) {
           flags |= EJK_RPA_ST_PAGE_ID;
           page = 0;
         }
-        src = kvb + ((size_t)page * p.page_size + sl) * tok_stride + within * 16;
+        src = kvb + ((size_t)page * p.page_size + sl) * tok_stride + (within / (D / 8)) * head_stride +
+              (within % (D / 8)) * 16;
       }
       const int kvsel = within / (D / 8), d16 = within % (D / 8);
       const int row = (kvsel * (D / 64) + (d16 >> 3)) * TK + tok;

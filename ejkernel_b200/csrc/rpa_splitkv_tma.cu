@@ -726,14 +726,14 @@ cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_
   EncodeFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
   const uint64_t esz = 2;
-  const uint64_t D = p.D, C2 = 2ull * p.Hkv;
+  const uint64_t D = p.D, Dkv = p.Dkv, C2 = 2ull * p.Hkv;
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   const CUtensorMapDataType dt = (dtype == EJK_RPA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap map, map_v;
   if (p.v_cache == nullptr) {
     // dims, innermost first: 64 elements | token in page | 64-element chunk of D | combined head | page
     cuuint64_t dims[5] = {64, (cuuint64_t)p.page_size, D / 64, C2, (cuuint64_t)p.num_pages};
-    cuuint64_t strides[4] = {C2 * D * esz, 64 * esz, D * esz, (cuuint64_t)p.page_size * C2 * D * esz};
+    cuuint64_t strides[4] = {C2 * Dkv * esz, 64 * esz, Dkv * esz, (cuuint64_t)p.page_size * C2 * Dkv * esz};
     cuuint32_t box[5] = {64, (cuuint32_t)p.tma_block_tokens, (cuuint32_t)(D / 64), 2, 1};
     CUresult r = enc(&map, dt, 5, const_cast<void*>(p.kv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -94,6 +94,8 @@ struct Params {
   int32_t max_units, max_merge, max_slots, target_units, min_chunk;
   int32_t max_punits;
   int32_t prefill_item_rows; // rows one prefill work item covers (128 per tile, 1 or 2 tiles per CTA)
+  int32_t Dkv;               // elements between consecutive combined heads of kv_pages (head_dim, or the padded
+                             // head_dim of a v3 cache)
   int32_t sort_items;        // 1: split-KV work items are queued longest first, 0: in sequence order
   int32_t test_withhold;     // test hook: bit 0 / bit 1 = the CTA of the split-KV / prefill kernel that takes work item 0
                              // never announces the item's first KV stage, so that the waits on it run out

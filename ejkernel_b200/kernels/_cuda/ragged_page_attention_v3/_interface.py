@@ -17,9 +17,9 @@ semantics of its kernel (ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.
     (:262-263, :290-291).  ``q_scale`` divides the queries before they are cast to the cache dtype and
     multiplies the logits back (:249-265); with a 16-bit cache that only changes rounding and is folded away.
 
-The cache is updated IN PLACE and returned (the reference donates it, :141).  Only ``head_dim`` that is
-a multiple of 128 is supported: the reference pads other head dims to 128 inside the cache, and padded
-caches are not read by the kernels here.  There is no CPU fallback.
+The cache is updated IN PLACE and returned (the reference donates it, :141).  A ``head_dim`` that is not
+a multiple of 128 lives in a cache padded to one (``align_to(D, 128)``, :45-57): the page write zero-fills
+the padding of the rows it writes, the attention kernels step over it.  There is no CPU fallback.
 """
 
 from __future__ import annotations
@@ -85,8 +85,6 @@ def ragged_page_attention_v3(
         raise ValueError("packing mismatch")
     if d_align != -(-D // 128) * 128:
         raise ValueError("cache last dim must be align_to(D,128)")
-    if d_align != D:
-        raise NotImplementedError(f"head_dim={D} is padded to {d_align} inside the v3 cache; only multiples of 128 are supported")
     if hx2_per_pack * pack != 2 * Hkv:
         raise NotImplementedError("a cache whose combined-head axis is padded beyond 2*num_kv_heads is not supported")
     S_max = kv_lens.shape[0]

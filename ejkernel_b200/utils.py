@@ -299,13 +299,16 @@ def make_workload(
     return b
 
 
-def to_v3_inputs(batch: RaggedBatch, fill: float = float("nan")):
+def to_v3_inputs(batch: RaggedBatch, fill: float = float("nan"), pad_fill: float = 3.0):
     """Recast a ``ragged_page_attention`` batch as inputs of ``ragged_page_attention_v3``.
 
     The new key/value rows of the step are the last ``q_len`` tokens of every sequence, taken out of
     the batch's (complete) pool; in the returned cache those positions hold ``fill`` so that the
     operator's page write is observable.  Returns ``(keys, values, kv_cache_5d, block_tables_flat,
-    distribution)``; after a correct v3 call the cache equals ``batch.kv_pages`` bit for bit.
+    distribution)``; after a correct v3 call the cache equals ``batch.kv_pages`` bit for bit.  When
+    ``head_dim`` is not a multiple of 128 the cache's last dim is padded to one, as the reference pads it;
+    the padding lanes start as ``pad_fill`` (the operator must step over them when it reads and zero
+    them in the rows it writes).
     Layout as in the reference's ``merge_kv`` / cache (ragged_page_attention_v3/_kernel.py:45-57).
     """
     m = batch.meta
@@ -329,7 +332,12 @@ def to_v3_inputs(batch: RaggedBatch, fill: float = float("nan")):
         values[cu[s] : cu[s] + ql] = rows[:, 1::2]
         cache[pages, slots] = fill
     pack = 32 // (pool.element_size() * 8)
-    cache5 = cache.view(pool.shape[0], page, 2 * Hkv // pack, pack, D)
+    d_align = -(-D // 128) * 128
+    if d_align != D:
+        padded = torch.full((*cache.shape[:-1], d_align), pad_fill, dtype=cache.dtype, device=dev)
+        padded[..., :D] = cache
+        cache = padded
+    cache5 = cache.view(pool.shape[0], page, 2 * Hkv // pack, pack, d_align)
     S = len(m["q_lens"])
     distribution = torch.tensor([S, S, S], dtype=torch.int32, device=dev)
     return keys, values, cache5, batch.block_tables.reshape(-1).contiguous(), distribution

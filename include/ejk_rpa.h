@@ -131,11 +131,12 @@ EJK_RPA_API int ejk_rpa_launch(const void* queries, const void* kv_pages, const 
  * Replaces ragged_paged_attention of ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:143-318:
  * `keys` / `values` are [total_tokens, num_kv_heads, head_dim]; row r of sequence s goes to cache
  * position kv_len - q_len + r (:227-229); `kv_cache` is updated IN PLACE (the reference donates it,
- * :141) and is the reference's [num_pages, page_size, 2*Hkv/pack, pack, head_dim] array, whose
- * bytes are those of the [num_pages, page_size, 2*Hkv, head_dim] layout of ejk_rpa_launch;
- * `block_tables` is the same table flattened; `distribution` is int32[3] whose last entry is the
- * number of sequences (:211).  head_dim must be a multiple of 128 (the reference pads it to one;
- * padded caches are not supported).  Everything else as ejk_rpa_launch (no sinks in v3). */
+ * :141) and is the reference's [num_pages, page_size, 2*Hkv/pack, pack, align_to(head_dim, 128)]
+ * array, whose bytes are those of the [num_pages, page_size, 2*Hkv, head_dim] layout of
+ * ejk_rpa_launch when head_dim is a multiple of 128; otherwise the rows are padded to the next
+ * multiple (:45-57): the page write zero-fills the padding of the rows it writes and the attention
+ * kernels step over it.  `block_tables` is the same table flattened; `distribution` is int32[3] whose
+ * last entry is the number of sequences (:211).  Everything else as ejk_rpa_launch (no sinks in v3). */
 EJK_RPA_API int ejk_rpa_v3_launch(const void* queries, const void* keys, const void* values, void* kv_cache,
                                   const int32_t* kv_lens, const int32_t* block_tables,
                                   const int32_t* query_start_loc, const int32_t* distribution, void* out,

@@ -312,8 +312,10 @@ def v3_reference(
         for r in range(q1 - q0):
             pos = kl - (q1 - q0) + r
             flat[int(tab[s, pos // page]), pos % page, : 2 * Hkv, : k.shape[2]] = fused[q0 + r]
+            flat[int(tab[s, pos // page]), pos % page, : 2 * Hkv, k.shape[2] :] = 0  # merge_kv pads with zeros (:45-57)
     scale = float(softmax_scale) * (1.0 if k_scale is None else float(k_scale))
-    out = dense_reference(queries, flat, ctx, tab, cu, np.array([S]), softmax_scale=scale,
+    # the cache's last dim is align_to(D, 128); attention reads the first D lanes (:240-241)
+    out = dense_reference(queries, flat[..., : k.shape[2]], ctx, tab, cu, np.array([S]), softmax_scale=scale,
                           sliding_window=sliding_window, logits_soft_cap=logits_soft_cap, precision=precision)
     if v_scale is not None:
         out = out * float(v_scale)

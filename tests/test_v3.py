@@ -17,8 +17,33 @@ def _cases():
     yield "mixed", make_ragged_batch([1, 40, 3, 130], [500, 40, 77, 900], num_q_heads=8, num_kv_heads=2, head_dim=128,
                                      page_size=16, seed=62, sliding_window=256, logits_soft_cap=30.0)
     yield "d256", make_ragged_batch([2, 70], [100, 300], num_q_heads=4, num_kv_heads=2, head_dim=256, page_size=32, seed=63)
+    # head_dim 64: the cache's last dim is padded to 128 (align_to(D, 128), _kernel.py:45-57)
+    yield "d64_padded", make_ragged_batch([1, 33, 2, 90], [700, 33, 130, 400], num_q_heads=8, num_kv_heads=2, head_dim=64,
+                                          page_size=16, seed=65, sliding_window=300)
+    # ... and with a page size the TMA gather cannot express (cp.async gather)
+    yield "d64_padded_page24", make_ragged_batch([1, 20], [333, 100], num_q_heads=4, num_kv_heads=2, head_dim=64,
+                                                 page_size=24, seed=66)
     yield "empty_seq", make_ragged_batch([1, 0, 5], [50, 20, 5], num_q_heads=4, num_kv_heads=4, head_dim=128, page_size=8,
                                          max_num_seqs=5, pad_query_rows=3, seed=64)
+
+
+@pytest.mark.parametrize("name,b", list(_cases()), ids=[n for n, _ in _cases()])
+def _check_cache(new_cache, old_cache, b):
+    """First head_dim lanes: the complete pool, bit for bit.  Padding lanes (head_dim not a multiple of 128):
+    zero in the rows the call wrote (merge_kv pads with zeros), untouched elsewhere."""
+    P, page, C2, D = b.kv_pages.shape
+    flat = new_cache.reshape(P, page, C2, -1)
+    assert torch.equal(flat[..., :D], b.kv_pages), "page write must be bit-exact"
+    if flat.shape[-1] != D:
+        pad_new, pad_old = flat[..., D:].float(), old_cache.reshape(P, page, C2, -1)[..., D:].float()
+        written = torch.zeros(P, page, dtype=torch.bool, device=flat.device)
+        m = b.meta
+        for s_, (ql, kl) in enumerate(zip(m["q_lens"], m["kv_lens"])):
+            if ql:
+                pos = torch.arange(kl - ql, kl, device=flat.device)
+                written[b.block_tables[s_, (pos // page).long()].long(), (pos % page).long()] = True
+        assert torch.count_nonzero(pad_new[written]) == 0
+        assert torch.equal(pad_new[~written], pad_old[~written])
 
 
 @pytest.mark.parametrize("name,b", list(_cases()), ids=[n for n, _ in _cases()])
@@ -27,7 +52,7 @@ def test_oracle_v3_restores_the_pool_and_matches_v1(name, b):
     out, new_cache = v3_reference(b.queries, keys, values, cache, b.context_lens, tab_flat, b.query_start_loc, dist,
                                   softmax_scale=b.softmax_scale, sliding_window=b.sliding_window,
                                   logits_soft_cap=b.logits_soft_cap)
-    assert torch.equal(new_cache.view(b.kv_pages.shape), b.kv_pages)
+    _check_cache(new_cache, cache, b)
     want = dense_reference(*b.args(), **b.kwargs())
     np.testing.assert_allclose(out, want, atol=1e-12)
     # scales: k_scale multiplies the logits, v_scale the output (_kernel.py:262-263,290-291)
@@ -60,12 +85,13 @@ def test_cuda_v3_matches_oracle_and_restores_the_pool(rpa_lib, name, b):
     bc = b.to("cuda")
     keys, values, cache, tab_flat, dist = to_v3_inputs(bc)
     assert torch.isnan(cache.float()).any()
+    before = cache.clone()
     out, new_cache = ej.ragged_page_attention_v3(bc.queries, keys, values, cache, bc.context_lens, tab_flat,
                                                  bc.query_start_loc, dist, softmax_scale=b.softmax_scale,
                                                  sliding_window=b.sliding_window, logits_soft_cap=b.logits_soft_cap)
     torch.cuda.synchronize()
     assert new_cache.data_ptr() == cache.data_ptr(), "the cache is updated in place"
-    assert torch.equal(new_cache.view(bc.kv_pages.shape), bc.kv_pages), "page write must be bit-exact"
+    _check_cache(new_cache, before, bc)
     assert_parity(out, dense_reference(*b.args(), **b.kwargs()), b.total_tokens, what=f"v3 {name}")
     assert torch.count_nonzero(out[b.total_tokens:]) == 0
 
@@ -84,7 +110,3 @@ def test_cuda_v3_scales_and_full_size_decode(rpa_lib):
     assert torch.equal(new_cache.view(b.kv_pages.shape), b.kv_pages)
     # same kernels on the same bytes: v3 with folded scales reproduces v1 exactly (x2 is exact in bf16)
     assert torch.equal(out, ref * 2.0)
-    with pytest.raises((ValueError, NotImplementedError)):  # head_dim 64 would need a cache padded to 128
-        b64 = make_ragged_batch([1], [10], num_q_heads=4, num_kv_heads=2, head_dim=64, page_size=8, seed=1).to("cuda")
-        k, v, c, t, d = to_v3_inputs(b64)
-        ej.ragged_page_attention_v3(b64.queries, k, v, c, b64.context_lens, t, b64.query_start_loc, d)
