@@ -262,8 +262,8 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.wait_timeout_ms = g_opt.wait_ms;
   p.test_withhold = g_opt.test_withhold;
   p.sort_items = g_opt.sort_items;
-  const bool use_tma = value_cache || (g_opt.path == 2) || (g_opt.path == 0 && tma_path_supported(p));
-  if (use_tma && !tma_path_supported(p)) return value_cache ? EJK_RPA_E_SHAPE : EJK_RPA_E_ARG;
+  const bool use_tma = (g_opt.path == 2) || (g_opt.path == 0 && tma_path_supported(p));
+  if (use_tma && !tma_path_supported(p)) return EJK_RPA_E_ARG;
   // Batches that can hold a sequence with many query rows also get the tcgen05 prefill-tile
   // kernel; whether any sequence actually qualifies is decided by the planner on the device.
   const bool use_prefill = use_tma && prefill_rows > 0 && prefill_path_supported(p) &&

@@ -145,8 +145,14 @@ rpa_splitkv_kernel(const Params p) {
           flags |= EJK_RPA_ST_PAGE_ID;
           page = 0;
         }
-        src = kvb + ((size_t)page * p.page_size + sl) * tok_stride + (within / (D / 8)) * head_stride +
-              (within % (D / 8)) * 16;
+        if (p.v_cache == nullptr) {
+          src = kvb + ((size_t)page * p.page_size + sl) * tok_stride + (within / (D / 8)) * head_stride +
+                (within % (D / 8)) * 16;
+        } else {
+          // separate caches [blocks, Hkv, block_size, D] (page_attention): K from one, V from the other
+          const uint8_t* base = reinterpret_cast<const uint8_t*>((within / (D / 8)) ? p.v_cache : p.kv);
+          src = base + ((((size_t)page * Hkv + c.h) * p.page_size + sl) * D) * sizeof(T) + (within % (D / 8)) * 16;
+        }
       }
       const int kvsel = within / (D / 8), d16 = within % (D / 8);
       const int row = (kvsel * (D / 64) + (d16 >> 3)) * TK + tok;

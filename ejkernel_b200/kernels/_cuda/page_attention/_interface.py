@@ -13,7 +13,8 @@ it).  ``max_context_len``, ``num_splits``, ``mask_value``, ``pages_per_compute_b
 split of long contexts is chosen on the device.
 
 It runs the same split-KV kernels as ``ragged_page_attention`` through a tensor map over the split
-layout (``ejk_page_attention_launch``); ``block_size`` must be a power of two >= 8.  A sequence
+layout (``ejk_page_attention_launch``); a ``block_size`` that is not a power of two >= 8 goes through
+the cp.async gather instead (slower).  A sequence
 with ``context_len == 0`` yields zeros (the reference's softmax over all-masked scores would average
 stale blocks).  There is no CPU fallback.
 """
@@ -63,8 +64,6 @@ def page_attention(
         raise ValueError(f"num_heads={Hq} must be divisible by num_kv_heads={Hkv}")
     if D not in (64, 128, 256):
         raise NotImplementedError(f"head_dim={D} is not supported by the CUDA path (64, 128, 256)")
-    if block_size < 8 or block_size & (block_size - 1):
-        raise NotImplementedError(f"block_size={block_size} must be a power of two >= 8 for the CUDA path")
     if context_lens.dtype != torch.int32 or block_tables.dtype != torch.int32:
         raise ValueError("context_lens and block_tables must be int32")
     if attn_logits_soft_cap is not None and attn_logits_soft_cap == 0.0:

@@ -150,7 +150,7 @@ EJK_RPA_API int ejk_rpa_v3_launch(const void* queries, const void* keys, const v
  * Triton split-KV + reduce version ejkernel/kernels/_triton/page_attention/_interface.py:88-369).  Same
  * kernels as ejk_rpa_launch with a different tensor map: every sequence has one query row that sees all
  * keys below its context length.  `shape`: total_tokens = max_num_seqs = num_seqs, pages_per_seq =
- * max_blocks, num_pages = num_blocks, page_size = block_size (a power of two >= 8, else EJK_RPA_E_SHAPE).
+ * max_blocks, num_pages = num_blocks, page_size = block_size (a power of two >= 8 for the TMA gather; any other size takes the cp.async gather).
  * `attrs`: softmax_scale = attn_scale, logits_soft_cap = attn_logits_soft_cap (0 = none); the rest 0. */
 EJK_RPA_API int ejk_page_attention_launch(const void* query, const void* key_cache, const void* value_cache,
                                           const int32_t* context_lens, const int32_t* block_tables, void* out,

@@ -33,7 +33,8 @@ def test_oracle_page_attention_agrees_with_ragged_oracle():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("page,hq,hkv,d", [(16, 8, 2, 128), (8, 8, 4, 64), (32, 16, 8, 256), (64, 4, 4, 128), (16, 32, 2, 128)])
+@pytest.mark.parametrize("page,hq,hkv,d", [(16, 8, 2, 128), (8, 8, 4, 64), (32, 16, 8, 256), (64, 4, 4, 128), (16, 32, 2, 128),
+                                           (4, 8, 2, 128), (24, 8, 4, 64), (1, 4, 2, 128)])  # the last three: cp.async gather
 def test_cuda_page_attention_matches_oracle(rpa_lib, page, hq, hkv, d):
     import ejkernel_b200 as ej
 
@@ -68,10 +69,11 @@ def test_cuda_page_attention_reference_test_shapes_soft_cap_and_errors(rpa_lib):
     assert_parity(out, want, 2, what="page_attention soft cap")
     zero = ej.page_attention(bc.queries, kcb.cuda(), vcb.cuda(), torch.zeros(2, dtype=torch.int32, device="cuda"), bc.block_tables)
     assert torch.count_nonzero(zero) == 0
-    with pytest.raises(NotImplementedError):
-        ej.page_attention(q, kc[:, :, :4].contiguous(), vc[:, :, :4].contiguous(),
-                          torch.tensor([4, 4], dtype=torch.int32, device="cuda"),
-                          torch.tensor([[0], [1]], dtype=torch.int32, device="cuda"))
+    # block_size 4 (not expressible as a TMA box): still all ones
+    small = ej.page_attention(q, kc[:, :, :4].contiguous(), vc[:, :, :4].contiguous(),
+                              torch.tensor([4, 4], dtype=torch.int32, device="cuda"),
+                              torch.tensor([[0], [1]], dtype=torch.int32, device="cuda"))
+    assert torch.equal(small, torch.ones_like(small))
     with pytest.raises(ValueError):
         ej.page_attention(q, kc, vc, torch.tensor([48, 32], device="cuda"),
                           torch.tensor([[0, 1, 2, 3], [4, 5, 6, 7]], dtype=torch.int32, device="cuda"))
