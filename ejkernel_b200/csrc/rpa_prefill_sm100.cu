@@ -86,12 +86,13 @@ struct CfgP {
   static constexpr int OFF_RING = OFF_KV + NS * STAGE_BYTES;
   static constexpr int OFF_META = OFF_RING + kRingP * (int)sizeof(ItemDescP);
   static constexpr int OFF_BAR = OFF_META + NS * 8;
-  // barriers: kv_full[NS] kv_empty[NS], then per tile: s_full s_free p_full[2] pv_done[2] q_full o_free skip turn
-  static constexpr int BAR_PER_TILE = 10;
+  // barriers: kv_full[NS] kv_empty[NS], then per tile: s_full s_free p_full[2] pv_done[2] q_full o_free turn
+  static constexpr int BAR_PER_TILE = 9;
   static constexpr int N_BAR = 2 * NS + NT * BAR_PER_TILE;
   static constexpr int OFF_TMEM = OFF_BAR + N_BAR * 8;
-  static constexpr int OFF_ABORT = OFF_TMEM + 8;   // abort flag, then the published-items counter
-  static constexpr int SMEM_BYTES = OFF_ABORT + 8 + 1024;
+  // abort flag, the published-items counter, per tile the count of items its softmax warps have skipped
+  static constexpr int OFF_ABORT = OFF_TMEM + 8;
+  static constexpr int SMEM_BYTES = OFF_ABORT + 8 + 4 * NT + 1024;
   static constexpr uint32_t P_COLS = BN / 2;               // one P buffer (16-bit pairs)
   static constexpr uint32_t TMEM_S = 0;                    // S_x at x*BN
   static constexpr uint32_t TMEM_P = NT * BN;              // P_x[b] at 2*BN + (2x + b)*P_COLS
@@ -115,6 +116,10 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   int2* metas = reinterpret_cast<int2*>(smem + C::OFF_META);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT);
   volatile int* items_pub = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT + 4);  // items in the ring so far
+  // skipped[x]: one count per softmax warp of tile x and item without rows for the tile.  A counter, not an
+  // mbarrier: the group is not held back by anybody while it skips items, so it can be several items
+  // ahead of the role that waits for it, and a phase parity would alias.
+  volatile int* skipped = reinterpret_cast<volatile int*>(smem + C::OFF_ABORT + 8);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_TMEM);
   const uint32_t bar0 = sb + C::OFF_BAR;
   auto bar_kv_full = [&](int s) { return bar0 + s * 8; };
@@ -126,8 +131,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   auto bar_pv_done = [&](int x, int b) { return tile_bar(x, 4 + b); };  // P_x.V(t) complete (commit): buffer t&1 is free
   auto bar_q_full = [&](int x) { return tile_bar(x, 6); };
   auto bar_o_free = [&](int x) { return tile_bar(x, 7); };
-  auto bar_skip = [&](int x) { return tile_bar(x, 8); };      // the 4 warps have seen an item without rows for tile x
-  auto bar_turn = [&](int x) { return tile_bar(x, 9); };      // tile x has issued the exponentials of a stage
+  auto bar_turn = [&](int x) { return tile_bar(x, 8); };      // tile x has issued the exponentials of a stage
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int Hkv = p.Hkv, G = p.G;
@@ -149,7 +153,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       }
       mbar_init(bar_q_full(x), C::SM_WARPS);
       mbar_init(bar_o_free(x), C::SM_WARPS);
-      mbar_init(bar_skip(x), C::SM_WARPS);
+      skipped[x] = 0;
       mbar_init(bar_turn(x), C::SM_WARPS);
     }
     *abort_flag = 0;
@@ -186,17 +190,21 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     // boundary is finished by several CTAs, whose parts the last one to arrive combines.
     // A part costs a pipeline restart, a 64-128 KB round trip of its unnormalised O through the
     // workspace and the combine (measured: 15-25 stages' worth per CTA), so the split is used only where
-    // the dynamic schedule is clearly worse: rounds * average item > 1.15 * (quota + 16 stages), e.g. 160
+    // the dynamic schedule is clearly worse: rounds * average item > 1.15 * (quota + 16 stages), with a
+    // quota of at least 8 stages, e.g. 160
     // equal items on 148 CTAs (0.289 -> 0.203 ms), not 128 or 256 of them, nor short items.
     const int n_items = p.header[kHdrNumPrefill];
     const long long W = (long long)p.header[kHdrPrefillStages] * Hkv;
+    constexpr int kMinQuota = 8;  // a part shorter than this is all overhead
     bool split = p.prefill_split && W > 0 && W < (1ll << 30);
+    long long quota_ll = (W + gridDim.x - 1) / gridDim.x;
+    if (quota_ll < kMinQuota) quota_ll = kMinQuota;
     if (split) {
       const long long U = (long long)n_items * Hkv, Cn = gridDim.x;
       const long long rounds = (U + Cn - 1) / Cn;
-      split = rounds * W * Cn * 20 >= 23 * U * (W + 16 * Cn);
+      split = rounds * W * 20 >= 23 * U * (quota_ll + 16);  // rounds * W / U >= 1.15 * (quota + 16)
     }
-    const int quota = split ? (int)((W + gridDim.x - 1) / gridDim.x) : 0;
+    const int quota = split ? (int)quota_ll : 0;
     long long g = (long long)blockIdx.x * quota;                 // next global stage of this CTA
     const long long g_end = (g + quota < W) ? g + quota : W;
     int it = 0;                                                  // item that contains stage g
@@ -301,7 +309,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         if (lane == 0) {
           if (first) {
             // every role is within NS + 2 items of this warp (the MMA warps through the stage ring, each
-            // softmax group through q_full / skip of its MMA warp): slot k - kRingP is free
+            // softmax group through q_full or its skip count): slot k - kRingP is free
             ItemDescP d;
             d.u = u;
             d.h = h;
@@ -389,8 +397,20 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         if (!act) {  // the item has no rows for this tile: only this role's share of the stage's release
           if (first && is_s) {
             // ... once the tile's softmax group has seen the item, so that it never falls behind
-            if (!mbar_wait_thread(bar_skip(x), skips & 1, abort_flag, wait_ns)) break;
             ++skips;
+            bool seen = skipped[x] >= C::SM_WARPS * skips;
+            if (!seen) {
+              const unsigned long long t0 = global_timer_ns();
+              while (!(seen = skipped[x] >= C::SM_WARPS * skips)) {
+                if (*abort_flag) break;
+                if (global_timer_ns() - t0 > wait_ns) {
+                  *abort_flag = 1;
+                  break;
+                }
+                __nanosleep(64);
+              }
+            }
+            if (!seen) break;
           }
           mbar_arrive(bar_kv_empty(st));
           ++gi;
@@ -487,7 +507,10 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       const bool active = (x == 0) || two;
       if (!active) {  // the item has no rows for this tile
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_skip(x));
+        if (lane == 0) {
+          __threadfence_block();  // the ring entry has been read
+          atomicAdd(const_cast<int*>(&skipped[x]), 1);
+        }
         gi += n_stages;
         continue;
       }

@@ -242,6 +242,42 @@ def test_prefill_items_split_along_kv(rpa_lib):
         _cabi.set_option("prefill_split", old)
 
 
+def test_idle_tile_with_short_pieces_many_launches(rpa_lib):
+    """Items with rows for one tile only leave the CTA's second tile idle; its softmax warps then skip
+    whole items without waiting for anybody and can be several items ahead of the MMA role that checks
+    on them -- whenever pieces are shorter than the stage ring: a quota that begins a stage or two
+    before an item's end (KV split), or a queue of one-stage items (dynamic schedule).  How far ahead
+    depends on timing, so every case is launched many times; each launch must leave the status word
+    clean (no wait may run out) and repeat the first bitwise."""
+    from ejkernel_b200 import _cabi
+    cases = [
+        # 32 (item, head) pairs of 79 stages, quota 18: CTAs 57 and 136 begin 1 stage before an item's end
+        dict(q=[16] * 4, kv=[5000] * 4, hq=32, hkv=8, d=128, split=1),
+        # 32 pairs of 313 stages, quota 68: CTA 23 begins 1 stage before an item's end
+        dict(q=[16] * 4, kv=[20000] * 4, hq=32, hkv=8, d=128, split=1),
+        # 1200 pairs of one stage each on the dynamic queue
+        dict(q=[16] * 300, kv=[40 + (i % 24) for i in range(300)], hq=16, hkv=4, d=64, split=0),
+    ]
+    old = (_cabi.get_option("prefill_split"), _cabi.get_option("wait_ms"))
+    try:
+        _cabi.set_option("wait_ms", 200)
+        for i, c in enumerate(cases):
+            b = make_ragged_batch(c["q"], c["kv"], num_q_heads=c["hq"], num_kv_heads=c["hkv"], head_dim=c["d"],
+                                  page_size=16, seed=140 + i)
+            bc = b.to("cuda")
+            _cabi.set_option("prefill_split", c["split"])
+            first = run_cuda(bc)
+            assert status_word(bc) == 0, i
+            assert_parity(first, oracle(b), b.total_tokens, what=f"idle tile case {i}")
+            for rep in range(40):
+                again = run_cuda(bc)
+                assert status_word(bc) == 0, (i, rep)
+                assert torch.equal(again, first), (i, rep)
+    finally:
+        _cabi.set_option("prefill_split", old[0])
+        _cabi.set_option("wait_ms", old[1])
+
+
 def test_overlapped_launches_equal_stream_order_bitwise(rpa_lib):
     """With programmatic dependent launches the prefill kernel starts under the planner's tail and the
     split-KV kernel runs beside the prefill kernel's last CTAs; the kernels write different rows, so
