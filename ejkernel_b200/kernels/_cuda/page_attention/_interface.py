@@ -24,19 +24,18 @@ from __future__ import annotations
 import ctypes
 import math
 
-import jaxtyping
 import torch
-from beartype import beartype
 from jaxtyping import Float, Int
 from torch import Tensor as Array
 
 from .... import _cabi
+from .._typecheck import typechecked_once
 from ..._registry import Backend, Platform, kernel_registry
 from ..ragged_page_attention._interface import _DTYPE_CODE, RpaWorkspace, _workspace_cache
 
 
 @kernel_registry.register("page_attention", Platform.CUDA, Backend.GPU)
-@jaxtyping.jaxtyped(typechecker=beartype)
+@typechecked_once
 def page_attention(
     query: Float[Array, "num_seqs num_heads head_dim"],
     key_cache: Float[Array, "num_blocks num_kv_heads block_size head_dim"],

@@ -30,13 +30,12 @@ from __future__ import annotations
 import ctypes
 import math
 
-import jaxtyping
 import torch
-from beartype import beartype
 from jaxtyping import Float, Int
 from torch import Tensor as Array
 
 from .... import _cabi
+from .._typecheck import typechecked_once
 from ..._registry import Backend, Platform, kernel_registry
 
 DTypeLike = torch.dtype | str | None
@@ -250,7 +249,7 @@ def ragged_page_attention_static_scratch_into(
 
 
 @kernel_registry.register("ragged_page_attention", Platform.CUDA, Backend.GPU)
-@jaxtyping.jaxtyped(typechecker=beartype)
+@typechecked_once
 def ragged_page_attention(
     queries: Float[Array, "total_tokens num_q_heads head_dim"],
     kv_pages: Float[Array, "num_pages page_size num_combined_kv_heads head_dim"],

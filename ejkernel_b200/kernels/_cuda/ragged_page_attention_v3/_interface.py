@@ -26,13 +26,12 @@ from __future__ import annotations
 
 import ctypes
 
-import jaxtyping
 import torch
-from beartype import beartype
 from jaxtyping import Float, Int32
 from torch import Tensor as Array
 
 from .... import _cabi
+from .._typecheck import typechecked_once
 from ..._registry import Backend, Platform, kernel_registry
 from ..ragged_page_attention._interface import _DTYPE_CODE, RpaWorkspace, _workspace_cache
 
@@ -42,7 +41,7 @@ def _packing(dtype: torch.dtype) -> int:
 
 
 @kernel_registry.register("ragged_page_attention_v3", Platform.CUDA, Backend.GPU)
-@jaxtyping.jaxtyped(typechecker=beartype)
+@typechecked_once
 def ragged_page_attention_v3(
     queries: Float[Array, "total_tokens num_q_heads head_dim"],
     keys: Float[Array, "total_tokens num_kv_heads head_dim"],
