@@ -15,8 +15,10 @@
 //     hold S_x(j) in registers (one tcgen05.ld) they release the S columns and the tile's S issuer
 //     puts S_x(j+1) on the pipe while the exponentials of stage j are computed; P_x(j) goes to
 //     buffer j & 1, so it never waits for P_x.V(j-1) either.
-//   * S and P.V of each tile are issued by different warps (four single-thread issuing roles), so
-//     that no role's waits delay another's MMAs.
+//   * S of each tile and the P.V products are issued by different warps (three single-thread issuing
+//     roles), so that no role's waits delay another's MMAs.  One thread issues P.V for both tiles:
+//     their P arrive in turn anyway, and with 12 warps instead of 13 a thread gets 168 registers
+//     instead of 128 (the register file is handed out to a CTA in units of four warps).
 //   * the two tiles' softmax warps share the schedulers and the MUFU unit (4 exponentials per cycle
 //     and scheduler); they take turns at the exponentials, so that one tile's waits and TMEM
 //     traffic overlap the other's MUFU phase instead of both phases running in lockstep.
@@ -27,7 +29,7 @@
 // row maxima costs more than the shorter rows save), 80/96/128-token stages with P aliased on S
 // (the tile's S -> softmax -> P.V chain then bounds the stage).
 //
-// Warp roles (416 threads with two tiles, one CTA per SM, persistent over the planner's prefill queue):
+// Warp roles (384 threads with two tiles, one CTA per SM, persistent over the planner's prefill queue):
 //   warp 0        TMA producer: one box {64 elems, 8 tokens, D/64, (K_h, V_h)} per 8-token group,
 //                 SWIZZLE_128B, 8 boxes per stage, page ids from the block table; publishes every
 //                 item in a ring.  No multicast.
@@ -35,7 +37,7 @@
 //   warps 2-5     softmax of tile 0, warps 6-9 of tile 1: thread = TMEM lane = tile row; the row's
 //                 logits of the stage sit in registers; lazy rescaling of O (only when the maximum
 //                 grows by more than 2^8), normalisation, sinks, store.
-//   warps 10-12   S issuer of tile 1, P.V issuers of tiles 0 and 1 (one tile: warp 6 issues P.V)
+//   warps 10-11   S issuer of tile 1, P.V issuer of both tiles (one tile: warp 6 issues P.V)
 //
 // All hand-offs are mbarriers; every wait is bounded in wall time (Params::wait_timeout_ms): on
 // expiry the warp raises the CTA's abort flag, every other wait gives up when it sees it, the status
@@ -75,7 +77,8 @@ struct CfgP {
   static constexpr int NT = (D <= 128) ? 2 : 1;       // 128-row tiles per CTA (TMEM holds one 256-column O)
   static constexpr int SM_WARPS = 4;                  // softmax warps per tile: one thread per row
   // producer, S issuer of tile 0, softmax groups, the other issuers
-  static constexpr int THREADS = 64 + 32 * SM_WARPS * NT + 32 * (2 * NT - 1);
+  // (the register file is handed out in units of four warps: 12 warps get 168 registers each, 13 only 128)
+  static constexpr int THREADS = 64 + 32 * SM_WARPS * NT + 32 * NT;
   static constexpr int STAGE_BYTES = BN * 2 * D * 2;
   static constexpr int NS = (D == 64) ? 8 : (D == 128) ? 4 : 2;
   static constexpr int GROUP_BYTES = 8 * 2 * D * 2;   // one 8-token group: [K|V][D/64][8][64]
@@ -141,7 +144,8 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(bar_kv_full(s), 1);
-      // released by the four MMA-issuing roles (commit, or a plain arrival when the tile is idle)
+      // released by the MMA-issuing roles, once per tile for S and once for P.V (commit, or a plain arrival
+      // when the tile is idle)
       mbar_init(bar_kv_empty(s), 2 * NT);
     }
     for (int x = 0; x < NT; ++x) {
@@ -359,17 +363,17 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     }
   } else if (warp == 1 || warp >= 2 + C::SM_WARPS * NT) {
     // =============================== MMA issuers ===============================
-    // Four single-thread roles: S and P.V of each tile are issued by different warps.  An issuing
+    // Single-thread roles: S of each tile and P.V (of both tiles) are issued by different warps.  An issuing
     // thread spends most of a stage on latency (an mbarrier poll or a shared-memory read costs it
     // 100+ cycles while the tensor pipe and the TMA unit stream through shared memory, a
     // tcgen05.mma 50-150), so one thread issuing S and P.V for a tile, or worse for both tiles,
     // becomes the bottleneck of the whole CTA.  No ordering between the roles is needed beyond the
     // barriers: S_x(t+1) only needs the S columns back (s_free), P_x.V(t) only P_x(t) (p_full).
     if (lane == 0) {
-      // roles in the order S_0 .. S_{NT-1}, PV_0 .. PV_{NT-1}; S_0 is warp 1, the others follow the softmax warps
+      // roles in the order S_0 .. S_{NT-1}, PV; S_0 is warp 1, the others follow the softmax warps
       const int role = (warp == 1) ? 0 : warp - (2 + C::SM_WARPS * NT) + 1;
       const bool is_s = role < NT;
-      const int x = is_s ? role : role - NT;
+      const int x = is_s ? role : 0;
       constexpr uint32_t idesc_s = instr_desc<T>(kBN, false);
       constexpr uint32_t idesc_pv = instr_desc<T>(D, true);
       // hi word of a descriptor: stride byte offset >> 4, version 1 (bit 46), SWIZZLE_128B (bits 61-63)
@@ -380,14 +384,57 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       // V is MN-major: leading byte offset = distance between 64-element chunks of D (1024 B)
       const uint64_t v_desc0 = kHiGroup | (uint64_t)(((sb + C::OFF_KV + C::V_OFF) >> 4) | ((1024u >> 4) << 16));
       const uint32_t tm_s = tmem_base + C::TMEM_S + x * kBN;
-      const uint32_t tm_p = tmem_base + C::TMEM_P + x * 2 * C::P_COLS;
-      const uint32_t tm_o = tmem_base + C::TMEM_O + x * D;
 
       int gi = 0;     // KV stage counter (every role sees the same stage sequence)
       int t = 0;      // stages this tile took part in (barrier parities)
       int items = 0;  // items this tile took part in
       int skips = 0;  // items this tile had no rows for
-      while (true) {
+      int tx[NT], itemsx[NT];  // the same two counters per tile, for the P.V role
+#pragma unroll
+      for (int y = 0; y < NT; ++y) tx[y] = itemsx[y] = 0;
+      while (!is_s) {
+        // ---- P.V of all tiles, tile 0 first (the order in which the tiles take their turns at the
+        // exponentials, so P_0(t) is ready before P_1(t), and P_0(t+1) only after that) ----
+        const int st = gi % NS;
+        if (!mbar_wait_thread(bar_kv_full(st), (gi / NS) & 1, abort_flag, wait_ns)) break;
+        const int mx = metas[st].x;
+        if (mx < 0) break;
+        const bool first = (mx & 0x100) != 0;
+        bool gave_up = false;
+#pragma unroll
+        for (int y = 0; y < NT; ++y) {
+          if (gave_up) continue;
+          if (y > 0 && !(mx & 0x200)) {  // no rows for this tile: only its share of the stage's release
+            mbar_arrive(bar_kv_empty(st));
+            continue;
+          }
+          if (first) ++itemsx[y];
+          const int ty = tx[y];
+          // O_y (+)= P_y . V: P_y(t) must be in its TMEM buffer; the first P.V of an item overwrites
+          // O_y, which the previous item's epilogue must have read
+          if (!mbar_wait_thread(bar_p_full(y, ty & 1), (ty >> 1) & 1, abort_flag, wait_ns) ||
+              (first && itemsx[y] > 1 && !mbar_wait_thread(bar_o_free(y), itemsx[y] & 1, abort_flag, wait_ns))) {
+            gave_up = true;
+            continue;
+          }
+          tc_fence_after();
+          const uint32_t tm_p = tmem_base + C::TMEM_P + y * 2 * C::P_COLS;
+          const uint32_t tm_o = tmem_base + C::TMEM_O + y * D;
+          const uint64_t vd = v_desc0 + (uint64_t)((st * C::STAGE_BYTES) >> 4);
+#pragma unroll
+          for (int kk = 0; kk < kBN / 16; ++kk) {
+            // V: 16 tokens = two 8-token groups per MMA; P: 16 tokens = 8 columns of 16-bit pairs
+            tc_mma_ts(tm_o, tm_p + (ty & 1) * C::P_COLS + kk * 8, vd + (uint64_t)((kk * 2 * C::GROUP_BYTES) >> 4), idesc_pv,
+                      !(first && kk == 0));
+          }
+          tc_commit(bar_pv_done(y, ty & 1));
+          tc_commit(bar_kv_empty(st));  // this tile's P.V MMAs that read the stage have been issued
+          ++tx[y];
+        }
+        if (gave_up) break;
+        ++gi;
+      }
+      while (is_s) {
         const int st = gi % NS;
         if (!mbar_wait_thread(bar_kv_full(st), (gi / NS) & 1, abort_flag, wait_ns)) break;
         const int mx = metas[st].x;
@@ -395,7 +442,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         const bool first = (mx & 0x100) != 0;
         const bool act = (x == 0) || (mx & 0x200) != 0;
         if (!act) {  // the item has no rows for this tile: only this role's share of the stage's release
-          if (first && is_s) {
+          if (first) {
             // ... once the tile's softmax group has seen the item, so that it never falls behind
             ++skips;
             bool seen = skipped[x] >= C::SM_WARPS * skips;
@@ -417,7 +464,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
           continue;
         }
         if (first) ++items;
-        if (is_s) {
+        {
           // the new query tile must be in shared memory, and S_x of the previous stage in the
           // softmax warps' registers
           if (first && !mbar_wait_thread(bar_q_full(x), (items - 1) & 1, abort_flag, wait_ns)) break;
@@ -432,20 +479,6 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
             tc_mma(tm_s, q_desc + qoff, kd + koff, idesc_s, kk > 0);
           }
           tc_commit(bar_s_full(x));
-        } else {
-          // O_x (+)= P_x . V: P_x(t) must be in its TMEM buffer; the first P.V of an item overwrites
-          // O_x, which the previous item's epilogue must have read
-          if (!mbar_wait_thread(bar_p_full(x, t & 1), (t >> 1) & 1, abort_flag, wait_ns)) break;
-          if (first && items > 1 && !mbar_wait_thread(bar_o_free(x), items & 1, abort_flag, wait_ns)) break;
-          tc_fence_after();
-          const uint64_t vd = v_desc0 + (uint64_t)((st * C::STAGE_BYTES) >> 4);
-#pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) {
-            // V: 16 tokens = two 8-token groups per MMA; P: 16 tokens = 8 columns of 16-bit pairs
-            tc_mma_ts(tm_o, tm_p + (t & 1) * C::P_COLS + kk * 8, vd + (uint64_t)((kk * 2 * C::GROUP_BYTES) >> 4), idesc_pv,
-                      !(first && kk == 0));
-          }
-          tc_commit(bar_pv_done(x, t & 1));
         }
         tc_commit(bar_kv_empty(st));  // this role's MMAs that read the stage have been issued
         ++t;
