@@ -18,7 +18,8 @@
 //   * S of each tile and the P.V products are issued by different warps (three single-thread issuing
 //     roles), so that no role's waits delay another's MMAs.  One thread issues P.V for both tiles:
 //     their P arrive in turn anyway, and with 12 warps instead of 13 a thread gets 168 registers
-//     instead of 128 (the register file is handed out to a CTA in units of four warps).
+//     instead of 128 (each of the SM's four schedulers has its own 16 K registers and the warps
+//     are dealt round to them: a thirteenth warp puts four warps on one scheduler).
 //   * the two tiles' softmax warps share the schedulers and the MUFU unit (4 exponentials per cycle
 //     and scheduler); they take turns at the exponentials, so that one tile's waits and TMEM
 //     traffic overlap the other's MUFU phase instead of both phases running in lockstep.
@@ -77,7 +78,7 @@ struct CfgP {
   static constexpr int NT = (D <= 128) ? 2 : 1;       // 128-row tiles per CTA (TMEM holds one 256-column O)
   static constexpr int SM_WARPS = 4;                  // softmax warps per tile: one thread per row
   // producer, S issuer of tile 0, softmax groups, the other issuers
-  // (the register file is handed out in units of four warps: 12 warps get 168 registers each, 13 only 128)
+  // (16 K registers per scheduler: with 12 warps, three per scheduler, a thread gets 168; with 13 only 128)
   static constexpr int THREADS = 64 + 32 * SM_WARPS * NT + 32 * NT;
   static constexpr int STAGE_BYTES = BN * 2 * D * 2;
   static constexpr int NS = (D == 64) ? 8 : (D == 128) ? 4 : 2;
