@@ -500,12 +500,35 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     const uint32_t tm_s = tmem_base + lane_addr + C::TMEM_S + x * kBN;
     const uint32_t tm_p0 = tmem_base + lane_addr + C::TMEM_P + x * 2 * C::P_COLS;
     const uint32_t tm_o = tmem_base + lane_addr + C::TMEM_O + x * D;
-    uint8_t* q_smem = smem + C::OFF_Q + x * C::Q_BYTES;
     int gi = 0;   // KV stage counter (all roles see the same stage sequence)
     int ti = 0;   // stages this tile took part in
     int k = 0;    // item counter (all roles see the same item sequence)
     int pc = 0;   // stages in which both tiles took part (the tiles take turns at the exponentials)
     bool alive = true;
+    // The query row of an item (K-major, 128B swizzle) goes from global to shared memory with cp.async,
+    // no registers in between, so that the row of the NEXT item can be fetched under the last stage of
+    // the current one: the tile's query buffer is free as soon as the item's last S has completed, and
+    // with the row in place the S issuer starts the next item while this thread is still in the epilogue.
+    const uint32_t q_row_smem = sb + C::OFF_Q + x * C::Q_BYTES + (uint32_t)row * 128;
+    auto q_issue = [&](const Unit& uu, int hh) {
+      const int R = uu.row0 + x * kBM + row;
+      const bool ok = R < uu.q_len * G;
+      const int qt = R / G, g = R - qt * G;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(p.q);
+      if (ok) src += ((size_t)(uu.q_start + qt) * p.Hq + hh * G + g) * D * sizeof(T);
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c)
+        cp_async16(q_row_smem + (uint32_t)(c >> 3) * (kBM * 128) + (uint32_t)(((c & 7) ^ (row & 7)) << 4),
+                   ok ? src + c * 16 : src, ok ? 16 : 0);  // rows past the item's end are zero-filled
+      cp_async_commit();
+    };
+    auto q_finish = [&]() {
+      cp_async_wait<0>();
+      fence_async_smem();  // the MMA reads the tile through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_q_full(x));
+    };
+    bool q_ready = false;    // this item's query row was fetched during the previous item
     // The group follows the item sequence through the producer's item ring (a counter says how many
     // items have been published; an mbarrier parity could alias, because a group whose tile is idle
     // skips whole items) and counts stages itself, so that per stage it waits only for S.
@@ -558,22 +581,13 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       const int pos_row = row_ok ? (u.kv_len - u.q_len + qt) : -1;
       const int lo_row = (p.window > 0) ? pos_row - p.window : -1;
       float m_run = -INFINITY, l_run = 0.f;
-      {
+      if (!q_ready) {
         // all S MMAs of this tile's previous item completed before its last s_full fired, which
         // this thread waited for, so the query tile may be overwritten
-        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) +
-                                                          ((size_t)out_row_q * p.Hq + out_head) * D * sizeof(T));
-#pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
-          uint4 v = make_uint4(0u, 0u, 0u, 0u);
-          if (row_ok) v = __ldg(src + c);
-          const uint32_t off = (uint32_t)(c >> 3) * (kBM * 128) + (uint32_t)row * 128 + (uint32_t)(((c & 7) ^ (row & 7)) << 4);
-          *reinterpret_cast<uint4*>(q_smem + off) = v;
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_q_full(x));
+        q_issue(u, h);
+        q_finish();
       }
+      q_ready = false;
       for (int js = 0; js < n_stages; ++js, ++gi, ++ti) {
         const int st = gi % NS;
         const int pos = u.kv_begin + js * kBN;  // first key of the stage
@@ -729,9 +743,24 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
         if (lane == 0) mbar_arrive(bar_p_full(x, ti & 1));
 
         if (pos + kBN >= u.kv_end) {
-          // ---- last stage of the piece: wait for its P.V, then normalise and store, or (a part of a
-          // split item) publish the unnormalised part and, if it is the last to arrive, combine ----
+          // ---- last stage of the piece.  All S of the item completed long ago, so the tile's query
+          // buffer is free: fetch the next item's query row (if the producer has published that item
+          // already; it normally has, it runs stages ahead) under the wait for the last P.V ...
+          bool q_pending = *items_pub > k;
+          q_pending = __all_sync(0xffffffffu, q_pending);
+          if (q_pending) {
+            __threadfence_block();
+            const Unit un = ring[k % kRingP].u;
+            q_pending = un.seq >= 0 && (x == 0 || un.q_len * G > un.row0 + kBM);
+            if (q_pending) q_issue(un, ring[k % kRingP].h);
+          }
+          // ---- ... wait for the P.V, then normalise and store, or (a part of a split item) publish the
+          // unnormalised part and, if it is the last to arrive, combine ----
           if (!mbar_wait(bar_pv_done(x, ti & 1), (ti >> 1) & 1, abort_flag, wait_ns)) { alive = false; break; }
+          if (q_pending) {  // the next item's first S runs while this one's epilogue does
+            q_finish();
+            q_ready = true;
+          }
           tc_fence_after();
           if (u.n_chunks > 1) {
             // Slot of the part CTA c holds of this (item, head): a CTA has at most two parts, the item
@@ -861,6 +890,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       }
     }
   }
+  cp_async_wait<0>();  // a query row fetched ahead when a wait ran out
   if (*abort_flag) flags |= EJK_RPA_ST_TIMEOUT;
   // every role has left its loop (all waits are bounded), so the TMEM can go back
   tc_fence_before();
