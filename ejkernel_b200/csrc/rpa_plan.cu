@@ -291,25 +291,7 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
           pu + cnt[3] > p.max_punits) {
         flags |= EJK_RPA_ST_INTERNAL;
       } else if (si.prefill) {
-        for (int t = 0; t < si.tiles && n_prefill_total <= p.max_punits; ++t) {
-          int lo, hi;
-          tile_range(p, si, t, lo, hi, p.prefill_item_rows);
-          Unit un;
-          un.seq = s;
-          un.row0 = t * p.prefill_item_rows;
-          un.kv_begin = lo;
-          un.kv_end = hi;
-          un.slot = -1;
-          un.q_start = si.q_start;
-          un.q_len = si.q_len;
-          un.kv_len = si.kv_len;
-          un.merge_idx = -1;
-          un.chunk_idx = 0;
-          un.n_chunks = 1;
-          un.pad = 0;
-          store_unit(&p.punits[atomicAdd(&s_bucket[bucket_of(lo, hi)], 1)], un);
-        }
-        (void)pu;
+        (void)pu;  // prefill items are queued by the ordered pass below
       } else {
         for (int t = 0; t < si.tiles; ++t) {
           int lo, hi, n, cs;
@@ -350,6 +332,65 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
     }
 #pragma unroll
     for (int k = 0; k < kCnt; ++k) base[k] += total[k];
+  }
+  // ---- prefill items into their queue, in an order that does not depend on thread timing: the KV split
+  // of the tile kernel cuts the items in queue order, so the order decides where partial sums are
+  // combined and therefore the last bit of the result.  One warp walks the sequences 32 at a time;
+  // lanes whose items fall into the same length bucket take consecutive positions in lane order.
+  if (p.prefill_min_rows > 0 && n_prefill_total > 0 && n_prefill_total <= p.max_punits && base[3] <= p.max_punits) {
+    if (tid < 32) {
+      const int lane = tid;
+      for (int s0 = 0; s0 < S; s0 += 32) {
+        const int s = s0 + lane;
+        SeqInfo si;
+        si.ok = false;
+        si.prefill = false;
+        si.tiles = 0;
+        unsigned f = 0;
+        if (s < S) si = load_seq(p, s, f, s_seq, false);
+        const int tiles = (si.ok && si.prefill) ? si.tiles : 0;
+        int max_t = tiles;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const int other = __shfl_xor_sync(0xffffffffu, max_t, o);
+          max_t = other > max_t ? other : max_t;
+        }
+        for (int t = 0; t < max_t; ++t) {
+          const bool have = t < tiles;
+          int lo = 0, hi = 0, b = -1 - lane;  // lanes without an item match nobody
+          if (have) {
+            tile_range(p, si, t, lo, hi, p.prefill_item_rows);
+            b = bucket_of(lo, hi);
+          }
+          const unsigned same = __match_any_sync(0xffffffffu, b);
+          if (have) {
+            const int leader = __ffs(same) - 1;
+            int pos = 0;
+            if (lane == leader) {
+              pos = s_bucket[b];
+              s_bucket[b] = pos + __popc(same);
+            }
+            pos = __shfl_sync(same, pos, leader) + __popc(same & ((1u << lane) - 1u));
+            Unit un;
+            un.seq = s;
+            un.row0 = t * p.prefill_item_rows;
+            un.kv_begin = lo;
+            un.kv_end = hi;
+            un.slot = -1;
+            un.q_start = si.q_start;
+            un.q_len = si.q_len;
+            un.kv_len = si.kv_len;
+            un.merge_idx = -1;
+            un.chunk_idx = 0;
+            un.n_chunks = 1;
+            un.pad = 0;
+            store_unit(&p.punits[pos], un);
+          }
+          __syncwarp();  // the next round's leaders read the cursors this round's leaders moved
+        }
+      }
+    }
+    __syncthreads();
   }
   // arrival counters of the fused merge start at zero on every call
   {

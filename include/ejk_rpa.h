@@ -194,7 +194,7 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *   "min_chunk"  smallest KV chunk, in tokens, a split may have (default 256)
  *   "path"       0 = auto, 1 = force the cp.async gather, 2 = force the TMA gather
  *   "prefill_rows" sequences with at least this many (query token, head-in-group) rows per kv head are
- *                served by 128-row tcgen05 tiles instead of 8-row split-KV tiles (default 64; 0 = never)
+ *                served by 128-row tcgen05 tiles instead of 8-row split-KV tiles (default 32; 0 = never)
  *   "prefill_split" 1 (default) = when the workspace has the size ejk_rpa_workspace_bytes reports, prefill items are
  *                cut along KV at per-CTA quota boundaries and their parts combined by the last one to finish;
  *                0 = whole items from a longest-first queue (also what a smaller workspace gets)

@@ -278,6 +278,23 @@ def test_idle_tile_with_short_pieces_many_launches(rpa_lib):
         _cabi.set_option("wait_ms", old[1])
 
 
+def test_prefill_queue_order_does_not_depend_on_thread_timing(rpa_lib):
+    """The KV split cuts the prefill items in queue order, so the order in which the planner queues
+    items of one length bucket decides where partial sums are combined.  Many multi-token sequences
+    with nearly equal lengths (one bucket, different stage counts), launched repeatedly: every
+    launch must repeat the first bit for bit."""
+    for i, (hq, hkv, d) in enumerate([(1, 1, 256), (8, 2, 128), (16, 4, 64)]):
+        n = 39
+        b = make_ragged_batch([33 + (j * 7) % 30 for j in range(n)], [900 + 37 * ((j * 11) % n) for j in range(n)],
+                              num_q_heads=hq, num_kv_heads=hkv, head_dim=d, page_size=16, seed=150 + i)
+        bc = b.to("cuda")
+        first = run_cuda(bc)
+        assert status_word(bc) == 0
+        assert_parity(first, oracle(b), b.total_tokens, what=f"reproducible queue case {i}")
+        for rep in range(12):
+            assert torch.equal(run_cuda(bc), first), (i, rep)
+
+
 def test_overlapped_launches_equal_stream_order_bitwise(rpa_lib):
     """With programmatic dependent launches the prefill kernel starts under the planner's tail and the
     split-KV kernel runs beside the prefill kernel's last CTAs; the kernels write different rows, so
