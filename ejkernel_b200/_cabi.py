@@ -38,6 +38,7 @@ EXPORTS = (
     "ejk_rpa_get_option",
     "ejk_rpa_last_launch_count",
     "ejk_rpa_profile_read",
+    "ejk_rpa_profile_read_kernels",
     "ejk_rpa_launch_static_scratch",
     "ejk_rpa_v3_launch",
     "ejk_page_attention_launch",
@@ -67,6 +68,7 @@ class Attrs(Structure):
         ("sink_rows", c_int32),
         ("num_kv_pages_per_block", c_int32),
         ("num_queries_per_block", c_int32),
+        ("out_scale", c_float),
     ]
 
 
@@ -154,6 +156,8 @@ def load() -> ctypes.CDLL:
     ]
     lib.ejk_rpa_profile_read.restype = c_int
     lib.ejk_rpa_profile_read.argtypes = [POINTER(c_float), POINTER(c_float), POINTER(c_float)]
+    lib.ejk_rpa_profile_read_kernels.restype = c_int
+    lib.ejk_rpa_profile_read_kernels.argtypes = [POINTER(c_float)] * 4
     _lib = lib
     return lib
 
@@ -182,6 +186,13 @@ def profile_read() -> tuple[float, float, float]:
     a, b, c = c_float(0), c_float(0), c_float(0)
     check(load().ejk_rpa_profile_read(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)), "profile_read")
     return a.value, b.value, c.value
+
+
+def profile_read_kernels() -> tuple[float, float, float, float]:
+    """(planner, prefill-tile kernel, split-KV kernel, merge) device milliseconds of this thread's last profiled launch."""
+    v = [c_float(0) for _ in range(4)]
+    check(load().ejk_rpa_profile_read_kernels(*[ctypes.byref(x) for x in v]), "profile_read_kernels")
+    return tuple(x.value for x in v)
 
 
 def decode_status(word: int) -> list[str]:

@@ -26,7 +26,8 @@ static ffi::Error EjkRpaSm100Impl(cudaStream_t stream, ffi::AnyBuffer queries, f
                                   ffi::Buffer<ffi::F32> softmax_aux,  // shape [rows, 0] when absent
                                   ffi::Result<ffi::AnyBuffer> out, ffi::Result<ffi::Buffer<ffi::U8>> workspace,
                                   ffi::Result<ffi::Buffer<ffi::S32>> status, float softmax_scale,
-                                  float logits_soft_cap, int32_t sliding_window) {
+                                  float logits_soft_cap, int32_t sliding_window, int32_t num_kv_pages_per_block,
+                                  int32_t num_queries_per_block) {
   const auto qd = queries.dimensions();
   const auto kd = kv_pages.dimensions();
   const auto td = block_tables.dimensions();
@@ -53,6 +54,16 @@ static ffi::Error EjkRpaSm100Impl(cudaStream_t stream, ffi::AnyBuffer queries, f
   const auto ad = softmax_aux.dimensions();
   attrs.num_sinks = ad.size() == 2 ? static_cast<int32_t>(ad[1]) : 0;
   attrs.sink_rows = ad.size() == 2 ? static_cast<int32_t>(ad[0]) : 0;
+  attrs.num_kv_pages_per_block = num_kv_pages_per_block;  // tile hints of RaggedPageAttentionConfig, 0 = auto
+  attrs.num_queries_per_block = num_queries_per_block;
+  // the scratch result must be what ejk_rpa_workspace_bytes() asked for: say so here, by name, instead of
+  // letting the launch answer with a bare error code
+  if (workspace->size_bytes() < ejk_rpa_workspace_bytes_min(&shape) ||
+      (reinterpret_cast<uintptr_t>(workspace->typed_data()) & 255))
+    return ffi::Error::InvalidArgument(
+        "ragged_page_attention[cuda]: the workspace result must hold ejk_rpa_workspace_bytes(shape) bytes, 256-byte aligned");
+  // `out` is a fresh, uninitialised XLA buffer: the launch itself writes every row of it (rows past the last
+  // sequence are zero-filled by the kernels), so no memset is needed here
   // the status word is a fresh result buffer: clear it on the stream before the kernels OR bits in
   cudaMemsetAsync(status->typed_data(), 0, sizeof(int32_t), stream);
   const int rc = ejk_rpa_launch(queries.untyped_data(), kv_pages.untyped_data(), context_lens.typed_data(),
@@ -79,5 +90,7 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(EjkRpaSm100, EjkRpaSm100Impl,
                                   .Ret<ffi::Buffer<ffi::S32>>()    // status word
                                   .Attr<float>("softmax_scale")
                                   .Attr<float>("logits_soft_cap")
-                                  .Attr<int32_t>("sliding_window"));
+                                  .Attr<int32_t>("sliding_window")
+                                  .Attr<int32_t>("num_kv_pages_per_block")
+                                  .Attr<int32_t>("num_queries_per_block"));
 #endif  // xla/ffi/api/ffi.h available

@@ -1,6 +1,8 @@
 // C ABI of the ragged paged attention path (declared in include/ejk_rpa.h).
+#include <atomic>
 #include <cmath>
 #include <cstring>
+#include <mutex>
 
 #include "rpa_types.h"
 
@@ -29,27 +31,34 @@ Options g_opt;
 thread_local int t_last_launches = 0;
 
 // cudaEvents around the three kernels of a launch; only touched when option "profile" is 1
-struct ProfileEvents {
-  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+struct ProfileEvents {  // before the planner, after it, after the prefill-tile kernel, after the split-KV kernel, after the merge
+  cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
   bool created = false, recorded = false;
 };
 thread_local ProfileEvents t_prof;
 
 struct DeviceInfo {
-  bool known = false;
+  std::atomic<bool> known{false};
   int sm_count = 0;
   int cc_major = 0;
 };
 DeviceInfo g_dev[64];
+std::mutex g_dev_mutex;  // first-use set-up per device; launches may come from several host threads
 
 const DeviceInfo* device_info() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   DeviceInfo& d = g_dev[dev];
-  if (!d.known) {
-    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
-    if (cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return nullptr;
-    d.known = true;
+  if (!d.known.load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    if (!d.known.load(std::memory_order_relaxed)) {
+      int sm = 0, cc = 0;
+      if (cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
+      if (cudaDeviceGetAttribute(&cc, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return nullptr;
+      d.sm_count = sm;
+      d.cc_major = cc;
+      d.known.store(true, std::memory_order_release);
+    }
   }
   return &d;
 }
@@ -160,20 +169,24 @@ size_t ejk_rpa_workspace_bytes(const ejk_rpa_shape* shape) {
 // Shared body of the launch entry points.  `value_cache` != null selects the split cache layout
 // (kv_pages is then the key cache); with it, null query_start_loc / num_seqs mean "one query row per
 // sequence, all sequences".
-static int launch_impl(const void* queries, const void* kv_pages, const void* value_cache, const int32_t* context_lens,
-                       const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
-                       const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
-                       int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream,
-                       int kv_dim = 0) {
-  t_last_launches = 0;
-  if (!queries || !kv_pages || !context_lens || !block_tables || !out || !workspace || !shape || !attrs)
-    return EJK_RPA_E_NULL;
+// Every host-side check of a launch, with nothing enqueued: entry points that enqueue work of their own
+// before the attention kernels (the v3 page write) call it first, so that an invalid argument returns its
+// negative code with no kernel launched and nothing modified.  `workspace` may be null when the caller
+// supplies it later (workspace_bytes is then not checked either).
+static int validate(const void* queries, const void* kv_pages, const void* value_cache, const int32_t* context_lens,
+                    const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
+                    const float* softmax_aux, const void* out, const void* workspace, size_t workspace_bytes,
+                    bool need_workspace, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs,
+                    const DeviceInfo** dev_out) {
+  if (!queries || !kv_pages || !context_lens || !block_tables || !out || !shape || !attrs) return EJK_RPA_E_NULL;
+  if (need_workspace && !workspace) return EJK_RPA_E_NULL;
   if (!value_cache && (!query_start_loc || !num_seqs)) return EJK_RPA_E_NULL;
   if (int e = check_shape(shape)) return e;
   const ejk_rpa_shape& s = *shape;
   const ejk_rpa_attrs& a = *attrs;
   if (!(a.softmax_scale == a.softmax_scale) || std::isinf(a.softmax_scale)) return EJK_RPA_E_ARG;
   if (!(a.logits_soft_cap == a.logits_soft_cap) || std::isinf(a.logits_soft_cap)) return EJK_RPA_E_ARG;
+  if (!(a.out_scale == a.out_scale) || std::isinf(a.out_scale)) return EJK_RPA_E_ARG;
   if (a.num_sinks < 0 || (a.num_sinks > 0 && !softmax_aux)) return EJK_RPA_E_ARG;
   if (a.num_sinks > 0 && a.sink_rows != s.num_q_heads && a.sink_rows != s.num_kv_heads && a.sink_rows != 1)
     return EJK_RPA_E_ARG;
@@ -183,8 +196,33 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   const DeviceInfo* d = device_info();
   if (!d) return EJK_RPA_E_DEVICE;
   if (d->cc_major != 10) return EJK_RPA_E_DEVICE;
+  if (need_workspace) {
+    const WorkspaceLayout L = layout_for(s, d->sm_count);
+    if (workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return EJK_RPA_E_WORKSPACE;
+  }
+  if (g_opt.path == 2) {  // the TMA gather was forced: refuse here, before anything is enqueued, what it cannot serve
+    Params probe;
+    std::memset(&probe, 0, sizeof(probe));
+    probe.page_size = s.page_size;
+    if (!tma_path_supported(probe)) return EJK_RPA_E_ARG;
+  }
+  if (dev_out) *dev_out = d;
+  return 0;
+}
+
+static int launch_impl(const void* queries, const void* kv_pages, const void* value_cache, const int32_t* context_lens,
+                       const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
+                       const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
+                       int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream,
+                       int kv_dim = 0) {
+  t_last_launches = 0;
+  const DeviceInfo* d = nullptr;
+  if (int e = validate(queries, kv_pages, value_cache, context_lens, block_tables, query_start_loc, num_seqs,
+                       softmax_aux, out, workspace, workspace_bytes, true, shape, attrs, &d))
+    return e;
+  const ejk_rpa_shape& s = *shape;
+  const ejk_rpa_attrs& a = *attrs;
   const WorkspaceLayout L = layout_for(s, d->sm_count);
-  if (workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return EJK_RPA_E_WORKSPACE;
 
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   Params p;
@@ -249,6 +287,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.num_sinks = a.num_sinks;
   p.sink_rows = a.sink_rows;
   const float log2e = 1.4426950408889634f;
+  p.out_scale = (a.out_scale != 0.f) ? a.out_scale : 1.f;
   p.scale = a.softmax_scale;
   p.scale_log2 = a.softmax_scale * log2e;
   p.cap = a.logits_soft_cap;
@@ -313,17 +352,18 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
     if (e != cudaSuccess) return static_cast<int>(e);
     ++t_last_launches;
   }
+  if (prof) cudaEventRecord(t_prof.ev[2], st);
   e = use_tma ? launch_splitkv_tma(p, s.dtype, d->sm_count, st, pdl) : launch_splitkv(p, s.dtype, d->sm_count, st);
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
-  if (prof) cudaEventRecord(t_prof.ev[2], st);
+  if (prof) cudaEventRecord(t_prof.ev[3], st);
   if (!p.fused_merge) {
     e = launch_merge(p, s.dtype, d->sm_count, st);
     if (e != cudaSuccess) return static_cast<int>(e);
     ++t_last_launches;
   }
   if (prof) {
-    cudaEventRecord(t_prof.ev[3], st);
+    cudaEventRecord(t_prof.ev[4], st);
     t_prof.recorded = true;
   }
   return 0;
@@ -348,6 +388,7 @@ int ejk_page_attention_launch(const void* query, const void* key_cache, const vo
                               const int32_t* context_lens, const int32_t* block_tables, void* out, void* workspace,
                               size_t workspace_bytes, int32_t* status, const ejk_rpa_shape* shape,
                               const ejk_rpa_attrs* attrs, void* stream) {
+  t_last_launches = 0;
   if (!value_cache) return EJK_RPA_E_NULL;
   if (shape && shape->total_tokens != shape->max_num_seqs) return EJK_RPA_E_SHAPE;  // one query row per sequence
   if (reinterpret_cast<uintptr_t>(value_cache) & 15) return EJK_RPA_E_ALIGN;
@@ -359,8 +400,13 @@ int ejk_rpa_v3_launch(const void* queries, const void* keys, const void* values,
                       const int32_t* kv_lens, const int32_t* block_tables, const int32_t* query_start_loc,
                       const int32_t* distribution, void* out, void* workspace, size_t workspace_bytes, int32_t* status,
                       const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
+  t_last_launches = 0;
   if (!keys || !values || !kv_cache || !distribution) return EJK_RPA_E_NULL;
-  if (int e = check_shape(shape)) return e;
+  // every host check of the attention launch comes before the page write: a call that is going to be refused
+  // must not have modified the cache (a retry would apply the write twice) nor have launched anything
+  if (int e = validate(queries, kv_cache, nullptr, kv_lens, block_tables, query_start_loc, distribution + 2, nullptr, out,
+                       workspace, workspace_bytes, true, shape, attrs, nullptr))
+    return e;
   // the v3 cache pads head_dim to a multiple of 128 (align_to(D, 128), _kernel.py:45-57); the page write
   // zero-fills the padding like merge_kv does and the attention kernels step over it
   const int d_align = (shape->head_dim + 127) / 128 * 128;
@@ -389,28 +435,33 @@ int ejk_rpa_v3_launch(const void* queries, const void* keys, const void* values,
 static __device__ __align__(256) unsigned char g_static_scratch[EJK_RPA_STATIC_SCRATCH_BYTES];
 
 namespace {
-void* g_static_scratch_ptr[64] = {};
+std::atomic<void*> g_static_scratch_ptr[64];
 }
 
 int ejk_rpa_launch_static_scratch(const void* queries, const void* kv_pages, const int32_t* context_lens,
                                   const int32_t* block_tables, const int32_t* query_start_loc,
                                   const int32_t* num_seqs, const float* softmax_aux, void* out, int32_t* status,
                                   const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream) {
-  if (int e = check_shape(shape)) return e;
+  t_last_launches = 0;
   if (g_opt.profile) return EJK_RPA_E_ARG;  // the profiling hook creates CUDA events; not on this path
-  const DeviceInfo* d = device_info();
-  if (!d) return EJK_RPA_E_DEVICE;
+  // the same argument and device checks as ejk_rpa_launch, before anything touches the runtime: a null
+  // pointer or a GPU of another generation gets its EJK_RPA_E_* code, not a raw CUDA error from the look-up
+  const DeviceInfo* d = nullptr;
+  if (int e = validate(queries, kv_pages, nullptr, context_lens, block_tables, query_start_loc, num_seqs, softmax_aux,
+                       out, nullptr, 0, false, shape, attrs, &d))
+    return e;
   if (layout_for(*shape, d->sm_count).total > (size_t)EJK_RPA_STATIC_SCRATCH_BYTES) return EJK_RPA_E_SCRATCH;
   int dev = 0;
   if (cudaError_t ce = cudaGetDevice(&dev); ce != cudaSuccess) return static_cast<int>(ce);
   if (dev < 0 || dev >= 64) return EJK_RPA_E_DEVICE;
-  if (!g_static_scratch_ptr[dev]) {
-    void* ptr = nullptr;
+  void* ptr = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (!ptr) {
+    // two host threads may both get here on their first call: both look up the same address
     if (cudaError_t ce = cudaGetSymbolAddress(&ptr, g_static_scratch); ce != cudaSuccess) return static_cast<int>(ce);
-    g_static_scratch_ptr[dev] = ptr;
+    g_static_scratch_ptr[dev].store(ptr, std::memory_order_release);
   }
-  return ejk_rpa_launch(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, softmax_aux, out,
-                        g_static_scratch_ptr[dev], (size_t)EJK_RPA_STATIC_SCRATCH_BYTES, status, shape, attrs, stream);
+  return ejk_rpa_launch(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, softmax_aux, out, ptr,
+                        (size_t)EJK_RPA_STATIC_SCRATCH_BYTES, status, shape, attrs, stream);
 }
 
 int ejk_rpa_set_option(const char* name, int value) {
@@ -469,18 +520,25 @@ int ejk_rpa_get_option(const char* name, int* value) {
 
 int ejk_rpa_last_launch_count(void) { return t_last_launches; }
 
-int ejk_rpa_profile_read(float* plan_ms, float* main_ms, float* merge_ms) {
+int ejk_rpa_profile_read_kernels(float* plan_ms, float* prefill_ms, float* splitkv_ms, float* merge_ms) {
   if (!t_prof.recorded) return EJK_RPA_E_ARG;
-  cudaError_t e = cudaEventSynchronize(t_prof.ev[3]);
+  cudaError_t e = cudaEventSynchronize(t_prof.ev[4]);
   if (e != cudaSuccess) return static_cast<int>(e);
-  float* dst[3] = {plan_ms, main_ms, merge_ms};
-  for (int i = 0; i < 3; ++i) {
+  float* dst[4] = {plan_ms, prefill_ms, splitkv_ms, merge_ms};
+  for (int i = 0; i < 4; ++i) {
     float ms = 0.f;
     e = cudaEventElapsedTime(&ms, t_prof.ev[i], t_prof.ev[i + 1]);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (dst[i]) *dst[i] = ms;
   }
   return 0;
+}
+
+int ejk_rpa_profile_read(float* plan_ms, float* main_ms, float* merge_ms) {
+  float pre = 0.f, skv = 0.f;
+  const int rc = ejk_rpa_profile_read_kernels(plan_ms, &pre, &skv, merge_ms);
+  if (rc == 0 && main_ms) *main_ms = pre + skv;
+  return rc;
 }
 
 }  // extern "C"

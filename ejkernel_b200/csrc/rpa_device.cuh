@@ -167,6 +167,16 @@ __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
+// Zero-fills rows [row0, T) of a dense [T, row_bytes] output, spread over all threads of the grid.
+// row_bytes is a multiple of 16 and `out` is 16-byte aligned (both checked on the host).
+__device__ __forceinline__ void zero_tail_rows(void* out, int row0, int T, size_t row_bytes) {
+  if (row0 >= T) return;
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(out) + (size_t)row0 * row_bytes);
+  const size_t n16 = (size_t)(T - row0) * row_bytes / 16;
+  const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) dst[i] = z;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));

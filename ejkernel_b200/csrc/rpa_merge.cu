@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) rpa_merge_kernel(const Param
       l_fin = l_tot * sc;
       for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
     }
-    sc = (l_fin > 0.f) ? sc / l_fin : 0.f;
+    sc = (l_fin > 0.f) ? sc * p.out_scale / l_fin : 0.f;  // out_scale: v_scale of the v3 operator, else 1
     T* dst = out + ((size_t)(mi.q_start + qt) * p.Hq + hq) * D + lane * VPL;
 #pragma unroll
     for (int i = 0; i < VPL; i += 2) {

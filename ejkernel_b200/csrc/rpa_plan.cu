@@ -224,6 +224,10 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
     p.header[kHdrTotalKeys] = (int)(total > 0x7fffffffull ? 0x7fffffffull : total);
     p.header[kHdrQueue] = 0;
     p.header[kHdrPrefillQueue] = 0;
+    // rows of `out` from here on belong to no sequence; the split-KV kernel zero-fills them (the reference's
+    // result starts as zeros, _xla_impl_fwd.py:58)
+    int tail = p.query_start_loc ? p.query_start_loc[S] : S;
+    p.header[kHdrTailStart] = tail < 0 ? 0 : (tail > p.T ? p.T : tail);
   }
   __syncthreads();
   const int chunk = s_chunk;

@@ -817,7 +817,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
                 l_fin = l_tot * scl;
                 for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2eP - mf);
               }
-              scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
+              scl = (l_fin > 0.f) ? scl * p.out_scale / l_fin : 0.f;  // out_scale: v_scale of the v3 operator, else 1
               T* orow = reinterpret_cast<T*>(p.out) + ((size_t)out_row_q * p.Hq + out_head) * D;
 #pragma unroll 1
               for (int c0 = 0; c0 < D; c0 += 32) {
@@ -864,7 +864,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
             l_fin = l_row * scl;
             for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2eP - mf);
           }
-          scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
+          scl = (l_fin > 0.f) ? scl * p.out_scale / l_fin : 0.f;  // out_scale: v_scale of the v3 operator, else 1
           T* orow = reinterpret_cast<T*>(p.out) + ((size_t)out_row_q * p.Hq + out_head) * D;
 #pragma unroll 1
           for (int c0 = 0; c0 < D; c0 += 32) {

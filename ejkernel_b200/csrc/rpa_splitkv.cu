@@ -390,7 +390,7 @@ rpa_splitkv_kernel(const Params p) {
             l_fin = lt * sc;
             for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
           }
-          sc = (l_fin > 0.f) ? sc / l_fin : 0.f;
+          sc = (l_fin > 0.f) ? sc * p.out_scale / l_fin : 0.f;  // out_scale: v_scale of the v3 operator, else 1
         }
         row_scale[r] = sc;
         row_m[r] = mt;
@@ -470,6 +470,7 @@ rpa_splitkv_kernel(const Params p) {
   }
   cp_async_wait<0>();
   if (flags && p.status) atomicOr(reinterpret_cast<unsigned*>(p.status), flags);
+  zero_tail_rows(p.out, p.header[kHdrTailStart], p.T, (size_t)p.Hq * D * sizeof(T));
 }
 
 template <typename T, int D, int NT, int NS>

@@ -496,7 +496,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
               l_fin = lt * scl;
               for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
             }
-            scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
+            scl = (l_fin > 0.f) ? scl * p.out_scale / l_fin : 0.f;  // out_scale: v_scale of the v3 operator, else 1
           }
           row_scale[r] = scl;
           row_m[r] = mt;
@@ -641,7 +641,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
                   l_fin = l_tot * scl;
                   for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
                 }
-                scl = (l_fin > 0.f) ? scl / l_fin : 0.f;
+                scl = (l_fin > 0.f) ? scl * p.out_scale / l_fin : 0.f;  // out_scale: v_scale of the v3 operator, else 1
                 T* dst = out + ((size_t)(u.q_start + qt) * p.Hq + hq) * D + lane * VPL;
 #pragma unroll
                 for (int i = 0; i < VPL; i += 2)
@@ -663,6 +663,13 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
     if (*abort_flag) flags |= EJK_RPA_ST_TIMEOUT;
   }
   if (flags && p.status) atomicOr(reinterpret_cast<unsigned*>(p.status), flags);
+  zero_tail_rows(p.out, p.header[kHdrTailStart], p.T, (size_t)p.Hq * D * sizeof(T));
+  // In a mixed batch this grid is a programmatic dependent of the prefill-tile grid and never waited for it
+  // (the two write different rows).  Whatever follows in the stream, though, is only ordered after THIS grid:
+  // one thread per CTA now waits for the prefill grid, so this grid cannot complete before it, and a later
+  // kernel (a reader of `out`, the next call's planner) is ordered after both.  All prefill CTAs are resident
+  // before this grid starts (it is released when each of them has seen the plan), so the wait cannot starve them.
+  if ((p.pdl & 1) && tid == 0) pdl_wait();
 }
 
 // ---- host side: tensor map over kv_pages ----

@@ -52,6 +52,7 @@ enum HeaderWord {
   kHdrNumPrefill = 6,     // work items of the tcgen05 prefill-tile kernel
   kHdrPrefillQueue = 7,   // its work queue head
   kHdrPrefillStages = 8,  // sum of the items' 64-token KV stages (per kv head)
+  kHdrTailStart = 9,      // first row of `out` past the last sequence: rows [this, T) are zero-filled
   kHdrWords = 64,
 };
 
@@ -104,6 +105,7 @@ struct Params {
   int32_t prefill_min_rows;  // sequences with q_len*G >= this go to the prefill-tile kernel; 0 = never
   int32_t window;      // <= 0: none
   int32_t num_sinks, sink_rows;
+  float out_scale;     // factor on the normalised output (v_scale of the v3 operator), 1 otherwise
   float scale;         // softmax_scale
   float scale_log2;    // softmax_scale * log2(e)
   float cap;           // 0: none

@@ -31,7 +31,7 @@ from torch import Tensor as Array
 from .... import _cabi
 from .._typecheck import typechecked_once
 from ..._registry import Backend, Platform, kernel_registry
-from ..ragged_page_attention._interface import _DTYPE_CODE, RpaWorkspace, _workspace_cache
+from ..ragged_page_attention._interface import _DTYPE_CODE, cached_workspace
 
 
 @kernel_registry.register("page_attention", Platform.CUDA, Backend.GPU)
@@ -79,12 +79,9 @@ def page_attention(
 
     device = query.device
     shape = _cabi.Shape(S, S, block_tables.shape[1], P, block_size, Hq, Hkv, D, _DTYPE_CODE[query.dtype])
-    key = (device.index, *[getattr(shape, f) for f, _ in shape._fields_], _cabi.get_option("waves"))
-    ws = _workspace_cache.get(key)
-    if ws is None:
-        ws = _workspace_cache[key] = RpaWorkspace(shape, device)
+    ws = cached_workspace(shape, device)
     attrs = _cabi.Attrs(scale, 0.0 if attn_logits_soft_cap is None else float(attn_logits_soft_cap), 0, 0, 0, 0, 0)
-    out = torch.zeros_like(query)
+    out = torch.empty_like(query)  # one row per sequence, every row is written
     with torch.cuda.device(device):
         rc = _cabi.load().ejk_page_attention_launch(
             query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), context_lens.data_ptr(),

@@ -29,6 +29,8 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
+from collections import OrderedDict
 
 import torch
 from jaxtyping import Float, Int
@@ -50,12 +52,9 @@ class RpaWorkspace:
     what lets a tracing runtime allocate it ahead of time.
     """
 
-    def __init__(self, shape: _cabi.Shape, device: torch.device):
-        lib = _cabi.load()
-        with torch.cuda.device(device):
-            nbytes = int(lib.ejk_rpa_workspace_bytes(ctypes.byref(shape)))
-        if nbytes == 0:
-            raise ValueError("ejk_rpa_workspace_bytes rejected the shape")
+    def __init__(self, shape: _cabi.Shape, device: torch.device, nbytes: int | None = None):
+        if nbytes is None:
+            nbytes = workspace_bytes(shape, device)
         self.shape = shape
         self.nbytes = nbytes
         self.buffer = torch.empty(nbytes, dtype=torch.uint8, device=device)
@@ -63,7 +62,40 @@ class RpaWorkspace:
         assert self.buffer.data_ptr() % 256 == 0
 
 
-_workspace_cache: dict[tuple, RpaWorkspace] = {}
+def workspace_bytes(shape: _cabi.Shape, device: torch.device) -> int:
+    with torch.cuda.device(device):
+        nbytes = int(_cabi.load().ejk_rpa_workspace_bytes(ctypes.byref(shape)))
+    if nbytes == 0:
+        raise ValueError("ejk_rpa_workspace_bytes rejected the shape")
+    return nbytes
+
+
+# Workspaces of the operator entry points that own their scratch (the public operators; the ``*_into`` forms
+# take the caller's).  One per (device, CUDA stream): calls on one stream are ordered and may share scratch,
+# calls on different streams may run at the same time and must not.  A workspace serves every shape whose
+# need fits into it and is replaced by a larger one (next power of two) when a call needs more, so a serving
+# loop whose token count changes every step settles on one buffer instead of allocating one per shape; the
+# least recently used entries are dropped beyond ``_WORKSPACE_CACHE_MAX`` streams.
+_WORKSPACE_CACHE_MAX = 16
+_workspace_cache: "OrderedDict[tuple[int, int], RpaWorkspace]" = OrderedDict()
+
+
+def cached_workspace(shape: _cabi.Shape, device: torch.device) -> RpaWorkspace:
+    need = workspace_bytes(shape, device)
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspace_cache.get(key)
+    if ws is None or ws.nbytes < need:
+        cap = 1 << max(16, (need - 1).bit_length())
+        status = None if ws is None else ws.status  # a pending status bit survives the growth
+        ws = RpaWorkspace(shape, device, cap)
+        if status is not None:
+            ws.status = status
+        _workspace_cache[key] = ws
+    _workspace_cache.move_to_end(key)
+    while len(_workspace_cache) > _WORKSPACE_CACHE_MAX:
+        _workspace_cache.popitem(last=False)
+    ws.shape = shape
+    return ws
 
 
 def _shape_of(queries, kv_pages, block_tables) -> _cabi.Shape:
@@ -135,13 +167,23 @@ def _validate(queries, kv_pages, context_lens, block_tables, query_start_loc, nu
             raise ValueError(f"{name} must be contiguous (dense row-major)")
 
 
+_num_seqs_consts: dict[tuple[int, int], torch.Tensor] = {}
+
+
 def _num_seqs_tensor(num_seqs, device) -> torch.Tensor:
     if isinstance(num_seqs, torch.Tensor):
         t = num_seqs.reshape(-1)[:1]
         if t.dtype != torch.int32:
             t = t.to(torch.int32)
         return t.to(device).contiguous()
-    return torch.tensor([int(num_seqs)], dtype=torch.int32, device=device)
+    # a Python int: one small device constant per (device, value), made once (no per-call host-to-device copy)
+    key = (device.index, int(num_seqs))
+    t = _num_seqs_consts.get(key)
+    if t is None:
+        if len(_num_seqs_consts) > 4096:
+            _num_seqs_consts.clear()
+        t = _num_seqs_consts[key] = torch.tensor([int(num_seqs)], dtype=torch.int32, device=device)
+    return t
 
 
 def ragged_page_attention_into(
@@ -307,16 +349,13 @@ def ragged_page_attention(
         raise ValueError(f"{softmax_scale=} must be finite")
     device = queries.device
     shape = _shape_of(queries, kv_pages, block_tables)
-    key = (device.index, *[getattr(shape, f) for f, _ in shape._fields_], _cabi.get_option("waves"))
-    ws = _workspace_cache.get(key)
-    if ws is None:
-        ws = _workspace_cache[key] = RpaWorkspace(shape, device)
+    ws = cached_workspace(shape, device)
     aux = None
     if softmax_aux is not None:
         aux = softmax_aux.to(device=device, dtype=torch.float32)
         aux = aux.reshape(1, -1) if aux.ndim == 1 else aux
         aux = aux.contiguous()
-    out = torch.zeros_like(queries)
+    out = torch.empty_like(queries)  # every row is written: sequences by their tiles, the rest zero-filled
     ragged_page_attention_into(
         out, ws, queries, kv_pages, context_lens, block_tables, query_start_loc,
         _num_seqs_tensor(num_seqs, device),
@@ -324,15 +363,26 @@ def ragged_page_attention(
         softmax_aux=aux, num_kv_pages_per_block=num_kv_pages_per_block,
         num_queries_per_block=num_queries_per_block,
     )
+    _debug_check_status(ws, "ragged_page_attention")
     return out
 
 
-def read_status(queries: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.Tensor, clear: bool = True) -> int:
-    """Status word of the cached workspace for this shape (forces a device sync).  Debug aid: the
-    reference has no device-side error reporting at all."""
-    shape = _shape_of(queries, kv_pages, block_tables)
-    key = (queries.device.index, *[getattr(shape, f) for f, _ in shape._fields_], _cabi.get_option("waves"))
-    ws = _workspace_cache.get(key)
+def _debug_check_status(ws: RpaWorkspace, what: str) -> None:
+    """Opt-in (``EJKERNEL_B200_CHECK_STATUS=1``): read the status word after the call -- this synchronises --
+    and raise when it says the outputs are invalid (a wait ran out, or the planner ran out of workspace)."""
+    if os.environ.get("EJKERNEL_B200_CHECK_STATUS", "0") not in ("", "0"):
+        word = int(ws.status.item())
+        if word & (_cabi.ST_TIMEOUT | _cabi.ST_INTERNAL):
+            ws.status.zero_()
+            raise _cabi.RpaLibraryError(f"{what}: status word {word:#x}: " + "; ".join(_cabi.decode_status(word)))
+
+
+def read_status(queries: torch.Tensor, kv_pages: torch.Tensor | None = None, block_tables: torch.Tensor | None = None,
+                clear: bool = True) -> int:
+    """Status word of the operator's workspace for the device of ``queries`` and the current stream (forces a
+    device sync).  Debug aid: the reference has no device-side error reporting at all."""
+    device = queries.device
+    ws = _workspace_cache.get((device.index, torch.cuda.current_stream(device).cuda_stream))
     if ws is None:
         return 0
     word = int(ws.status.item())

@@ -33,7 +33,7 @@ from torch import Tensor as Array
 from .... import _cabi
 from .._typecheck import typechecked_once
 from ..._registry import Backend, Platform, kernel_registry
-from ..ragged_page_attention._interface import _DTYPE_CODE, RpaWorkspace, _workspace_cache
+from ..ragged_page_attention._interface import _DTYPE_CODE, cached_workspace
 
 
 def _packing(dtype: torch.dtype) -> int:
@@ -67,7 +67,9 @@ def ragged_page_attention_v3(
     Float[Array, "num_pages page_size num_kv_heads_x2_per_kv_packing kv_packing head_dim_padded"],
 ]:
     """Returns ``(out, kv_cache)``; ``kv_cache`` is the same tensor, updated in place."""
-    del chunk_prefill_size, num_kv_pages_per_block, num_queries_per_block, vmem_limit_bytes, q_scale
+    del chunk_prefill_size, num_kv_pages_per_block, num_queries_per_block, vmem_limit_bytes
+    if q_scale is not None:
+        raise NotImplementedError("q_scale (queries quantised to the cache dtype, _kernel.py:249-265) is not implemented")
     # static half of the reference's contract (_kernel.py:73-126)
     if not queries.is_cuda:
         raise RuntimeError("ragged_page_attention_v3[cuda]: tensors must live on a CUDA device (no CPU fallback)")
@@ -108,14 +110,12 @@ def ragged_page_attention_v3(
     pps = block_tables.numel() // S_max
     shape = _cabi.Shape(T, S_max, pps, P, page_size, Hq, Hkv, D, _DTYPE_CODE[queries.dtype])
     device = queries.device
-    key = (device.index, *[getattr(shape, f) for f, _ in shape._fields_], _cabi.get_option("waves"))
-    ws = _workspace_cache.get(key)
-    if ws is None:
-        ws = _workspace_cache[key] = RpaWorkspace(shape, device)
+    ws = cached_workspace(shape, device)
     scale = float(softmax_scale) * (1.0 if k_scale is None else float(k_scale))
     attrs = _cabi.Attrs(scale, 0.0 if logits_soft_cap is None else float(logits_soft_cap),
-                        0 if sliding_window is None else int(sliding_window), 0, 0, 0, 0)
-    out = torch.zeros_like(queries)
+                        0 if sliding_window is None else int(sliding_window), 0, 0, 0, 0,
+                        0.0 if v_scale is None else float(v_scale))  # v_scale: in float32, before the output cast
+    out = torch.empty_like(queries)
     with torch.cuda.device(device):
         rc = _cabi.load().ejk_rpa_v3_launch(
             queries.data_ptr(), keys.data_ptr(), values.data_ptr(), kv_cache.data_ptr(), kv_lens.data_ptr(),
@@ -124,6 +124,4 @@ def ragged_page_attention_v3(
             torch.cuda.current_stream(device).cuda_stream,
         )
     _cabi.check(rc, "ejk_rpa_v3_launch")
-    if v_scale is not None:
-        out.mul_(float(v_scale))
     return out, kv_cache

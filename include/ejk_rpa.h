@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define EJK_RPA_VERSION 1
+#define EJK_RPA_VERSION 2
 
 #if defined(__GNUC__)
 #define EJK_RPA_API __attribute__((visibility("default")))
@@ -93,6 +93,9 @@ typedef struct ejk_rpa_attrs {
                                      "min_chunk" for this call) */
   int32_t num_queries_per_block;  /* tile hint, 0 = auto: sequences with at least this many query tokens are served
                                      by 128-row tensor tiles (overrides option "prefill_rows" for this call) */
+  float out_scale;       /* 0 = none (1.0): factor applied to the normalised output in float32, before the cast to
+                            the output dtype -- `v_scale` of the v3 operator
+                            (ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:283-284) */
 } ejk_rpa_attrs;
 
 /* Library version (EJK_RPA_VERSION of the build).  No reference counterpart; the reference
@@ -104,7 +107,9 @@ EJK_RPA_API const char* ejk_rpa_error_string(int code);
 
 /* Bytes of scratch the launch needs for this static shape on the current device (split-KV
  * partials, the device-built work list, the merge list).  Depends on shapes only, never on
- * lengths, so a tracing runtime can allocate it as an extra result buffer.  Returns 0 on an
+ * lengths, so a tracing runtime can allocate it as an extra result buffer.  It also grows with the
+ * process-wide option "waves" (more work items per CTA need more partial slots): size the workspace
+ * after setting that option, or a later launch answers EJK_RPA_E_WORKSPACE.  Returns 0 on an
  * invalid shape.  The reference has no scratch: XLA materialises its own temporaries
  * (_xla_impl_fwd.py:113-114). */
 EJK_RPA_API size_t ejk_rpa_workspace_bytes(const ejk_rpa_shape* shape);
@@ -120,8 +125,10 @@ EJK_RPA_API size_t ejk_rpa_workspace_bytes_min(const ejk_rpa_shape* shape);
  * (_triton_impl_fwd.py:485-613).  `workspace` must be 256-byte aligned and hold
  * ejk_rpa_workspace_bytes(shape) bytes; its contents need not be initialised.  `status`
  * (device int32, may be null) gets EJK_RPA_ST_* bits OR-ed in; the caller zeroes it.
- * `softmax_aux` is float32 [sink_rows, num_sinks] or null.  Rows of `out` that belong to no
- * sequence (>= query_start_loc[num_seqs]) are left untouched. */
+ * `softmax_aux` is float32 [sink_rows, num_sinks] or null.  Rows of `out` past the last sequence
+ * (>= query_start_loc[num_seqs]) are zero-filled, as in the reference, whose result starts as zeros
+ * (_xla_impl_fwd.py:58); `out` therefore needs no initialisation.  Rows of a sequence whose entry breaks the
+ * contract (a status bit is set) are unspecified. */
 EJK_RPA_API int ejk_rpa_launch(const void* queries, const void* kv_pages, const int32_t* context_lens,
                    const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                    const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
@@ -224,6 +231,11 @@ EJK_RPA_API int ejk_rpa_last_launch_count(void);
  * measuring hook that replaces the reference's wall-clock Tuner.measure
  * (ejkernel/ops/config/selection.py:226-245). */
 EJK_RPA_API int ejk_rpa_profile_read(float* plan_ms, float* main_ms, float* merge_ms);
+
+/* The same with the two attention kernels apart: `prefill_ms` is the tensor-tile kernel that serves sequences
+ * with many query rows (0 when the batch shape has none), `splitkv_ms` the split-KV kernel of the decode rows;
+ * main_ms above is their sum.  A bench uses it to hold each kernel against its own roofline (tensor / HBM). */
+EJK_RPA_API int ejk_rpa_profile_read_kernels(float* plan_ms, float* prefill_ms, float* splitkv_ms, float* merge_ms);
 
 #ifdef __cplusplus
 }

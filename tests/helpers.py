@@ -14,8 +14,10 @@ REL_RMS = 1.0  # loose sanity bound on max error / RMS of the expected output; t
 
 def run_cuda(batch: RaggedBatch, **override) -> torch.Tensor:
     from ejkernel_b200.kernels._cuda.ragged_page_attention import ragged_page_attention
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import read_status
 
     b = batch if batch.queries.is_cuda else batch.to("cuda")
+    read_status(b.queries)  # the operator's status word is per stream, not per shape: drop what earlier calls left
     kw = b.kwargs()
     kw.update(override)
     out = ragged_page_attention(*b.args(), **kw)

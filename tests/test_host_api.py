@@ -97,7 +97,7 @@ def test_library_exports_every_declared_symbol(rpa_lib):
     assert declared == set(_cabi.EXPORTS), (declared, set(_cabi.EXPORTS))
     for name in declared:
         assert getattr(rpa_lib, name) is not None
-    assert rpa_lib.ejk_rpa_version() == 1
+    assert rpa_lib.ejk_rpa_version() == 2
     assert _cabi.error_string(0) == "ok" and "head_dim" in _cabi.error_string(-3)
     # option plumbing is host-only
     old = _cabi.get_option("waves")

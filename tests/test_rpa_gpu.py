@@ -624,3 +624,109 @@ def test_public_module_entry(rpa_lib):
     with pytest.raises(ValueError):
         ej.ragged_page_attention(bc.queries, bc.kv_pages, bc.context_lens, bc.block_tables, bc.query_start_loc,
                                  bc.num_seqs, platform="xla")
+
+
+def test_a_reader_enqueued_right_after_a_mixed_call_sees_the_prefill_rows(rpa_lib):
+    """In a mixed batch the split-KV kernel is a programmatic dependent of the prefill-tile kernel and does
+    not wait for it while it works; before it completes, one thread per CTA waits for the prefill grid, so a
+    kernel enqueued behind the call with no host synchronisation in between (here a copy of ``out``) is
+    ordered after BOTH kernels.  One long prefill sequence beside a one-token decode is the shape in which
+    the split-KV kernel would otherwise finish long before the prefill kernel."""
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import RpaWorkspace, ragged_page_attention_into
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import _shape_of
+
+    b = make_ragged_batch([1, 1024], [40, 6000], num_q_heads=16, num_kv_heads=4, head_dim=128, page_size=16, seed=91)
+    want = oracle(b)
+    bc = b.to("cuda")
+    ws = RpaWorkspace(_shape_of(bc.queries, bc.kv_pages, bc.block_tables), bc.queries.device)
+    out = torch.empty_like(bc.queries)
+    copies = []
+    for rep in range(20):
+        out.fill_(float("nan"))
+        ragged_page_attention_into(out, ws, *bc.args(), softmax_scale=bc.softmax_scale)
+        copies.append(out.clone())  # enqueued on the same stream, no host sync since the launch
+    torch.cuda.synchronize()
+    assert int(ws.status.item()) == 0
+    # per sequence: the tight criterion scales with the rms of the expected rows, and a 40-key row is ten times
+    # larger than rows that average 6000 keys
+    assert_parity(out[:1], want[:1], 1, what="mixed batch, decode row")
+    assert_parity(out[1:], want[1:], b.total_tokens - 1, what="mixed batch, prefill rows")
+    for c in copies:
+        assert torch.equal(c, out), "a copy enqueued right behind the call missed rows of the prefill kernel"
+
+
+def test_operator_workspace_is_bounded_and_per_stream(rpa_lib):
+    """The public operator owns its scratch: one buffer per (device, stream) that grows to the largest need, so
+    a serving loop with a different token count every step does not allocate one workspace per shape, and two
+    streams running calls of the same shape at the same time do not share scratch."""
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import ragged_page_attention
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import _interface as itf
+
+    torch.cuda.synchronize()
+    itf._workspace_cache.clear()
+    rng = np.random.default_rng(3)
+    outs = {}
+    for T in range(1, 201):  # 200 distinct shapes
+        kv = [int(x) for x in rng.integers(1, 400, 2)]
+        b = make_ragged_batch([1, T - 1] if T > 1 else [1, 0], [kv[0], kv[1] + T], num_q_heads=8, num_kv_heads=2,
+                              head_dim=64, page_size=16, pages_per_seq=40, num_pages=90, max_num_seqs=2, seed=T).to("cuda")
+        o = ragged_page_attention(*b.args(), softmax_scale=b.softmax_scale)
+        if T in (1, 57, 200):
+            outs[T] = (b, o)
+    torch.cuda.synchronize()
+    assert len(itf._workspace_cache) == 1
+    (ws,) = itf._workspace_cache.values()
+    b200 = outs[200][0]
+    assert ws.nbytes < 4 * itf.workspace_bytes(itf._shape_of(b200.queries, b200.kv_pages, b200.block_tables), b200.queries.device)
+    for T, (b, o) in outs.items():
+        assert_parity(o, oracle(b), b.total_tokens, what=f"T={T}")
+
+    # two streams, same shape, overlapping in time: each result equals the single-stream result bit for bit
+    ba = make_workload("c2", num_seqs=48, len_scale=0.5, device="cuda")
+    bb = make_workload("c2", num_seqs=48, len_scale=0.5, device="cuda", seed=77)
+    ra = ragged_page_attention(*ba.args(), softmax_scale=ba.softmax_scale)
+    rb = ragged_page_attention(*bb.args(), softmax_scale=bb.softmax_scale)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    got = []
+    for _ in range(10):
+        with torch.cuda.stream(s1):
+            oa = ragged_page_attention(*ba.args(), softmax_scale=ba.softmax_scale)
+        with torch.cuda.stream(s2):
+            ob = ragged_page_attention(*bb.args(), softmax_scale=bb.softmax_scale)
+        got.append((oa, ob))
+    torch.cuda.synchronize()
+    assert len(itf._workspace_cache) == 3
+    for oa, ob in got:
+        assert torch.equal(oa, ra) and torch.equal(ob, rb)
+
+
+def test_rows_past_the_last_sequence_are_zero_filled_by_the_launch(rpa_lib):
+    """``out`` needs no initialisation: like the reference, whose result starts as zeros, the launch writes
+    zeros to every row past the last sequence (a padded token axis is the normal case under a tracing runtime)."""
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import RpaWorkspace, ragged_page_attention_into
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import _shape_of
+
+    for q_lens, kv_lens, pad in (([1, 1, 1], [70, 9, 300], 61), ([40, 1], [100, 5], 300), ([1], [10], 0)):
+        b = make_ragged_batch(q_lens, kv_lens, num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16,
+                              pad_query_rows=pad, max_num_seqs=5, seed=pad).to("cuda")
+        ws = RpaWorkspace(_shape_of(b.queries, b.kv_pages, b.block_tables), b.queries.device)
+        for path in (0, 1):  # TMA gather and cp.async gather
+            from ejkernel_b200 import _cabi
+            _cabi.set_option("path", path)
+            try:
+                out = torch.full_like(b.queries, float("nan"))
+                ragged_page_attention_into(out, ws, *b.args(), softmax_scale=b.softmax_scale)
+                torch.cuda.synchronize()
+            finally:
+                _cabi.set_option("path", 0)
+            T = b.total_tokens
+            assert torch.isfinite(out.float()).all()
+            assert torch.count_nonzero(out[T:]) == 0
+            assert_parity(out, oracle(b), T, what="padded batch")
+    # no sequence at all: everything is zero
+    b.num_seqs = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.full_like(b.queries, float("nan"))
+    ragged_page_attention_into(out, ws, *b.args(), softmax_scale=b.softmax_scale)
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(out) == 0

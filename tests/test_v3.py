@@ -27,7 +27,6 @@ def _cases():
                                          max_num_seqs=5, pad_query_rows=3, seed=64)
 
 
-@pytest.mark.parametrize("name,b", list(_cases()), ids=[n for n, _ in _cases()])
 def _check_cache(new_cache, old_cache, b):
     """First head_dim lanes: the complete pool, bit for bit.  Padding lanes (head_dim not a multiple of 128):
     zero in the rows the call wrote (merge_kv pads with zeros), untouched elsewhere."""
@@ -110,3 +109,55 @@ def test_cuda_v3_scales_and_full_size_decode(rpa_lib):
     assert torch.equal(new_cache.view(b.kv_pages.shape), b.kv_pages)
     # same kernels on the same bytes: v3 with folded scales reproduces v1 exactly (x2 is exact in bf16)
     assert torch.equal(out, ref * 2.0)
+
+
+@pytest.mark.gpu
+def test_a_refused_v3_call_leaves_the_cache_untouched_and_launches_nothing(rpa_lib):
+    """Every host-side check of the launch comes before the page write: a call that returns a negative code
+    has not modified the cache (a retry would otherwise apply the write twice) and has launched no kernel."""
+    import ctypes
+
+    from ejkernel_b200 import _cabi
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import RpaWorkspace
+
+    b = make_ragged_batch([1, 5], [90, 33], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=71).to("cuda")
+    keys, values, cache, tab_flat, dist = to_v3_inputs(b)
+    T, Hq, D = b.queries.shape
+    shape = _cabi.Shape(T, 2, b.block_tables.shape[1], cache.shape[0], 16, Hq, 2, D, _cabi.BF16)
+    ws = RpaWorkspace(shape, b.queries.device)
+    out = torch.full_like(b.queries, 7.0)
+    attrs = _cabi.Attrs(b.softmax_scale, 0.0, 0, 0, 0, 0, 0)
+    before = cache.clone()
+    P = lambda t: None if t is None else t.data_ptr()
+
+    def call(**kw):
+        a = dict(queries=P(b.queries), keys=P(keys), values=P(values), cache=P(cache), kv_lens=P(b.context_lens),
+                 tab=P(tab_flat), cu=P(b.query_start_loc), dist=P(dist), out=P(out), ws=P(ws.buffer), ws_bytes=ws.nbytes,
+                 attrs=attrs)
+        a.update(kw)
+        return rpa_lib.ejk_rpa_v3_launch(a["queries"], a["keys"], a["values"], a["cache"], a["kv_lens"], a["tab"], a["cu"],
+                                         a["dist"], a["out"], a["ws"], a["ws_bytes"], P(ws.status), ctypes.byref(shape),
+                                         ctypes.byref(a["attrs"]), torch.cuda.current_stream().cuda_stream)
+
+    nan_scale = _cabi.Attrs(float("nan"), 0.0, 0, 0, 0, 0, 0)
+    for what, kw, code in (
+        ("null kv_lens", dict(kv_lens=None), -1),
+        ("null block_tables", dict(tab=None), -1),
+        ("null query_start_loc", dict(cu=None), -1),
+        ("null out", dict(out=None), -1),
+        ("null workspace", dict(ws=None), -1),
+        ("short workspace", dict(ws_bytes=1024), -5),
+        ("misaligned workspace", dict(ws=P(ws.buffer) + 16), -5),
+        ("cache not 16-byte aligned", dict(cache=P(cache) + 2), -8),
+        ("queries not 16-byte aligned", dict(queries=P(b.queries) + 2), -8),
+        ("NaN scale", dict(attrs=nan_scale), -6),
+    ):
+        rc = call(**kw)
+        assert rc == code, (what, rc, _cabi.error_string(rc))
+        assert rpa_lib.ejk_rpa_last_launch_count() == 0, what
+        torch.cuda.synchronize()
+        assert torch.equal(cache.view(torch.int16), before.view(torch.int16)), f"{what}: the cache was modified"
+        assert bool((out == 7.0).all()), f"{what}: something was launched"
+    assert call() == 0  # and the same arguments, unbroken, go through
+    torch.cuda.synchronize()
+    assert torch.equal(cache.view(b.kv_pages.shape), b.kv_pages)

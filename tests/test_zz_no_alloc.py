@@ -25,7 +25,7 @@ from ejkernel_b200 import _cabi
 from ejkernel_b200.kernels._cuda.ragged_page_attention import RpaWorkspace, ragged_page_attention_into
 from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import _shape_of
 from ejkernel_b200.utils import make_ragged_batch, make_workload
-from oracle.rpa_oracle import compare
+from oracle.rpa_oracle import compare, dense_reference
 from tests.helpers import ATOL, REL_RMS, RTOL
 
 pytestmark = pytest.mark.gpu
@@ -72,6 +72,20 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row(rpa_lib):
         r = compare(out[:T], want[:T].float().cpu().numpy(), atol=ATOL, rtol=RTOL)
         assert r["finite"] and r["allclose"] and r["tight"] and r["max_rel_rms"] <= REL_RMS, r
         assert torch.count_nonzero(out[T:]) == 0
+    # the second batch once more, directly against the CPU oracle, with the device's free memory read before and
+    # after: the call must not have allocated anything (the look-up of the array's address happened on the first call)
+    bcpu = second.to("cpu")
+    oracle_out = dense_reference(*bcpu.args(), **bcpu.kwargs())
+    out.fill_(float("nan"))
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    rc = _launch_static(rpa_lib, second, out, status)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert rc == 0 and int(status.item()) == 0
+    assert free_after == free_before, "the workspace-free entry point allocated device memory"
+    r = compare(out, oracle_out, atol=ATOL, rtol=RTOL, rows=second.total_tokens)
+    assert r["finite"] and r["allclose"] and r["tight"], r
 
 
 def test_static_scratch_refuses_shapes_beyond_its_maximum(rpa_lib):
@@ -86,3 +100,13 @@ def test_static_scratch_refuses_shapes_beyond_its_maximum(rpa_lib):
     assert "static buffer" in _cabi.error_string(rc)
     torch.cuda.synchronize()
     assert bool((out == 7.0).all()), "a refused call must not launch anything"
+    # invalid arguments are refused with the library's own codes before the array's address is looked up
+    small = make_ragged_batch([1], [20], num_q_heads=4, num_kv_heads=2, head_dim=64, page_size=8, seed=2).to("cuda")
+    shape = _shape_of(small.queries, small.kv_pages, small.block_tables)
+    attrs = _cabi.Attrs(small.softmax_scale, 0.0, 0, 0, 0, 0, 0)
+    o = torch.zeros_like(small.queries)
+    rc = rpa_lib.ejk_rpa_launch_static_scratch(
+        small.queries.data_ptr(), None, small.context_lens.data_ptr(), small.block_tables.data_ptr(),
+        small.query_start_loc.data_ptr(), small.num_seqs.data_ptr(), None, o.data_ptr(), status.data_ptr(),
+        ctypes.byref(shape), ctypes.byref(attrs), torch.cuda.current_stream().cuda_stream)
+    assert rc == -1  # EJK_RPA_E_NULL
