@@ -20,7 +20,7 @@ sample of the same batch.  ``--impl reference`` times only that CPU restatement.
 
 Outside the headline's timed region the default run also measures the other benchmark workloads and
 checks results:
-  ``per_workload`` (N = 1)  c3 (mixed prefill + decode: the tensor-tile kernel against the bf16 tensor peak and the
+  ``per_workload`` (N = 1)  c2 on a float8 (e4m3) KV pool; c3 (mixed prefill + decode: the tensor-tile kernel against the bf16 tensor peak and the
                             split-KV kernel against the HBM peak, each timed on its own), c4 (window + soft cap,
                             head_dim 256) and c5 (long context), each with step time, kernel time and roofline;
   ``c5_strong`` (N > 1)     the SAME 64 long-context sequences with Hkv/N kv heads per rank: strong scaling;
@@ -322,8 +322,16 @@ def parity_sample(batch, out, n_check: int = 4) -> dict:
                       torch.tensor([m["kv_lens"][s] for s in ids], dtype=torch.int32), tab, cu,
                       torch.tensor([len(ids)], dtype=torch.int32), batch.softmax_scale, batch.sliding_window,
                       batch.logits_soft_cap, None, {})
-    want = dense_reference(*sub.args(), **sub.kwargs(), precision="fp32")
     got = out[rows.to(out.device)].float().cpu().numpy()
+    if batch.kv_pages.element_size() == 1:
+        # e4m3 cache: the probabilities enter P.V as e4m3, each weight within 2^-4 relative, so an output element is
+        # within 2^-4 * (P @ |V|) of the exact one (plus the bf16 rounding of the output)
+        want, wb = dense_reference(*sub.args(), **sub.kwargs(), precision="fp32", return_weight_bound=True)
+        err = np.abs(got - want)
+        ok = bool(np.isfinite(got).all() and (err <= 2.0**-4 * 1.02 * wb + 2.0**-8 * np.abs(want) + 1e-3).all())
+        rms = float(np.sqrt(np.mean(want * want)))
+        return {"ok": ok, "checked": len(ids), "seqs": ids, "max_err_over_rms": float(err.max() / max(rms, 1e-30))}
+    want = dense_reference(*sub.args(), **sub.kwargs(), precision="fp32")
     r = compare(got, want, atol=2e-2, rtol=2e-2)
     return {"ok": bool(r["finite"] and r["allclose"] and r["tight"]), "checked": len(ids), "seqs": ids,
             "max_err_over_rms": r["max_rel_rms"]}
@@ -345,10 +353,11 @@ def main():
     total_seqs = n_seqs * (world if weak else 1)
     config = make_config(args, world)
 
-    def build(name, device, kv_head_slice, *, num_seqs=None, len_scale=1.0, tile=1, pad_query_rows=0):
+    def build(name, device, kv_head_slice, *, num_seqs=None, len_scale=1.0, tile=1, pad_query_rows=0, kv_dtype=None):
         q_l, kv_l, shape, extra = workload_spec(name, num_seqs=num_seqs, len_scale=len_scale, tile=tile)
         return make_ragged_batch(q_l, kv_l, dtype=torch.bfloat16, device=device, seed=1000 + WORKLOADS.index(name) + 1,
-                                 kv_head_slice=kv_head_slice, pad_query_rows=pad_query_rows, **shape, **extra)
+                                 kv_head_slice=kv_head_slice, pad_query_rows=pad_query_rows, kv_dtype=kv_dtype,
+                                 **shape, **extra)
 
     # ---------------- reference arm: CPU restatement only, rank 0 only ----------------
     if args.impl == "reference":
@@ -583,16 +592,19 @@ def main():
     default_run = args.workload == "c2" and args.num_seqs is None and args.len_scale == 1.0 and not args.strong
     if default_run and not args.headline_only:
         k_steps = max(5, min(args.steps, 30))
-        names = ("c3", "c4", "c5") if world == 1 else ("c5",)
+        # "c2_e4m3_kv": the headline batch on a float8 (e4m3) pool -- half the KV bytes per token
+        names = ("c3", "c4", "c5", "c2_e4m3_kv") if world == 1 else ("c5",)
         records = {}
         for name in names:
-            b = build(name, dev, head_slice_for(name))
+            e4m3 = name.endswith("_e4m3_kv")
+            b = build(name.split("_")[0], dev, head_slice_for(name.split("_")[0]),
+                      kv_dtype=torch.float8_e4m3fn if e4m3 else None)
             r, o = measure(b, k_steps, 3)
             add_parity(name, b, o)
             status_all |= r["status_word"]
             bytes_rank = algorithmic_kv_bytes(b)
             records[name] = {
-                "workload": f"{name}: {len(b.meta['kv_lens'])} seqs, {b.total_tokens} query tokens"
+                "workload": f"{name}: {len(b.meta['kv_lens'])} seqs, {b.total_tokens} query tokens, KV cache {b.kv_pages.dtype}"
                             + (f", {b.meta['num_kv_heads']} of 8 kv heads per GPU" if world > 1 else ""),
                 "ms_per_step": r["ms_per_step"], "kernel_ms": r["prefill_ms"] + r["splitkv_ms"], "plan_ms": r["plan_ms"],
                 "merge_ms": r["merge_ms"], "tokens_per_s": b.total_tokens / (r["ms_per_step"] * 1e-3),

@@ -14,7 +14,7 @@ from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libejk_rpa.so"
 
-BF16, F16 = 0, 1
+BF16, F16, E4M3 = 0, 1, 2
 STATIC_SCRATCH_BYTES = 32 << 20
 E_SCRATCH = -9
 
@@ -56,6 +56,7 @@ class Shape(Structure):
         ("num_kv_heads", c_int32),
         ("head_dim", c_int32),
         ("dtype", c_int32),
+        ("kv_dtype", c_int32),
     ]
 
 
@@ -68,6 +69,7 @@ class Attrs(Structure):
         ("sink_rows", c_int32),
         ("num_kv_pages_per_block", c_int32),
         ("num_queries_per_block", c_int32),
+        ("q_scale", c_float),
         ("out_scale", c_float),
     ]
 

@@ -74,6 +74,11 @@ int check_shape(const ejk_rpa_shape* s) {
   if (s->head_dim != 64 && s->head_dim != 128 && s->head_dim != 256) return EJK_RPA_E_HEAD_DIM;
   if (s->dtype != EJK_RPA_BF16 && s->dtype != EJK_RPA_F16) return EJK_RPA_E_DTYPE;
   if ((long long)s->pages_per_seq * s->page_size > 0x3fffffffLL) return EJK_RPA_E_SHAPE;
+  if (s->kv_dtype != 0 && s->kv_dtype != EJK_RPA_E4M3) return EJK_RPA_E_DTYPE;
+  if (s->kv_dtype == EJK_RPA_E4M3) {
+    if (s->head_dim != 128 && s->head_dim != 256) return EJK_RPA_E_HEAD_DIM;
+    if (s->page_size < 8 || (s->page_size & (s->page_size - 1)) != 0 || (s->num_kv_heads & 1)) return EJK_RPA_E_SHAPE;
+  }
   return 0;
 }
 
@@ -187,6 +192,9 @@ static int validate(const void* queries, const void* kv_pages, const void* value
   if (!(a.softmax_scale == a.softmax_scale) || std::isinf(a.softmax_scale)) return EJK_RPA_E_ARG;
   if (!(a.logits_soft_cap == a.logits_soft_cap) || std::isinf(a.logits_soft_cap)) return EJK_RPA_E_ARG;
   if (!(a.out_scale == a.out_scale) || std::isinf(a.out_scale)) return EJK_RPA_E_ARG;
+  if (!(a.q_scale == a.q_scale) || std::isinf(a.q_scale) || a.q_scale < 0.f) return EJK_RPA_E_ARG;
+  if (a.q_scale != 0.f && (value_cache || g_opt.path == 1)) return EJK_RPA_E_ARG;  // done where the TMA kernel stages Q
+  if (s.kv_dtype == EJK_RPA_E4M3 && (value_cache || g_opt.path == 1)) return EJK_RPA_E_ARG;
   if (a.num_sinks < 0 || (a.num_sinks > 0 && !softmax_aux)) return EJK_RPA_E_ARG;
   if (a.num_sinks > 0 && a.sink_rows != s.num_q_heads && a.sink_rows != s.num_kv_heads && a.sink_rows != 1)
     return EJK_RPA_E_ARG;
@@ -200,7 +208,9 @@ static int validate(const void* queries, const void* kv_pages, const void* value
     const WorkspaceLayout L = layout_for(s, d->sm_count);
     if (workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return EJK_RPA_E_WORKSPACE;
   }
-  if (g_opt.path == 2) {  // the TMA gather was forced: refuse here, before anything is enqueued, what it cannot serve
+  if (g_opt.path == 2 || a.q_scale != 0.f || s.kv_dtype == EJK_RPA_E4M3) {
+    // the TMA gather was forced, or is the only kernel that serves the call (re-rounded queries, e4m3 cache):
+    // refuse here, before anything is enqueued, what it cannot serve
     Params probe;
     std::memset(&probe, 0, sizeof(probe));
     probe.page_size = s.page_size;
@@ -288,6 +298,8 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.sink_rows = a.sink_rows;
   const float log2e = 1.4426950408889634f;
   p.out_scale = (a.out_scale != 0.f) ? a.out_scale : 1.f;
+  p.kv8 = s.kv_dtype == EJK_RPA_E4M3;
+  p.inv_q_scale = (a.q_scale != 0.f) ? 1.f / a.q_scale : 0.f;
   p.scale = a.softmax_scale;
   p.scale_log2 = a.softmax_scale * log2e;
   p.cap = a.logits_soft_cap;
@@ -310,7 +322,9 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   if (use_tma && !tma_path_supported(p)) return EJK_RPA_E_ARG;
   // Batches that can hold a sequence with many query rows also get the tcgen05 prefill-tile
   // kernel; whether any sequence actually qualifies is decided by the planner on the device.
-  const bool use_prefill = use_tma && prefill_rows > 0 && prefill_path_supported(p) &&
+  if ((p.kv8 || p.inv_q_scale != 0.f) && !use_tma) return EJK_RPA_E_ARG;
+  // an e4m3 cache and re-rounded queries (q_scale) are served by the split-KV kernel alone
+  const bool use_prefill = use_tma && !p.kv8 && p.inv_q_scale == 0.f && prefill_rows > 0 && prefill_path_supported(p) &&
                            (long long)s.total_tokens * p.G >= prefill_rows &&
                            s.total_tokens > s.max_num_seqs;  // more query rows than sequences: some are multi-token
   p.prefill_min_rows = use_prefill ? prefill_rows : 0;
@@ -415,7 +429,7 @@ int ejk_rpa_v3_launch(const void* queries, const void* keys, const void* values,
   cudaError_t ce = launch_kv_update(keys, values, kv_cache, kv_lens, block_tables, query_start_loc, num_seqs, status,
                                     shape->total_tokens, shape->max_num_seqs, shape->pages_per_seq, shape->num_pages,
                                     shape->page_size, shape->num_kv_heads, shape->head_dim, d_align,
-                                    static_cast<cudaStream_t>(stream));
+                                    shape->kv_dtype == EJK_RPA_E4M3 ? 1 : 2, static_cast<cudaStream_t>(stream));
   if (ce != cudaSuccess) return static_cast<int>(ce);
   const int rc = launch_impl(queries, kv_cache, nullptr, kv_lens, block_tables, query_start_loc, num_seqs, nullptr, out,
                              workspace, workspace_bytes, status, shape, attrs, stream, d_align);

@@ -75,11 +75,12 @@ rpa_kv_update_kernel(const uint4* __restrict__ k_new, const uint4* __restrict__ 
 cudaError_t launch_kv_update(const void* k_new, const void* v_new, void* cache, const int32_t* kv_lens,
                              const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                              int32_t* status, int T, int S_max, int pages_per_seq, int num_pages, int page_size, int Hkv,
-                             int D, int Dalign, cudaStream_t stream) {
+                             int D, int Dalign, int elem_bytes, cudaStream_t stream) {
+  // rows move as 16-byte words: 8 elements of a 16-bit cache, 16 of an e4m3 cache
   rpa_kv_update_kernel<<<T, kUpdThreads, 0, stream>>>(
       static_cast<const uint4*>(k_new), static_cast<const uint4*>(v_new), static_cast<uint4*>(cache), kv_lens,
-      block_tables, query_start_loc, num_seqs, status, T, S_max, pages_per_seq, num_pages, page_size, Hkv, D / 8,
-      Dalign / 8);
+      block_tables, query_start_loc, num_seqs, status, T, S_max, pages_per_seq, num_pages, page_size, Hkv,
+      D * elem_bytes / 16, Dalign * elem_bytes / 16);
   return cudaGetLastError();
 }
 

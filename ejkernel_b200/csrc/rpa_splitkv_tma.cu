@@ -21,6 +21,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "rpa_device.cuh"
 #include "rpa_types.h"
 
@@ -39,12 +41,19 @@ struct ItemDesc {
   int32_t pad[3];
 };
 
-template <int D, int NT, int NS>
+// KV8: 0 = the cache has the 16-bit dtype of the queries; 1 = e4m3 cache, queries kept at 16 bits (K is widened to
+// f16 in registers for Q.K^T); 2 = e4m3 cache and queries quantised to e4m3 as they are staged (q_scale of the v3
+// operator).  With an e4m3 cache a stage holds 128 tokens -- the same bytes as 64 tokens at 16 bits -- and every
+// consumer warp takes 32 of them, the K extent of one e4m3 mma.
+template <int D, int NT, int NS, int KV8 = 0>
 struct CfgT {
-  static constexpr int TK = kTileTokens;
+  static constexpr int ESZ = KV8 ? 1 : 2;                 // bytes per cache element
+  static constexpr int TK = KV8 ? 2 * kTileTokens : kTileTokens;
+  static constexpr int TW = TK / kConsumerWarps;          // tokens of a stage per consumer warp
+  static constexpr int DC = D * ESZ / 128;                // 128-byte columns per token and K or V
   static constexpr int RT = 8 * NT;
-  static constexpr int STAGE_BYTES = TK * 2 * D * 2;
-  static constexpr int Q_ROW_BYTES = D * 2 + 16;
+  static constexpr int STAGE_BYTES = TK * 2 * D * ESZ;
+  static constexpr int Q_ROW_BYTES = (KV8 == 2 ? D : D * 2) + 16;
   static constexpr int Q_BYTES = RT * Q_ROW_BYTES;
   static constexpr int OFF_Q = NS * STAGE_BYTES;
   static constexpr int OFF_OBUF = OFF_Q + NS * Q_BYTES;
@@ -59,6 +68,7 @@ struct CfgT {
   static constexpr int OFF_BAR = OFF_META + NS * 8;        // full[NS], empty[NS], cbar
   static constexpr int OFF_ABORT = OFF_BAR + (2 * NS + 1) * 8;
   static constexpr int SMEM_BYTES = OFF_ABORT + 16 + 1024;  // + alignment slack
+  static_assert(DC >= 1, "an e4m3 cache needs head_dim >= 128 (one 128-byte swizzle row per token)");
 };
 
 // ---- TMA wrapper (mbarrier helpers live in rpa_device.cuh) ----
@@ -70,12 +80,61 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
-template <typename T, int D, int NT, int NS>
-__global__ void __launch_bounds__(kThreadsTma, (CfgT<D, NT, NS>::SMEM_BYTES <= 112 * 1024) ? 2 : 1)
+// ---- e4m3 helpers ----
+// D(16x8,f32) += A(16x32,row,e4m3) * B(32x8,col,e4m3)
+__device__ __forceinline__ void mma_e4m3(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two floats -> two e4m3 (round to nearest even, saturating at +-448) in 16 bits: `lo` in the low byte
+__device__ __forceinline__ uint32_t e4m3x2_from_f32(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// two e4m3 (16 bits) -> two f16 (exact): low byte -> low half
+__device__ __forceinline__ uint32_t f16x2_from_e4m3x2(uint32_t two) {
+  uint32_t r;
+  const uint16_t h = (uint16_t)two;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(r) : "h"(h));
+  return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t w);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+// In an e4m3 kernel the probabilities go to the P.V mma as e4m3 (the reference casts them to the cache dtype,
+// ragged_page_attention_v3/_kernel.py:281).  They are exp2(s - m) with a reference m that lags the true
+// maximum by at most 2^kLazyRescale, i.e. values up to 2^8 = 256 < 448; a new reference is set kRefBelowMax
+// below the maximum it was chosen for, which moves the values into the upper, normal range of e4m3.
+constexpr float kRefBelowMax = 4.0f;
+
+template <typename T, int D, int NT, int NS, int KV8>
+__global__ void __launch_bounds__(kThreadsTma, (CfgT<D, NT, NS, KV8>::SMEM_BYTES <= 112 * 1024) ? 2 : 1)
 rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_v,
                        const Params p) {
-  using C = CfgT<D, NT, NS>;
-  constexpr int TK = C::TK, RT = C::RT;
+  using C = CfgT<D, NT, NS, KV8>;
+  constexpr int TK = C::TK, RT = C::RT, TW = C::TW;
   constexpr int KT = D / 16;
 
   extern __shared__ uint8_t smem_raw[];
@@ -119,7 +178,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
   if (warp == kConsumerWarps) {
     // =============================== producer warp ===============================
     const int blocks_per_stage = TK >> pb_shift;
-    const uint32_t box_bytes = (uint32_t)pb * 2 * D * sizeof(T);
+    const uint32_t box_bytes = (uint32_t)pb * 2 * D * C::ESZ;
     int s = 0;
     uint32_t empty_parity = 1;  // a fresh barrier passes a wait on parity 1: all stages start empty
     int k = 0;
@@ -180,7 +239,44 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
                   reinterpret_cast<const uint8_t*>(p.q) +
                   ((size_t)(u.q_start + qt) * p.Hq + h * G + g) * D * sizeof(T) + ch * 16));
             }
-            *reinterpret_cast<uint4*>(qdst + r * C::Q_ROW_BYTES + ch * 16) = v;
+            if constexpr (KV8 == 2) {
+              // queries / q_scale, saturated to the e4m3 range and rounded to e4m3 (_kernel.py:249-254): 8 bytes
+              const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+              uint32_t o[2];
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                // the reference divides in the queries' dtype first (one rounding to 16 bits), then casts
+                float2 a = unpack2<T>(w[2 * i]), b = unpack2<T>(w[2 * i + 1]);
+                a = unpack2<T>(Mma<T>::pack(a.x * p.inv_q_scale, a.y * p.inv_q_scale));
+                b = unpack2<T>(Mma<T>::pack(b.x * p.inv_q_scale, b.y * p.inv_q_scale));
+                o[i] = e4m3x2_from_f32(a.x, a.y) | (e4m3x2_from_f32(b.x, b.y) << 16);
+              }
+              *reinterpret_cast<uint2*>(qdst + r * C::Q_ROW_BYTES + ch * 8) = make_uint2(o[0], o[1]);
+            } else if constexpr (KV8 == 1 && !std::is_same<T, __half>::value) {
+              // the e4m3 keys are widened to f16 (exact), so the queries go to f16 too (values beyond +-65504 saturate)
+              uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 a = unpack2<T>(w[i]);
+                w[i] = Mma<__half>::pack(fminf(fmaxf(a.x, -65504.f), 65504.f), fminf(fmaxf(a.y, -65504.f), 65504.f));
+              }
+              *reinterpret_cast<uint4*>(qdst + r * C::Q_ROW_BYTES + ch * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+              if (KV8 == 0 && p.inv_q_scale != 0.f) {
+                // 16-bit cache with q_scale: queries / q_scale, clipped to the finite range of the cache dtype and
+                // rounded to it (_kernel.py:249-254); the logits are multiplied back through softmax_scale
+                constexpr float kMaxT = std::is_same<T, __half>::value ? 65504.f : 3.3895313892515355e38f;
+                uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 a = unpack2<T>(w[i]);
+                  w[i] = Mma<T>::pack(fminf(fmaxf(a.x * p.inv_q_scale, -kMaxT), kMaxT),
+                                      fminf(fmaxf(a.y * p.inv_q_scale, -kMaxT), kMaxT));
+                }
+                v = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+              *reinterpret_cast<uint4*>(qdst + r * C::Q_ROW_BYTES + ch * 16) = v;
+            }
           }
         }
         int nblk = (u.kv_end - pos + pb - 1) >> pb_shift;
@@ -255,18 +351,30 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
     // per-thread shared-memory offsets of the ldmatrix rows (constant for the whole kernel)
     const uint32_t swz = (uint32_t)(lane & 7) << 4;
     const uint32_t dc_stride = (uint32_t)pb * 128;
-    uint32_t k_off, v_off;
-    {
-      const int tl = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;  // K: second matrix = tokens 8..15
+    // token tl of the stage sits in box tl / pb at row tl % pb; a box is [K|V][DC columns][pb rows][128 bytes]
+    auto row_off = [&](int tl, int kv) {
       const int j = tl >> pb_shift, tp = tl & (pb - 1);
-      k_off = (uint32_t)((j * 2) * (D / 64)) * dc_stride + (uint32_t)tp * 128;
-      const int tv = warp * 16 + (lane & 7) + (lane >> 4) * 8;        // V: third/fourth matrix = tokens 8..15
-      const int jv = tv >> pb_shift, tpv = tv & (pb - 1);
-      v_off = (uint32_t)((jv * 2 + 1) * (D / 64)) * dc_stride + (uint32_t)tpv * 128;
+      return (uint32_t)((j * 2 + kv) * C::DC) * dc_stride + (uint32_t)tp * 128;
+    };
+    uint32_t k_off, v_off, k_off1 = 0;
+    if constexpr (KV8 == 0) {
+      k_off = row_off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 0);  // K: second matrix = tokens 8..15
+      v_off = row_off(warp * 16 + (lane & 7) + (lane >> 4) * 8, 1);        // V: third/fourth matrix = tokens 8..15
+    } else {
+      // K: two 16-token blocks, in each the matrices (tokens 0-7 | 8-15) x (16-byte chunk c | c + 1);
+      // V: four transposed matrices of one chunk, tokens 8j .. 8j+7
+      k_off = row_off(warp * TW + (lane & 7) + ((lane >> 3) & 1) * 8, 0);
+      k_off1 = row_off(warp * TW + 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 0);
+      v_off = row_off(warp * TW + (lane & 7) + (lane >> 3) * 8, 1);
     }
     const int k_dhalf = lane >> 4, v_dhalf = (lane >> 3) & 1;
 
-    uint32_t qf[NT][KT][2];
+    // query fragments (B operands of Q.K^T), per 8-row tile and k step:
+    //   16-bit cache: D/16 steps x 2 registers; e4m3 queries: D/32 steps x 2; f16 queries against e4m3 keys:
+    //   D/32 steps x 4 (two f16 mmas per 32-byte chunk of K)
+    constexpr int QK_STEPS = KV8 ? D / 32 : D / 16;
+    constexpr int QREGS = KV8 == 1 ? 4 : 2;
+    uint32_t qf[NT][QK_STEPS][QREGS];
     float acc[NT][KT][4];
     float m_run[NT][2], l_run[NT][2];
     int pos_r[NT][2], lo_r[NT][2];
@@ -299,11 +407,26 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
         const uint8_t* qs = smem + C::OFF_Q + s * C::Q_BYTES;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          const uint8_t* qrow = qs + (nt * 8 + (lane >> 2)) * C::Q_ROW_BYTES + (lane & 3) * 4;
+          if constexpr (KV8 == 1) {
+            // f16 queries: elements 32kt + 4t .. +3 (first mma of the chunk) and 32kt + 16 + 4t .. +3 (second)
+            const uint8_t* qrow = qs + (nt * 8 + (lane >> 2)) * C::Q_ROW_BYTES + (lane & 3) * 8;
 #pragma unroll
-          for (int kt = 0; kt < KT; ++kt) {
-            qf[nt][kt][0] = *reinterpret_cast<const uint32_t*>(qrow + kt * 32);
-            qf[nt][kt][1] = *reinterpret_cast<const uint32_t*>(qrow + kt * 32 + 16);
+            for (int kt = 0; kt < QK_STEPS; ++kt) {
+              const uint2 a = *reinterpret_cast<const uint2*>(qrow + kt * 64);
+              const uint2 b = *reinterpret_cast<const uint2*>(qrow + kt * 64 + 32);
+              qf[nt][kt][0] = a.x;
+              qf[nt][kt][1] = a.y;
+              qf[nt][kt][2] = b.x;
+              qf[nt][kt][3] = b.y;
+            }
+          } else {
+            // 16-bit: elements 16kt + 2t, +1 and 16kt + 8 + 2t, +1; e4m3: bytes 32kt + 4t .. +3 and 32kt + 16 + 4t .. +3
+            const uint8_t* qrow = qs + (nt * 8 + (lane >> 2)) * C::Q_ROW_BYTES + (lane & 3) * 4;
+#pragma unroll
+            for (int kt = 0; kt < QK_STEPS; ++kt) {
+              qf[nt][kt][0] = *reinterpret_cast<const uint32_t*>(qrow + kt * 32);
+              qf[nt][kt][1] = *reinterpret_cast<const uint32_t*>(qrow + kt * 32 + 16);
+            }
           }
         }
         const int base = u.kv_len - u.q_len;
@@ -328,109 +451,255 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
             for (int e = 0; e < 4; ++e) acc[nt][kt][e] = 0.f;
       }
 
-      const int key0 = pos + warp * 16;
-      if (key0 < u.kv_end) {
-        float sc[NT][4];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) sc[nt][e] = 0.f;
-#pragma unroll
-        for (int kt = 0; kt < KT; ++kt) {
-          const int d16 = kt * 2;  // + k_dhalf at run time; both fold into one XOR below
-          uint32_t a[4];
-          ldmatrix_x4(a, sbase + k_off + (uint32_t)(d16 >> 3) * dc_stride +
-                             ((((uint32_t)(d16 & 7) | (uint32_t)k_dhalf) << 4) ^ swz));
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) Mma<T>::run(sc[nt], a, qf[nt][kt][0], qf[nt][kt][1]);
-        }
-        const bool tail = key0 + 16 > u.kv_end;  // tokens past the chunk end: stale or unowned bytes
-        const bool need_mask = tail || (key0 + 15 > pos_min) || (key0 <= lo_max);
-        uint32_t pbf[NT][2];
-        bool grow = false;
-        float mx[NT][2];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float x = sc[nt][e];
-            if (p.cap != 0.f) x = p.cap_log2 * soft_cap_tanh(x * p.inv_cap_scale);
-            else x *= p.scale_log2;
-            if (need_mask) {
-              const int key = key0 + (lane >> 2) + (e >> 1) * 8;
-              const int j = e & 1;
-              if (key > pos_r[nt][j] || key <= lo_r[nt][j]) x = -INFINITY;
+      if constexpr (KV8 == 0) {
+        const int key0 = pos + warp * 16;
+        if (key0 < u.kv_end) {
+          float sc[NT][4];
+  #pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+  #pragma unroll
+            for (int e = 0; e < 4; ++e) sc[nt][e] = 0.f;
+  #pragma unroll
+          for (int kt = 0; kt < KT; ++kt) {
+            const int d16 = kt * 2;  // + k_dhalf at run time; both fold into one XOR below
+            uint32_t a[4];
+            ldmatrix_x4(a, sbase + k_off + (uint32_t)(d16 >> 3) * dc_stride +
+                               ((((uint32_t)(d16 & 7) | (uint32_t)k_dhalf) << 4) ^ swz));
+  #pragma unroll
+            for (int nt = 0; nt < NT; ++nt) Mma<T>::run(sc[nt], a, qf[nt][kt][0], qf[nt][kt][1]);
+          }
+          const bool tail = key0 + 16 > u.kv_end;  // tokens past the chunk end: stale or unowned bytes
+          const bool need_mask = tail || (key0 + 15 > pos_min) || (key0 <= lo_max);
+          uint32_t pbf[NT][2];
+          bool grow = false;
+          float mx[NT][2];
+  #pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+  #pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float x = sc[nt][e];
+              if (p.cap != 0.f) x = p.cap_log2 * soft_cap_tanh(x * p.inv_cap_scale);
+              else x *= p.scale_log2;
+              if (need_mask) {
+                const int key = key0 + (lane >> 2) + (e >> 1) * 8;
+                const int j = e & 1;
+                if (key > pos_r[nt][j] || key <= lo_r[nt][j]) x = -INFINITY;
+              }
+              sc[nt][e] = x;
             }
-            sc[nt][e] = x;
+  #pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              float v = fmaxf(sc[nt][j], sc[nt][j + 2]);
+              v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+              v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+              v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+              mx[nt][j] = v;
+              // lazy rescaling: keep the old reference maximum unless the new one is 2^8 larger
+              grow |= (v > m_run[nt][j] + kLazyRescale) || (m_run[nt][j] == -INFINITY && v > -INFINITY);
+            }
           }
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            float v = fmaxf(sc[nt][j], sc[nt][j + 2]);
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-            v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
-            mx[nt][j] = v;
-            // lazy rescaling: keep the old reference maximum unless the new one is 2^8 larger
-            grow |= (v > m_run[nt][j] + kLazyRescale) || (m_run[nt][j] == -INFINITY && v > -INFINITY);
+          if (__any_sync(0xffffffffu, grow)) {
+  #pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              float alpha[2];
+  #pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const bool g = (mx[nt][j] > m_run[nt][j] + kLazyRescale) || (m_run[nt][j] == -INFINITY && mx[nt][j] > -INFINITY);
+                const float m_new = g ? mx[nt][j] : m_run[nt][j];
+                alpha[j] = g ? fast_exp2(m_run[nt][j] - m_new) : 1.f;  // exp2(-inf) = 0 on the first tile
+                m_run[nt][j] = m_new;
+                l_run[nt][j] *= alpha[j];
+              }
+  #pragma unroll
+              for (int kt = 0; kt < KT; ++kt) {
+                acc[nt][kt][0] *= alpha[0];
+                acc[nt][kt][1] *= alpha[1];
+                acc[nt][kt][2] *= alpha[0];
+                acc[nt][kt][3] *= alpha[1];
+              }
+            }
+          }
+  #pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+  #pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const float m_use = (m_run[nt][j] == -INFINITY) ? 0.f : m_run[nt][j];
+              const float p0 = fast_exp2(sc[nt][j] - m_use);
+              const float p1 = fast_exp2(sc[nt][j + 2] - m_use);
+              sc[nt][j] = p0;
+              sc[nt][j + 2] = p1;
+              l_run[nt][j] += p0 + p1;
+            }
+            pbf[nt][0] = movmatrix_trans(Mma<T>::pack(sc[nt][0], sc[nt][1]));
+            pbf[nt][1] = movmatrix_trans(Mma<T>::pack(sc[nt][2], sc[nt][3]));
+          }
+          // V^T fragments; in a tail tile the registers of tokens >= kv_end are cleared so that
+          // 0 * (stale NaN) can never reach the accumulators
+          uint32_t vmask_lo = 0xffffffffu, vmask_hi = 0xffffffffu;
+          if (tail) {
+            const int t0 = key0 + (lane & 3) * 2;
+            vmask_lo = (t0 < u.kv_end ? 0x0000ffffu : 0u) | (t0 + 1 < u.kv_end ? 0xffff0000u : 0u);
+            vmask_hi = (t0 + 8 < u.kv_end ? 0x0000ffffu : 0u) | (t0 + 9 < u.kv_end ? 0xffff0000u : 0u);
+          }
+  #pragma unroll
+          for (int mt = 0; mt < KT; ++mt) {
+            const int d16 = mt * 2;
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, sbase + v_off + (uint32_t)(d16 >> 3) * dc_stride +
+                                     ((((uint32_t)(d16 & 7) | (uint32_t)v_dhalf) << 4) ^ swz));
+            if (tail) {
+              a[0] &= vmask_lo;
+              a[1] &= vmask_lo;
+              a[2] &= vmask_hi;
+              a[3] &= vmask_hi;
+            }
+  #pragma unroll
+            for (int nt = 0; nt < NT; ++nt) Mma<T>::run(acc[nt][mt], a, pbf[nt][0], pbf[nt][1]);
           }
         }
-        if (__any_sync(0xffffffffu, grow)) {
+      } else {
+        // ---------------- e4m3 cache: this warp's 32 tokens of the stage ----------------
+        const int key0 = pos + warp * TW;
+        if (key0 < u.kv_end) {
+          // S^T[32 tokens x 8 rows] = K . Q^T as two 16-token blocks
+          float sc[NT][2][4];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) sc[nt][b][e] = 0.f;
+#pragma unroll
+          for (int kt = 0; kt < QK_STEPS; ++kt) {
+            const int c16 = kt * 2;  // 16-byte chunk of the token row; + k_dhalf at run time
+            const uint32_t coff = (uint32_t)(c16 >> 3) * dc_stride + ((((uint32_t)(c16 & 7) | (uint32_t)k_dhalf) << 4) ^ swz);
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+              // a[0] = (token g, bytes 4t..4t+3 of the chunk), a[1] = token g+8, a[2] / a[3] = the next chunk
+              uint32_t a[4];
+              ldmatrix_x4(a, sbase + (b ? k_off1 : k_off) + coff);
+              if constexpr (KV8 == 2) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_e4m3(sc[nt][b], a, qf[nt][kt][0], qf[nt][kt][1]);
+              } else {
+                // widen to f16: the low two bytes of a register become k slots 2t, 2t+1, the high two k slots
+                // 8+2t, 8+2t+1 of one f16 mma -- the query fragments were loaded in the same order
+                const uint32_t l0 = f16x2_from_e4m3x2(a[0]), h0 = f16x2_from_e4m3x2(a[0] >> 16);
+                const uint32_t l1 = f16x2_from_e4m3x2(a[1]), h1 = f16x2_from_e4m3x2(a[1] >> 16);
+                const uint32_t l2 = f16x2_from_e4m3x2(a[2]), h2 = f16x2_from_e4m3x2(a[2] >> 16);
+                const uint32_t l3 = f16x2_from_e4m3x2(a[3]), h3 = f16x2_from_e4m3x2(a[3] >> 16);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                  mma_f16(sc[nt][b], l0, l1, h0, h1, qf[nt][kt][0], qf[nt][kt][1]);
+                  mma_f16(sc[nt][b], l2, l3, h2, h3, qf[nt][kt][2], qf[nt][kt][3]);
+                }
+              }
+            }
+          }
+          const bool tail = key0 + TW > u.kv_end;  // tokens past the chunk end: stale or unowned bytes
+          const bool need_mask = tail || (key0 + TW - 1 > pos_min) || (key0 <= lo_max);
+          bool grow = false;
+          float mx[NT][2];
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            float alpha[2];
+#pragma unroll
+            for (int b = 0; b < 2; ++b)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float x = sc[nt][b][e];
+                if (p.cap != 0.f) x = p.cap_log2 * soft_cap_tanh(x * p.inv_cap_scale);
+                else x *= p.scale_log2;
+                if (need_mask) {
+                  // a 128-token stage can straddle the end of a chunk (chunks are cut at multiples of 64): keys from
+                  // kv_end on belong to the next chunk, or to nobody
+                  const int key = key0 + b * 16 + (lane >> 2) + (e >> 1) * 8;
+                  const int j = e & 1;
+                  if (key > pos_r[nt][j] || key <= lo_r[nt][j] || key >= u.kv_end) x = -INFINITY;
+                }
+                sc[nt][b][e] = x;
+              }
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-              const bool g = (mx[nt][j] > m_run[nt][j] + kLazyRescale) || (m_run[nt][j] == -INFINITY && mx[nt][j] > -INFINITY);
-              const float m_new = g ? mx[nt][j] : m_run[nt][j];
-              alpha[j] = g ? fast_exp2(m_run[nt][j] - m_new) : 1.f;  // exp2(-inf) = 0 on the first tile
-              m_run[nt][j] = m_new;
-              l_run[nt][j] *= alpha[j];
-            }
-#pragma unroll
-            for (int kt = 0; kt < KT; ++kt) {
-              acc[nt][kt][0] *= alpha[0];
-              acc[nt][kt][1] *= alpha[1];
-              acc[nt][kt][2] *= alpha[0];
-              acc[nt][kt][3] *= alpha[1];
+              float v = fmaxf(fmaxf(sc[nt][0][j], sc[nt][0][j + 2]), fmaxf(sc[nt][1][j], sc[nt][1][j + 2]));
+              v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+              v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+              v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+              mx[nt][j] = v;
+              // the reference sits kRefBelowMax below the maximum it was chosen for and is kept until the
+              // maximum has grown 2^8 beyond it, so exp2(s - m) never exceeds 256 (e4m3 holds 448)
+              grow |= (v > m_run[nt][j] + kLazyRescale) || (m_run[nt][j] == -INFINITY && v > -INFINITY);
             }
           }
-        }
+          if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
+            for (int nt = 0; nt < NT; ++nt) {
+              float alpha[2];
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const float m_use = (m_run[nt][j] == -INFINITY) ? 0.f : m_run[nt][j];
-            const float p0 = fast_exp2(sc[nt][j] - m_use);
-            const float p1 = fast_exp2(sc[nt][j + 2] - m_use);
-            sc[nt][j] = p0;
-            sc[nt][j + 2] = p1;
-            l_run[nt][j] += p0 + p1;
+              for (int j = 0; j < 2; ++j) {
+                const bool g = (mx[nt][j] > m_run[nt][j] + kLazyRescale) || (m_run[nt][j] == -INFINITY && mx[nt][j] > -INFINITY);
+                const float m_new = g ? mx[nt][j] - kRefBelowMax : m_run[nt][j];
+                alpha[j] = g ? fast_exp2(m_run[nt][j] - m_new) : 1.f;  // exp2(-inf) = 0 on the first tile
+                m_run[nt][j] = m_new;
+                l_run[nt][j] *= alpha[j];
+              }
+#pragma unroll
+              for (int mt = 0; mt < KT; ++mt) {
+                acc[nt][mt][0] *= alpha[0];
+                acc[nt][mt][1] *= alpha[1];
+                acc[nt][mt][2] *= alpha[0];
+                acc[nt][mt][3] *= alpha[1];
+              }
+            }
           }
-          pbf[nt][0] = movmatrix_trans(Mma<T>::pack(sc[nt][0], sc[nt][1]));
-          pbf[nt][1] = movmatrix_trans(Mma<T>::pack(sc[nt][2], sc[nt][3]));
-        }
-        // V^T fragments; in a tail tile the registers of tokens >= kv_end are cleared so that
-        // 0 * (stale NaN) can never reach the accumulators
-        uint32_t vmask_lo = 0xffffffffu, vmask_hi = 0xffffffffu;
-        if (tail) {
-          const int t0 = key0 + (lane & 3) * 2;
-          vmask_lo = (t0 < u.kv_end ? 0x0000ffffu : 0u) | (t0 + 1 < u.kv_end ? 0xffff0000u : 0u);
-          vmask_hi = (t0 + 8 < u.kv_end ? 0x0000ffffu : 0u) | (t0 + 9 < u.kv_end ? 0xffff0000u : 0u);
-        }
+          // probabilities -> e4m3, transposed into the B fragments of P.V: after the transpose the four bytes of
+          // pb[nt][b] belong to query row g and tokens 16b + {2t, 2t+8, 2t+1, 2t+9}
+          uint32_t pb8[NT][2];
 #pragma unroll
-        for (int mt = 0; mt < KT; ++mt) {
-          const int d16 = mt * 2;
-          uint32_t a[4];
-          ldmatrix_x4_trans(a, sbase + v_off + (uint32_t)(d16 >> 3) * dc_stride +
-                                   ((((uint32_t)(d16 & 7) | (uint32_t)v_dhalf) << 4) ^ swz));
+          for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const float m_use = (m_run[nt][j] == -INFINITY) ? 0.f : m_run[nt][j];
+                const float p0 = fast_exp2(sc[nt][b][j] - m_use);
+                const float p1 = fast_exp2(sc[nt][b][j + 2] - m_use);
+                sc[nt][b][j] = p0;
+                sc[nt][b][j + 2] = p1;
+                l_run[nt][j] += p0 + p1;
+              }
+              // element (token g, row 2t) pairs with (token g+8, row 2t) in the low half, rows 2t+1 in the high half
+              const uint32_t w = e4m3x2_from_f32(sc[nt][b][0], sc[nt][b][2]) | (e4m3x2_from_f32(sc[nt][b][1], sc[nt][b][3]) << 16);
+              pb8[nt][b] = movmatrix_trans(w);
+            }
+          }
+          // V^T fragments: four transposed 8-token matrices of one 16-byte chunk; register j holds, for the
+          // two head-dim lanes 2g and 2g+1, tokens 8j + 2t (low half) and 8j + 2t + 1 (high half).  In a tail
+          // tile the bytes of tokens >= kv_end are cleared, so that 0 * (stale NaN) cannot reach the accumulators.
+          uint32_t vmask[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
           if (tail) {
-            a[0] &= vmask_lo;
-            a[1] &= vmask_lo;
-            a[2] &= vmask_hi;
-            a[3] &= vmask_hi;
+            const int t0 = key0 + (lane & 3) * 2;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              vmask[j] = (t0 + 8 * j < u.kv_end ? 0x0000ffffu : 0u) | (t0 + 8 * j + 1 < u.kv_end ? 0xffff0000u : 0u);
           }
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) Mma<T>::run(acc[nt][mt], a, pbf[nt][0], pbf[nt][1]);
+          for (int mt = 0; mt < KT; ++mt) {
+            uint32_t r[4];
+            ldmatrix_x4_trans(r, sbase + v_off + (uint32_t)(mt >> 3) * dc_stride + (((uint32_t)(mt & 7) << 4) ^ swz));
+            if (tail) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) r[j] &= vmask[j];
+            }
+            // rows of the mma: g <-> head-dim lane 16mt + 2g, g+8 <-> lane 16mt + 2g + 1; k slots in the token
+            // order of pb8
+            uint32_t a[4];
+            a[0] = prmt(r[0], r[1], 0x6240u);
+            a[1] = prmt(r[0], r[1], 0x7351u);
+            a[2] = prmt(r[2], r[3], 0x6240u);
+            a[3] = prmt(r[2], r[3], 0x7351u);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma_e4m3(acc[nt][mt], a, pb8[nt][0], pb8[nt][1]);
+          }
         }
       }
       // this warp is done with the stage's bytes (query fragments are in registers by now)
@@ -517,19 +786,22 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
               for (int sl = 0; sl < kConsumerWarps; ++sl) {
                 if (sl == slice) {
                   const int mt = sl * (KT / kConsumerWarps) + mi;
-                  const int d = mt * 16 + (lane >> 2);
+                  // accumulator rows g / g+8 of block mt are head-dim lanes 16mt + g / + 8, or, in the e4m3
+                  // kernels (see the V fragments), 16mt + 2g / + 1
+                  constexpr int HI = KV8 ? 1 : 8;
+                  const int d = mt * 16 + (lane >> 2) * (KV8 ? 2 : 1);
                   float* o0 = &obuf[r0 * D + d];
                   float* o1 = &obuf[(r0 + 1) * D + d];
                   if (round == 0) {
                     o0[0] = acc[nt][mt][0] * f0;
-                    o0[8] = acc[nt][mt][2] * f0;
+                    o0[HI] = acc[nt][mt][2] * f0;
                     o1[0] = acc[nt][mt][1] * f1;
-                    o1[8] = acc[nt][mt][3] * f1;
+                    o1[HI] = acc[nt][mt][3] * f1;
                   } else {
                     o0[0] += acc[nt][mt][0] * f0;
-                    o0[8] += acc[nt][mt][2] * f0;
+                    o0[HI] += acc[nt][mt][2] * f0;
                     o1[0] += acc[nt][mt][1] * f1;
-                    o1[8] += acc[nt][mt][3] * f1;
+                    o1[HI] += acc[nt][mt][3] * f1;
                   }
                 }
               }
@@ -690,10 +962,10 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-template <typename T, int D, int NT, int NS>
+template <typename T, int D, int NT, int NS, int KV8>
 cudaError_t launch_one(const Params& p, const CUtensorMap& map, const CUtensorMap& map_v, int n_sm, cudaStream_t stream, bool pdl) {
-  using C = CfgT<D, NT, NS>;
-  auto kern = rpa_splitkv_tma_kernel<T, D, NT, NS>;
+  using C = CfgT<D, NT, NS, KV8>;
+  auto kern = rpa_splitkv_tma_kernel<T, D, NT, NS, KV8>;
   static bool configured[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -707,16 +979,26 @@ cudaError_t launch_one(const Params& p, const CUtensorMap& map, const CUtensorMa
   return launch_kernel(kern, dim3(n_sm * per_sm), dim3(kThreadsTma), C::SMEM_BYTES, stream, pdl, map, map_v, p);
 }
 
-template <typename T>
+template <typename T, int KV8>
 cudaError_t dispatch(const Params& p, const CUtensorMap& map, const CUtensorMap& map_v, int n_sm, cudaStream_t stream, bool pdl) {
   const bool wide = p.rows_per_tile == 16;
-  switch (p.D) {
-    case 64:
-      return wide ? launch_one<T, 64, 2, 4>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 64, 1, 4>(p, map, map_v, n_sm, stream, pdl);
-    case 128:
-      return wide ? launch_one<T, 128, 2, 3>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 128, 1, 3>(p, map, map_v, n_sm, stream, pdl);
-    case 256:
-      return wide ? launch_one<T, 256, 2, 2>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 256, 1, 3>(p, map, map_v, n_sm, stream, pdl);
+  if constexpr (KV8 == 0) {
+    switch (p.D) {
+      case 64:
+        return wide ? launch_one<T, 64, 2, 4, 0>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 64, 1, 4, 0>(p, map, map_v, n_sm, stream, pdl);
+      case 128:
+        return wide ? launch_one<T, 128, 2, 3, 0>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 128, 1, 3, 0>(p, map, map_v, n_sm, stream, pdl);
+      case 256:
+        return wide ? launch_one<T, 256, 2, 2, 0>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 256, 1, 3, 0>(p, map, map_v, n_sm, stream, pdl);
+    }
+  } else {
+    // an e4m3 stage of 128 tokens has the bytes of a 16-bit stage of 64 tokens: same stage counts
+    switch (p.D) {
+      case 128:
+        return wide ? launch_one<T, 128, 2, 3, KV8>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 128, 1, 3, KV8>(p, map, map_v, n_sm, stream, pdl);
+      case 256:
+        return wide ? launch_one<T, 256, 2, 2, KV8>(p, map, map_v, n_sm, stream, pdl) : launch_one<T, 256, 1, 3, KV8>(p, map, map_v, n_sm, stream, pdl);
+    }
   }
   return cudaErrorInvalidValue;
 }
@@ -732,21 +1014,25 @@ bool tma_path_supported(const Params& p) {
 cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream, bool pdl) {
   EncodeFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
-  const uint64_t esz = 2;
+  // elements of the innermost dimension: one 128-byte swizzle row = 64 16-bit or 128 e4m3 values
+  const bool kv8 = p.kv8 != 0;
+  const uint64_t esz = kv8 ? 1 : 2, inner = 128 / esz;
   const uint64_t D = p.D, Dkv = p.Dkv, C2 = 2ull * p.Hkv;
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-  const CUtensorMapDataType dt = (dtype == EJK_RPA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = kv8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                     : (dtype == EJK_RPA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap map, map_v;
   if (p.v_cache == nullptr) {
-    // dims, innermost first: 64 elements | token in page | 64-element chunk of D | combined head | page
-    cuuint64_t dims[5] = {64, (cuuint64_t)p.page_size, D / 64, C2, (cuuint64_t)p.num_pages};
-    cuuint64_t strides[4] = {C2 * Dkv * esz, 64 * esz, Dkv * esz, (cuuint64_t)p.page_size * C2 * Dkv * esz};
-    cuuint32_t box[5] = {64, (cuuint32_t)p.tma_block_tokens, (cuuint32_t)(D / 64), 2, 1};
+    // dims, innermost first: one swizzle row of elements | token in page | column of D | combined head | page
+    cuuint64_t dims[5] = {inner, (cuuint64_t)p.page_size, D / inner, C2, (cuuint64_t)p.num_pages};
+    cuuint64_t strides[4] = {C2 * Dkv * esz, inner * esz, Dkv * esz, (cuuint64_t)p.page_size * C2 * Dkv * esz};
+    cuuint32_t box[5] = {(cuuint32_t)inner, (cuuint32_t)p.tma_block_tokens, (cuuint32_t)(D / inner), 2, 1};
     CUresult r = enc(&map, dt, 5, const_cast<void*>(p.kv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     map_v = map;
   } else {
+    if (kv8) return cudaErrorInvalidValue;  // separate key / value caches: 16-bit only
     // key_cache / value_cache [P, Hkv, page, D]: 64 elements | token in page | chunk of D | kv head | page
     cuuint64_t dims[5] = {64, (cuuint64_t)p.page_size, D / 64, (cuuint64_t)p.Hkv, (cuuint64_t)p.num_pages};
     cuuint64_t strides[4] = {D * esz, 64 * esz, (cuuint64_t)p.page_size * D * esz,
@@ -759,8 +1045,16 @@ cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   }
-  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16>(p, map, map_v, n_sm, stream, pdl);
-  return dispatch<__half>(p, map, map_v, n_sm, stream, pdl);
+  if (kv8) {
+    // queries quantised to e4m3 (q_scale given) or kept at 16 bits
+    if (p.inv_q_scale != 0.f)
+      return dtype == EJK_RPA_BF16 ? dispatch<__nv_bfloat16, 2>(p, map, map_v, n_sm, stream, pdl)
+                                   : dispatch<__half, 2>(p, map, map_v, n_sm, stream, pdl);
+    return dtype == EJK_RPA_BF16 ? dispatch<__nv_bfloat16, 1>(p, map, map_v, n_sm, stream, pdl)
+                                 : dispatch<__half, 1>(p, map, map_v, n_sm, stream, pdl);
+  }
+  if (dtype == EJK_RPA_BF16) return dispatch<__nv_bfloat16, 0>(p, map, map_v, n_sm, stream, pdl);
+  return dispatch<__half, 0>(p, map, map_v, n_sm, stream, pdl);
 }
 
 }  // namespace ejk

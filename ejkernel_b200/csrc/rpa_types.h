@@ -105,6 +105,8 @@ struct Params {
   int32_t prefill_min_rows;  // sequences with q_len*G >= this go to the prefill-tile kernel; 0 = never
   int32_t window;      // <= 0: none
   int32_t num_sinks, sink_rows;
+  int32_t kv8;         // 1: the cache holds e4m3 bytes (queries / out keep their 16-bit dtype)
+  float inv_q_scale;   // e4m3 cache only: != 0 quantises the staged queries to e4m3 after multiplying by this
   float out_scale;     // factor on the normalised output (v_scale of the v3 operator), 1 otherwise
   float scale;         // softmax_scale
   float scale_log2;    // softmax_scale * log2(e)
@@ -149,6 +151,6 @@ cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stre
 cudaError_t launch_kv_update(const void* k_new, const void* v_new, void* cache, const int32_t* kv_lens,
                              const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                              int32_t* status, int T, int S_max, int pages_per_seq, int num_pages, int page_size, int Hkv,
-                             int D, int Dalign, cudaStream_t stream);
+                             int D, int Dalign, int elem_bytes, cudaStream_t stream);
 
 }  // namespace ejk

@@ -43,6 +43,7 @@ from ..._registry import Backend, Platform, kernel_registry
 DTypeLike = torch.dtype | str | None
 
 _DTYPE_CODE = {torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16}
+FP8 = torch.float8_e4m3fn  # the 8-bit cache dtype (e4m3, no infinities, maximum 448)
 
 
 class RpaWorkspace:
@@ -102,7 +103,8 @@ def _shape_of(queries, kv_pages, block_tables) -> _cabi.Shape:
     T, Hq, D = queries.shape
     P, page, C2, _ = kv_pages.shape
     S_max, pps = block_tables.shape
-    return _cabi.Shape(T, S_max, pps, P, page, Hq, C2 // 2, D, _DTYPE_CODE[queries.dtype])
+    return _cabi.Shape(T, S_max, pps, P, page, Hq, C2 // 2, D, _DTYPE_CODE[queries.dtype],
+                       _cabi.E4M3 if kv_pages.dtype == FP8 else 0)
 
 
 def _validate(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, *, sliding_window,
@@ -119,10 +121,14 @@ def _validate(queries, kv_pages, context_lens, block_tables, query_start_loc, nu
             raise ValueError(f"{name} is on {t.device}, queries on {queries.device}")
     if queries.dtype not in _DTYPE_CODE:
         raise NotImplementedError(f"queries dtype {queries.dtype} is not supported by the CUDA path (bf16/f16 only)")
-    if kv_pages.dtype != queries.dtype:
-        raise NotImplementedError(f"kv_pages dtype {kv_pages.dtype} must equal queries dtype {queries.dtype}")
+    if kv_pages.dtype != queries.dtype and kv_pages.dtype != FP8:
+        raise NotImplementedError(f"kv_pages dtype {kv_pages.dtype} must equal queries dtype {queries.dtype} or be {FP8}")
     _, num_q_heads, head_dim = queries.shape
-    _, _, num_combined_kv_heads, head_dim_k = kv_pages.shape
+    _, page_size, num_combined_kv_heads, head_dim_k = kv_pages.shape
+    if kv_pages.dtype == FP8:
+        if head_dim not in (128, 256) or page_size < 8 or page_size & (page_size - 1) or num_combined_kv_heads % 4:
+            raise NotImplementedError("an e4m3 KV cache needs head_dim 128 or 256, a page size that is a power of two >= 8 "
+                                      "and an even number of kv heads")
     if num_combined_kv_heads % 2 != 0:
         raise ValueError(f"{num_combined_kv_heads=} must be even (K and V heads interleaved)")
     num_kv_heads = num_combined_kv_heads // 2

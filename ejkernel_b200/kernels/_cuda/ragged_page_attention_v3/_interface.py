@@ -13,9 +13,14 @@ semantics of its kernel (ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.
     i.e. ``kv_lens`` already counts the new tokens;
   * ``block_tables`` is flat ``[max_num_seqs * pages_per_seq]``; ``distribution[2]`` is the number of
     sequences (:211);
-  * ``softmax_scale`` defaults to 1.0 (sic); ``k_scale`` multiplies the logits, ``v_scale`` the output
-    (:262-263, :290-291).  ``q_scale`` divides the queries before they are cast to the cache dtype and
-    multiplies the logits back (:249-265); with a 16-bit cache that only changes rounding and is folded away.
+  * ``softmax_scale`` defaults to 1.0 (sic); ``k_scale`` multiplies the logits, ``v_scale`` the output, in
+    float32 before the cast to the output dtype (:262-263, :283-291).  ``q_scale`` divides the queries, which are
+    then clipped to the finite range of the cache dtype and cast to it, and multiplies the logits back (:249-265);
+  * the cache may be float8 e4m3 (``torch.float8_e4m3fn``) with ``keys`` / ``values`` of the same dtype and 16-bit
+    ``queries``: ``pack`` is then 4.  Without ``q_scale`` the keys are widened to f16 for Q.K^T; with it Q.K^T runs
+    on e4m3 operands.  The probabilities go into P.V as e4m3, as in the reference (:281), but unnormalised
+    (``exp(s - m)`` against a running reference ``m``, values in (0, 256]) where the reference rounds the
+    normalised ones -- which flushes every probability below 2^-10 to zero, i.e. most of a long context.
 
 The cache is updated IN PLACE and returned (the reference donates it, :141).  A ``head_dim`` that is not
 a multiple of 128 lives in a cache padded to one (``align_to(D, 128)``, :45-57): the page write zero-fills
@@ -33,11 +38,11 @@ from torch import Tensor as Array
 from .... import _cabi
 from .._typecheck import typechecked_once
 from ..._registry import Backend, Platform, kernel_registry
-from ..ragged_page_attention._interface import _DTYPE_CODE, cached_workspace
+from ..ragged_page_attention._interface import _DTYPE_CODE, FP8, cached_workspace
 
 
 def _packing(dtype: torch.dtype) -> int:
-    return 32 // (torch.finfo(dtype).bits)
+    return 32 // (torch.finfo(dtype).bits)  # get_dtype_packing, _kernel.py:38-39
 
 
 @kernel_registry.register("ragged_page_attention_v3", Platform.CUDA, Backend.GPU)
@@ -68,8 +73,6 @@ def ragged_page_attention_v3(
 ]:
     """Returns ``(out, kv_cache)``; ``kv_cache`` is the same tensor, updated in place."""
     del chunk_prefill_size, num_kv_pages_per_block, num_queries_per_block, vmem_limit_bytes
-    if q_scale is not None:
-        raise NotImplementedError("q_scale (queries quantised to the cache dtype, _kernel.py:249-265) is not implemented")
     # static half of the reference's contract (_kernel.py:73-126)
     if not queries.is_cuda:
         raise RuntimeError("ragged_page_attention_v3[cuda]: tensors must live on a CUDA device (no CPU fallback)")
@@ -80,8 +83,16 @@ def ragged_page_attention_v3(
     if Hq % Hkv != 0:
         raise ValueError("num_q_heads must be divisible by num_kv_heads")
     P, page_size, hx2_per_pack, pack, d_align = kv_cache.shape
-    if queries.dtype not in _DTYPE_CODE or any(t.dtype != queries.dtype for t in (keys, values, kv_cache)):
-        raise NotImplementedError("queries, keys, values and kv_cache must share one 16-bit float dtype (bf16/f16)")
+    if queries.dtype not in _DTYPE_CODE:
+        raise NotImplementedError("queries must be bf16 or f16")
+    if kv_cache.dtype not in (queries.dtype, FP8) or keys.dtype != kv_cache.dtype or values.dtype != kv_cache.dtype:
+        raise NotImplementedError("keys, values and kv_cache must share one dtype: that of the queries, or float8_e4m3fn")
+    fp8 = kv_cache.dtype == FP8
+    if fp8 and (D not in (128, 256) or page_size < 8 or page_size & (page_size - 1)):
+        raise NotImplementedError("an e4m3 KV cache needs head_dim 128 or 256 and a page size that is a power of two >= 8")
+    for name, sc in (("q_scale", q_scale), ("k_scale", k_scale), ("v_scale", v_scale)):
+        if sc is not None and not (sc > 0.0 and sc < float("inf")):
+            raise ValueError(f"{name} must be positive and finite")
     if pack != _packing(kv_cache.dtype):
         raise ValueError("packing mismatch")
     if d_align != -(-D // 128) * 128:
@@ -108,12 +119,14 @@ def ragged_page_attention_v3(
             raise ValueError(f"{name} is on {t.device}, queries on {queries.device}")
 
     pps = block_tables.numel() // S_max
-    shape = _cabi.Shape(T, S_max, pps, P, page_size, Hq, Hkv, D, _DTYPE_CODE[queries.dtype])
+    shape = _cabi.Shape(T, S_max, pps, P, page_size, Hq, Hkv, D, _DTYPE_CODE[queries.dtype], _cabi.E4M3 if fp8 else 0)
     device = queries.device
     ws = cached_workspace(shape, device)
-    scale = float(softmax_scale) * (1.0 if k_scale is None else float(k_scale))
+    # the logits are (q / q_scale) . k * softmax_scale * k_scale * q_scale (:259-265): one factor for the kernel
+    scale = float(softmax_scale) * (1.0 if k_scale is None else float(k_scale)) * (1.0 if q_scale is None else float(q_scale))
     attrs = _cabi.Attrs(scale, 0.0 if logits_soft_cap is None else float(logits_soft_cap),
                         0 if sliding_window is None else int(sliding_window), 0, 0, 0, 0,
+                        0.0 if q_scale is None else float(q_scale),
                         0.0 if v_scale is None else float(v_scale))  # v_scale: in float32, before the output cast
     out = torch.empty_like(queries)
     with torch.cuda.device(device):

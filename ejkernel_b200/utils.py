@@ -126,12 +126,14 @@ def make_ragged_batch(
     logits_soft_cap: float | None = None,
     kv_head_slice: tuple[int, int] | None = None,
     page_order: str = "permuted",
+    kv_dtype=None,
 ) -> RaggedBatch:
     """Build one ragged batch.
 
     ``block_tables[s, :n_s]`` are consecutive slices of one global random permutation of
     the pool's pages (``page_order="permuted"``) or consecutive page ids (``"linear"``,
-    as in the reference's own test builders); unused table entries are 0.
+    as in the reference's own test builders); unused table entries are 0.  ``kv_dtype`` gives the pool another
+    dtype than the queries (``torch.float8_e4m3fn``: the same N(0,1) draws rounded to e4m3).
 
     ``kv_head_slice=(h0, h1)`` materialises only KV heads ``[h0, h1)`` (and the query heads
     of their groups) while drawing the same index arrays, which is how one rank of a
@@ -182,13 +184,13 @@ def make_ragged_batch(
     q = torch.randn((max(T_buf, 1), Hkv_loc * G, head_dim), generator=gen, device=device, dtype=torch.float32).to(dtype)
     q = q[:T_buf] if T_buf > 0 else q[:0]
     # Draw the pool page-block by page-block so the fp32 staging buffer stays small.
-    kv = torch.empty((num_pages, page_size, 2 * Hkv_loc, head_dim), device=device, dtype=dtype)
+    kv = torch.empty((num_pages, page_size, 2 * Hkv_loc, head_dim), device=device, dtype=kv_dtype or dtype)
     page_elems = page_size * 2 * Hkv_loc * head_dim
     step = max(1, (1 << 27) // page_elems)
     for p0 in range(0, num_pages, step):
         p1 = min(num_pages, p0 + step)
         blk = torch.randn((p1 - p0, page_size, 2 * Hkv_loc, head_dim), generator=gen, device=device, dtype=torch.float32)
-        kv[p0:p1] = blk.to(dtype)
+        kv[p0:p1] = blk.to(kv_dtype or dtype)
         del blk
 
     meta = dict(
@@ -281,6 +283,7 @@ def make_workload(
     kv_head_slice: tuple[int, int] | None = None,
     pad_query_rows: int = 0,
     seed: int | None = None,
+    kv_dtype=None,
 ) -> RaggedBatch:
     q, kv, shape, extra = workload_lengths(name, num_seqs=num_seqs, len_scale=len_scale, seed=seed)
     idx = WORKLOADS.index(name.lower()) + 1
@@ -292,6 +295,7 @@ def make_workload(
         seed=(1000 + idx) if seed is None else seed,
         kv_head_slice=kv_head_slice,
         pad_query_rows=pad_query_rows,
+        kv_dtype=kv_dtype,
         **shape,
         **extra,
     )
@@ -313,7 +317,12 @@ def to_v3_inputs(batch: RaggedBatch, fill: float = float("nan"), pad_fill: float
     """
     m = batch.meta
     page, Hkv, D = m["page_size"], m["num_kv_heads"], m["head_dim"]
-    pool = batch.kv_pages
+    pool_t = batch.kv_pages
+    # an 8-bit pool is handled as bytes (indexed assignment is not defined for float8); NaN of e4m3 is 0x7f
+    eight = pool_t.element_size() == 1
+    pool = pool_t.view(torch.uint8) if eight else pool_t
+    if eight:
+        fill, pad_fill = 0x7F, 0x44
     dev = pool.device
     T = batch.queries.shape[0]
     keys = torch.zeros((T, Hkv, D), dtype=pool.dtype, device=dev)
@@ -338,6 +347,8 @@ def to_v3_inputs(batch: RaggedBatch, fill: float = float("nan"), pad_fill: float
         padded[..., :D] = cache
         cache = padded
     cache5 = cache.view(pool.shape[0], page, 2 * Hkv // pack, pack, d_align)
+    if eight:
+        keys, values, cache5 = (t.view(pool_t.dtype) for t in (keys, values, cache5))
     S = len(m["q_lens"])
     distribution = torch.tensor([S, S, S], dtype=torch.int32, device=dev)
     return keys, values, cache5, batch.block_tables.reshape(-1).contiguous(), distribution

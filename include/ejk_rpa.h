@@ -45,6 +45,8 @@ extern "C" {
 /* dtype codes for queries / kv_pages / out */
 #define EJK_RPA_BF16 0
 #define EJK_RPA_F16 1
+/* dtype code of an 8-bit cache (ejk_rpa_shape.kv_dtype): float8 e4m3 ("e4m3fn": no infinities, maximum 448) */
+#define EJK_RPA_E4M3 2
 
 /* invalid-argument codes */
 #define EJK_RPA_E_NULL (-1)      /* a required pointer is null */
@@ -77,7 +79,12 @@ typedef struct ejk_rpa_shape {
   int32_t num_q_heads;
   int32_t num_kv_heads;  /* kv_pages.shape[2] / 2 */
   int32_t head_dim;      /* 64, 128 or 256 */
-  int32_t dtype;         /* EJK_RPA_BF16 | EJK_RPA_F16 */
+  int32_t dtype;         /* EJK_RPA_BF16 | EJK_RPA_F16: queries and out (and the cache, unless kv_dtype says otherwise) */
+  int32_t kv_dtype;      /* 0 = the cache has `dtype`; EJK_RPA_E4M3 = kv_pages / kv_cache hold e4m3 bytes (the fp8 KV cache of
+                            the v3 operator, ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:45-57,157-159,249-291).
+                            Needs head_dim 128 or 256, a page_size that is a power of two >= 8 and an even num_kv_heads
+                            (the reference packs four combined heads per 32-bit word); every sequence is then served by the
+                            split-KV kernel. */
 } ejk_rpa_shape;
 
 /* Scalar attributes of one call (the keyword arguments of the reference operator). */
@@ -93,6 +100,11 @@ typedef struct ejk_rpa_attrs {
                                      "min_chunk" for this call) */
   int32_t num_queries_per_block;  /* tile hint, 0 = auto: sequences with at least this many query tokens are served
                                      by 128-row tensor tiles (overrides option "prefill_rows" for this call) */
+  float q_scale;         /* 0 = none: the queries are divided by it, clipped to the finite range of the cache dtype and
+                            rounded to it as they are staged (_kernel.py:249-254); with an e4m3 cache Q.K^T then runs on
+                            e4m3 operands.  The caller folds q_scale (and k_scale) into softmax_scale, as the reference
+                            multiplies the logits back (:262-265).  Every sequence is then served by the split-KV kernel;
+                            needs a page_size the TMA gather supports (a power of two >= 8). */
   float out_scale;       /* 0 = none (1.0): factor applied to the normalised output in float32, before the cast to
                             the output dtype -- `v_scale` of the v3 operator
                             (ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:283-284) */

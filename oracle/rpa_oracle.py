@@ -46,7 +46,7 @@ DEFAULT_MASK_VALUE = -0.7 * float(np.finfo(np.dtype("float32")).max)
 def _np(x, dtype=None):
     if isinstance(x, torch.Tensor):
         x = x.detach().cpu()
-        if x.dtype in (torch.bfloat16, torch.float16):
+        if x.dtype in (torch.bfloat16, torch.float16, torch.float8_e4m3fn):
             x = x.float()
         x = x.numpy()
     x = np.asarray(x)
@@ -92,11 +92,19 @@ def dense_reference(
     softmax_aux=None,
     precision: str = "fp64",
     seq_subset=None,
-) -> np.ndarray:
+    p_dtype=None,
+    return_weight_bound: bool = False,
+):
     """Intended semantics; returns float64 ``[T, Hq, D]`` (rows past the last sequence are 0).
 
     ``precision="fp32"`` runs the two contractions in float32 (for the larger cases);
     the softmax statistics stay in float64 either way.
+
+    ``p_dtype`` (a torch dtype) rounds the NORMALISED probabilities to that dtype before ``P @ V``, as the v3
+    operator of the reference does with the dtype of the cache
+    (ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:281).  ``return_weight_bound=True`` also returns
+    ``P @ |V|`` of the unrounded probabilities: a rounding of the weights with relative error <= eps changes
+    an output element by at most eps times that.
     """
     ft = np.float64 if precision == "fp64" else np.float32
     q = _np(queries, ft)
@@ -114,6 +122,7 @@ def dense_reference(
     scale = D**-0.5 if softmax_scale is None else float(softmax_scale)
     sinks = _sinks_per_q_head(softmax_aux, Hq, Hkv)
     out = np.zeros((T, Hq, D), dtype=np.float64)
+    wbound = np.zeros((T, Hq, D), dtype=np.float64) if return_weight_bound else None
     seqs = range(S) if seq_subset is None else seq_subset
     for s in seqs:
         q0, q1 = int(cu[s]), int(cu[s + 1])
@@ -148,9 +157,14 @@ def dense_reference(
             if sinks is not None:
                 den = den + np.exp(sk[:, None, :] - m).sum(axis=-1, keepdims=True)
             den = np.maximum(den, 1e-30)
-            o = np.einsum("gqk,kd->qgd", (p / den).astype(ft), v, optimize=True)
+            pn = p / den
+            if return_weight_bound:
+                wbound[q0:q1, h * G : (h + 1) * G, :] = np.einsum("gqk,kd->qgd", pn.astype(ft), np.abs(v), optimize=True)
+            if p_dtype is not None:
+                pn = torch.from_numpy(pn).to(p_dtype).to(torch.float64).numpy()
+            o = np.einsum("gqk,kd->qgd", pn.astype(ft), v, optimize=True)
             out[q0:q1, h * G : (h + 1) * G, :] = o
-    return out
+    return (out, wbound) if return_weight_bound else out
 
 
 # ----------------------------------------------------------------------------------------
@@ -279,9 +293,12 @@ def v3_reference(
     softmax_scale: float = 1.0,
     sliding_window: int | None = None,
     logits_soft_cap: float | None = None,
+    q_scale: float | None = None,
     k_scale: float | None = None,
     v_scale: float | None = None,
     precision: str = "fp64",
+    round_p: bool = False,
+    return_weight_bound: bool = False,
 ):
     """The v3 operator (ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:143-318): scatter the
     new key/value rows into the paged cache, then attend against the updated cache.
@@ -292,18 +309,26 @@ def v3_reference(
     ``(out float64 [T,Hq,D], updated cache as a torch tensor of the cache dtype)``; attention is
     ``dense_reference`` on the updated cache with scale ``softmax_scale * k_scale`` and the output
     times ``v_scale`` (:262-263, :290-291).
+
+    Quantised path (:249-291; keys, values and cache may be ``torch.float8_e4m3fn``): with ``q_scale`` the
+    queries are divided by it in their own dtype, clipped to the finite range of the cache dtype and cast to it,
+    and the logits are multiplied by ``q_scale`` again; ``round_p=True`` casts the normalised probabilities to the
+    cache dtype before ``P @ V`` as the reference does (:281) -- with an e4m3 cache that flushes every
+    probability below 2^-10 to zero, so it is off by default and the tests use it on short contexts only.
     """
     cache = kv_cache.detach().cpu().clone()
     P, page, hx2p, pack, D = cache.shape
     C2 = hx2p * pack
-    flat = cache.view(P, page, C2, D)
+    # an 8-bit cache is written as bytes (indexed assignment is not defined for float8 tensors)
+    as_bytes = (lambda t: t.view(torch.uint8)) if cache.element_size() == 1 else (lambda t: t)
+    flat = as_bytes(cache).view(P, page, C2, D)
     ctx = _np(kv_lens, np.int64)
     S_max = ctx.shape[0]
     tab = _np(block_tables, np.int64).reshape(S_max, -1)
     cu = _np(query_start_loc, np.int64)
     S = int(_np(distribution).reshape(-1)[-1])
-    k = keys.detach().cpu()
-    v = values.detach().cpu()
+    k = as_bytes(keys.detach().cpu())
+    v = as_bytes(values.detach().cpu())
     Hkv = k.shape[1]
     fused = torch.stack([k, v], dim=2).reshape(k.shape[0], 2 * Hkv, k.shape[2])  # merge_kv
     for s in range(S):
@@ -314,12 +339,21 @@ def v3_reference(
             flat[int(tab[s, pos // page]), pos % page, : 2 * Hkv, : k.shape[2]] = fused[q0 + r]
             flat[int(tab[s, pos // page]), pos % page, : 2 * Hkv, k.shape[2] :] = 0  # merge_kv pads with zeros (:45-57)
     scale = float(softmax_scale) * (1.0 if k_scale is None else float(k_scale))
+    q_in = queries
+    if q_scale is not None:
+        qt = queries.detach().cpu()
+        lim = float(torch.finfo(cache.dtype).max)
+        q_in = (qt / float(q_scale)).clamp(-lim, lim).to(cache.dtype)  # :249-254 (the division rounds to q's dtype first)
+        scale *= float(q_scale)  # :264-265
     # the cache's last dim is align_to(D, 128); attention reads the first D lanes (:240-241)
-    out = dense_reference(queries, flat[..., : k.shape[2]], ctx, tab, cu, np.array([S]), softmax_scale=scale,
-                          sliding_window=sliding_window, logits_soft_cap=logits_soft_cap, precision=precision)
+    res = dense_reference(q_in, flat.view(cache.dtype)[..., : k.shape[2]], ctx, tab, cu, np.array([S]), softmax_scale=scale,
+                          sliding_window=sliding_window, logits_soft_cap=logits_soft_cap, precision=precision,
+                          p_dtype=cache.dtype if round_p else None, return_weight_bound=return_weight_bound)
+    out, wb = res if return_weight_bound else (res, None)
     if v_scale is not None:
         out = out * float(v_scale)
-    return out, cache
+        wb = None if wb is None else wb * float(v_scale)
+    return (out, cache, wb) if return_weight_bound else (out, cache)
 
 
 def page_attention_reference(query, key_cache, value_cache, context_lens, block_tables, *, attn_scale=None,

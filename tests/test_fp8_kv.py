@@ -1,0 +1,179 @@
+"""The float8 (e4m3) KV cache: ``ragged_page_attention`` on an e4m3 pool and ``ragged_page_attention_v3`` with an
+e4m3 cache, ``q_scale`` / ``k_scale`` / ``v_scale`` (ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:45-57,
+157-159,249-291).
+
+Tolerance.  Keys and values are e4m3 on both sides, so they add no error.  The kernel feeds the probabilities to the
+P.V tensor-core instruction as e4m3 (the reference casts them to the cache dtype as well, :281): each weight is off
+by at most half an e4m3 ulp, 2^-4 relative, so an output element is off by at most ``2^-4 * (P @ |V|)``.  The oracle
+returns that bound per element (``return_weight_bound``); on top of it the tests allow the bf16 rounding of the
+output (2^-8 relative) and 1e-3.  The reference rounds the NORMALISED probabilities, the kernel's online softmax the
+unnormalised ones, so the two roundings differ element by element; against the oracle with the reference's rounding
+(``round_p=True``) twice the bound holds, on contexts short enough that the normalised probabilities stay e4m3 normals."""
+
+import numpy as np
+import pytest
+import torch
+
+from ejkernel_b200.utils import make_ragged_batch, make_workload, to_v3_inputs
+from oracle.rpa_oracle import dense_reference, v3_reference
+
+FP8 = torch.float8_e4m3fn
+EPS = 2.0**-4
+
+
+def _cases():
+    mk = lambda ql, kl, **kw: make_ragged_batch(ql, kl, kv_dtype=FP8, **kw)
+    yield "decode", mk([1, 1, 1, 1], [300, 17, 64, 2500], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=71)
+    yield "mixed", mk([1, 40, 3, 130], [500, 40, 77, 900], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16,
+                      seed=72, sliding_window=256, logits_soft_cap=30.0)
+    yield "gqa16_wide_tiles", mk([1, 2, 1], [700, 130, 33], num_q_heads=32, num_kv_heads=2, head_dim=128, page_size=32, seed=73)
+    yield "d256", mk([2, 70, 1], [100, 300, 1000], num_q_heads=4, num_kv_heads=2, head_dim=256, page_size=32, seed=74)
+    yield "page8", mk([1, 9], [333, 100], num_q_heads=8, num_kv_heads=4, head_dim=128, page_size=8, seed=75)
+    yield "page128", mk([1, 5, 1], [1000, 129, 128], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=128, seed=76)
+    yield "f16_queries", mk([1, 7], [260, 64], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=77,
+                            dtype=torch.float16)
+    yield "empty_seq", mk([1, 0, 5], [50, 20, 5], num_q_heads=4, num_kv_heads=4, head_dim=128, page_size=8, max_num_seqs=5,
+                          pad_query_rows=3, seed=78)
+
+
+CASES = list(_cases())
+IDS = [n for n, _ in CASES]
+
+
+def _within(got, want, bound, rows, factor=1.0):
+    g = got[:rows].float().cpu().numpy().astype(np.float64)
+    err = np.abs(g - want[:rows])
+    lim = factor * EPS * 1.02 * bound[:rows] + 2.0**-8 * np.abs(want[:rows]) + 1e-3
+    assert np.isfinite(g).all()
+    assert (err <= lim).all(), (float((err / lim).max()), float(err.max()))
+    # the errors of the weights are not aligned: the typical element is far inside the bound
+    assert np.sqrt(np.mean(err**2)) <= 0.5 * EPS * np.sqrt(np.mean(bound[:rows] ** 2)) + 1e-3
+
+
+@pytest.mark.parametrize("name,b", CASES, ids=IDS)
+def test_oracle_v3_with_an_e4m3_cache(name, b):
+    keys, values, cache, tab, dist = to_v3_inputs(b)
+    assert cache.dtype == FP8 and cache.shape[3] == 4  # four combined heads per 32-bit word (:38-39)
+    out, new_cache, wb = v3_reference(b.queries, keys, values, cache, b.context_lens, tab, b.query_start_loc, dist,
+                                      softmax_scale=b.softmax_scale, sliding_window=b.sliding_window,
+                                      logits_soft_cap=b.logits_soft_cap, return_weight_bound=True)
+    assert torch.equal(new_cache.view(torch.uint8).reshape(b.kv_pages.shape), b.kv_pages.view(torch.uint8))
+    np.testing.assert_allclose(out, dense_reference(*b.args(), **b.kwargs()), atol=1e-12)
+    # the reference's own rounding of the normalised probabilities stays within the weight bound while they are normals
+    if max(b.meta["kv_lens"]) <= 64:
+        out_r, _ = v3_reference(b.queries, keys, values, cache, b.context_lens, tab, b.query_start_loc, dist,
+                                softmax_scale=b.softmax_scale, round_p=True)
+        assert (np.abs(out_r - out) <= EPS * 1.02 * wb + 1e-9).all()
+
+
+def test_oracle_q_scale_rounds_the_queries_to_the_cache_dtype():
+    b = CASES[0][1]
+    keys, values, cache, tab, dist = to_v3_inputs(b)
+    a, _ = v3_reference(b.queries, keys, values, cache, b.context_lens, tab, b.query_start_loc, dist, softmax_scale=0.1,
+                        q_scale=0.03, k_scale=1.5, v_scale=2.0)
+    q8 = (b.queries / 0.03).clamp(-448, 448).to(FP8).float()
+    want = 2.0 * dense_reference(q8, *b.args()[1:], softmax_scale=0.1 * 1.5 * 0.03)
+    np.testing.assert_allclose(a, want, atol=1e-12)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,b", CASES, ids=IDS)
+def test_cuda_operator_on_an_e4m3_pool(rpa_lib, name, b):
+    from tests.helpers import run_cuda, status_word
+
+    bc = b.to("cuda")
+    out = run_cuda(bc)
+    assert status_word(bc) == 0
+    want, wb = dense_reference(*b.args(), **b.kwargs(), return_weight_bound=True)
+    _within(out, want, wb, b.total_tokens)
+    assert torch.count_nonzero(out[b.total_tokens:]) == 0
+    assert torch.equal(out, run_cuda(bc)), "two runs agree bit for bit"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("q_scale", [None, 0.04])
+@pytest.mark.parametrize("name,b", CASES[:5], ids=IDS[:5])
+def test_cuda_v3_with_an_e4m3_cache(rpa_lib, name, b, q_scale):
+    import ejkernel_b200 as ej
+
+    bc = b.to("cuda")
+    keys, values, cache, tab, dist = to_v3_inputs(bc)
+    kw = dict(softmax_scale=b.softmax_scale, sliding_window=b.sliding_window, logits_soft_cap=b.logits_soft_cap,
+              q_scale=q_scale, k_scale=1.25, v_scale=0.5)
+    out, new_cache = ej.ragged_page_attention_v3(bc.queries, keys, values, cache, bc.context_lens, tab, bc.query_start_loc,
+                                                 dist, **kw)
+    torch.cuda.synchronize()
+    assert new_cache.data_ptr() == cache.data_ptr()
+    assert torch.equal(new_cache.view(torch.uint8).reshape(b.kv_pages.shape), bc.kv_pages.view(torch.uint8)), "page write"
+    ck, cv, cc, ctab, cdist = to_v3_inputs(b)
+    want, _, wb = v3_reference(b.queries, ck, cv, cc, b.context_lens, ctab, b.query_start_loc, cdist, **kw,
+                               return_weight_bound=True)
+    _within(out, want, wb, b.total_tokens)
+
+
+@pytest.mark.gpu
+def test_cuda_against_the_reference_rounding_on_short_contexts(rpa_lib):
+    import ejkernel_b200 as ej
+
+    b = make_ragged_batch([1, 20, 1, 64], [40, 20, 64, 64], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16,
+                          seed=79, kv_dtype=FP8)
+    bc = b.to("cuda")
+    keys, values, cache, tab, dist = to_v3_inputs(bc)
+    out, _ = ej.ragged_page_attention_v3(bc.queries, keys, values, cache, bc.context_lens, tab, bc.query_start_loc, dist,
+                                         softmax_scale=b.softmax_scale, q_scale=0.05)
+    torch.cuda.synchronize()
+    ck, cv, cc, ctab, cdist = to_v3_inputs(b)
+    want, _, wb = v3_reference(b.queries, ck, cv, cc, b.context_lens, ctab, b.query_start_loc, cdist,
+                               softmax_scale=b.softmax_scale, q_scale=0.05, round_p=True, return_weight_bound=True)
+    g = out.float().cpu().numpy().astype(np.float64)
+    assert (np.abs(g - want) <= 2 * EPS * 1.02 * wb + 2.0**-8 * np.abs(want) + 1e-3).all()
+
+
+@pytest.mark.gpu
+def test_e4m3_page_gather_is_bit_exact(rpa_lib):
+    """q = 0 makes every weight exp2(0 - m) with m = -4: exactly 16 in e4m3; V carries integers 0..15 that encode
+    (page, slot, head, lane).  The float32 mean of such integers over a power-of-two number of keys is exact, so any
+    wrong byte, page or slot shows up as an unequal bit pattern."""
+    from tests.helpers import run_cuda
+
+    b = make_ragged_batch([1, 1, 4], [256, 64, 128], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=80,
+                          kv_dtype=FP8)
+    P, page, C2, D = b.kv_pages.shape
+    code = (torch.arange(P)[:, None, None, None] * 7 + torch.arange(page)[None, :, None, None] * 3
+            + torch.arange(C2)[None, None, :, None] * 5 + torch.arange(D)[None, None, None, :]) % 16
+    b.kv_pages = code.float().to(FP8)
+    b.queries.zero_()
+    out = run_cuda(b.to("cuda")).float().cpu()
+    want = torch.from_numpy(dense_reference(*b.args(), **b.kwargs())).to(torch.bfloat16).float()
+    assert torch.equal(out[: b.total_tokens], want[: b.total_tokens])
+
+
+@pytest.mark.gpu
+def test_q_scale_with_a_16_bit_cache(rpa_lib):
+    import ejkernel_b200 as ej
+
+    b = make_ragged_batch([1, 40, 3], [500, 40, 77], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=81)
+    bc = b.to("cuda")
+    keys, values, cache, tab, dist = to_v3_inputs(bc)
+    kw = dict(softmax_scale=b.softmax_scale, q_scale=3.0, k_scale=0.5, v_scale=2.0)
+    out, _ = ej.ragged_page_attention_v3(bc.queries, keys, values, cache, bc.context_lens, tab, bc.query_start_loc, dist, **kw)
+    torch.cuda.synchronize()
+    ck, cv, cc, ctab, cdist = to_v3_inputs(b)
+    want, _ = v3_reference(b.queries, ck, cv, cc, b.context_lens, ctab, b.query_start_loc, cdist, **kw)
+    from tests.helpers import assert_parity
+    assert_parity(out, want, b.total_tokens, what="q_scale, bf16 cache")
+
+
+@pytest.mark.gpu
+def test_e4m3_decode_batch_at_benchmark_shape(rpa_lib):
+    """A slice of the Llama-3-8B-shaped decode batch on an e4m3 pool: sampled sequences against the oracle."""
+    from tests.helpers import run_cuda, status_word
+
+    b = make_workload("c2", num_seqs=48, device="cuda", kv_dtype=FP8)
+    out = run_cuda(b)
+    assert status_word(b) == 0
+    bc = b.to("cpu")
+    ids = [0, 7, 23, 47]
+    want, wb = dense_reference(*bc.args(), **bc.kwargs(), seq_subset=ids, return_weight_bound=True, precision="fp32")
+    rows = torch.tensor(ids)
+    _within(out[rows], want[ids], wb[ids], len(ids))
