@@ -210,8 +210,18 @@ def main():
         T = b.total_tokens
         b = b.to(a.device)
         b.queries = b.queries[:T].contiguous()
-        o16 = launch_default(mod, b, **tri_kw)  # the launcher's own output dtype (= queries.dtype)
-        o32 = launch_default(mod, b, out_dtype=torch.float32, **tri_kw)  # same kernel, unrounded store
+        try:
+            o16 = launch_default(mod, b, **tri_kw)  # the launcher's own output dtype (= queries.dtype)
+            o32 = launch_default(mod, b, out_dtype=torch.float32, **tri_kw)  # same kernel, unrounded store
+        except Exception as e:
+            if a.device != "cuda":
+                raise
+            # e.g. the soft-cap branch declares a constexpr inside the unrolled page loop (:162), which the compiler
+            # rejects from the second page on ("LOG2_CONST is already defined"); the interpreter does not mind
+            out[f"{name}.error"] = np.array(f"{type(e).__name__}: {e}"[-400:])
+            print(name, "did not compile:", out[f"{name}.error"], flush=True)
+            np.savez_compressed(dst, **out)
+            continue
         out[f"{name}.out"] = bits(o16)
         out[f"{name}.out_f32"] = o32.cpu().numpy()
         if qblock:

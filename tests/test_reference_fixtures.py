@@ -73,3 +73,36 @@ def test_cuda_operator_matches_the_reference_kernel(name):
     out = run_cuda(bc)
     assert status_word(bc) == 0
     assert_parity(out, ref32, rows=b.queries.shape[0], what=f"reference Triton fixture {name}")
+
+
+# ---- the same reference kernel COMPILED by Triton for a B200 (tl.dot of float32 operands runs as TF32) ----
+FIX_CUDA = np.load(Path(__file__).parent / "golden" / "rpa_reference_triton_cuda.npz")
+CASES_CUDA = sorted({k.split(".")[0] for k in FIX_CUDA.files if k.endswith(".out_f32")})
+
+
+def test_compiled_fixture_file():
+    assert "compiled for NVIDIA B200" in str(FIX_CUDA["how"]) and {"tpu_a", "fresh_prefill", "small_window"} <= set(CASES_CUDA)
+    # what did not compile says why: the q-block kernel, and the soft-cap branch of the default kernel
+    assert "qblock_error" in FIX_CUDA.files and "LOG2_CONST" in str(FIX_CUDA["small_softcap.error"])
+
+
+@pytest.mark.parametrize("name", CASES_CUDA)
+def test_dense_oracle_matches_the_compiled_reference_kernel(name):
+    b, _, interp32 = load_case(name)
+    ref32 = FIX_CUDA[f"{name}.out_f32"]
+    got = dense_reference(*b.args(), **b.kwargs())
+    # TF32 contractions: 10 mantissa bits on q, k, p and v
+    r = compare(ref32, got, atol=2e-3, rtol=2e-3)
+    assert r["finite"] and r["allclose"] and r["max_rel_rms"] < 1e-2, r
+    # and the interpreter's run of the same kernel on the same inputs agrees with the compiled one
+    assert compare(ref32, interp32, atol=2e-3, rtol=2e-3)["allclose"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", CASES_CUDA)
+def test_cuda_operator_matches_the_compiled_reference_kernel(name):
+    from tests.helpers import assert_parity, run_cuda
+
+    b, _, _ = load_case(name)
+    assert_parity(run_cuda(b.to("cuda")), FIX_CUDA[f"{name}.out_f32"], rows=b.queries.shape[0],
+                  what=f"reference Triton kernel compiled for B200, {name}")
