@@ -72,6 +72,9 @@ def parse_args():
     ap.add_argument("--waves", type=int, default=None)
     ap.add_argument("--path", type=int, default=None)
     ap.add_argument("--headline-only", action="store_true", help="skip per_workload / c5_strong / parity_sample")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="on ONE GPU, run the shard one rank of an N-way kv-head split would get (profiling aid)")
+    ap.add_argument("--fused-merge", type=int, default=None)
     return ap.parse_args()
 
 
@@ -413,6 +416,8 @@ def main():
         _cabi.set_option("waves", args.waves)
     if args.path is not None:
         _cabi.set_option("path", args.path)
+    if args.fused_merge is not None:
+        _cabi.set_option("fused_merge", args.fused_merge)
     hbm_peak, tensor_peak, peak_src = load_peaks()
 
     def head_slice_for(name):
@@ -420,6 +425,8 @@ def main():
         if Hkv % world:
             raise SystemExit(f"num_kv_heads={Hkv} cannot be split over {world} ranks")
         per = Hkv // world
+        if world == 1 and args.shard_of > 1:
+            return (0, Hkv // args.shard_of)
         return (rank * per, (rank + 1) * per) if world > 1 else None
 
     def barrier():

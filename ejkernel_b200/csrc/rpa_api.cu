@@ -94,9 +94,10 @@ WorkspaceLayout layout_for(const ejk_rpa_shape& s, int n_sm) {
   long long tgt = ((long long)ctas * g_opt.waves + s.num_kv_heads - 1) / s.num_kv_heads;
   if (tgt < 1) tgt = 1;
   L.target_units = (int)tgt;
-  L.max_units = (int)(tgt + max_tiles);
+  L.target_units_max = (int)(2 * tgt);  // what the planner switches to when every row tile gets many chunks
+  L.max_units = (int)(2 * tgt + max_tiles);
   L.max_merge = (int)max_tiles;
-  L.max_slots = (int)(tgt + max_tiles);
+  L.max_slots = (int)(2 * tgt + max_tiles);
   L.max_punits = (int)(rows / kPrefillRows + s.max_num_seqs);
   size_t off = 0;
   L.header_off = off;
@@ -277,6 +278,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.max_slots = L.max_slots;
   p.max_punits = L.max_punits;
   p.target_units = L.target_units;
+  p.target_units_max = L.target_units_max;
   // Per-call tile hints of the reference's RaggedPageAttentionConfig (configs.py:242-258) override
   // the process-wide options: num_kv_pages_per_block = smallest KV chunk a row tile is split into
   // (in pages; rounded up to whole 64-token stages), num_queries_per_block = query tokens from

@@ -50,24 +50,40 @@ __global__ void __launch_bounds__(kMergeWarps * 32) rpa_merge_kernel(const Param
 #pragma unroll
     for (int i = 0; i < VPL; ++i) acc[i] = 0.f;
     float l_tot = 0.f;
-    for (int c = 0; c < n; ++c) {
-      const size_t base = ((size_t)(mi.slot0 + c) * Hkv + h) * RT + r;
-      const float2 ml = p.part_ml[base];
-      const float f = fast_exp2(ml.x - mu);
-      l_tot += ml.y * f;
-      const float* po = p.part_o + base * D + lane * VPL;
-      if constexpr (VPL == 2) {
-        const float2 v = *reinterpret_cast<const float2*>(po);
-        acc[0] += v.x * f;
-        acc[1] += v.y * f;
-      } else {
+    // eight chunks' loads in flight at a time (each is an L2 round trip, and a row of a long context has
+    // dozens of chunks); the sums still run in chunk order
+    constexpr int kInFlight = 8;
+    for (int c0 = 0; c0 < n; c0 += kInFlight) {
+      float2 ml[kInFlight];
+      float vv[kInFlight][VPL];
 #pragma unroll
-        for (int i = 0; i < VPL; i += 4) {
-          const float4 v = *reinterpret_cast<const float4*>(po + i);
-          acc[i] += v.x * f;
-          acc[i + 1] += v.y * f;
-          acc[i + 2] += v.z * f;
-          acc[i + 3] += v.w * f;
+      for (int j = 0; j < kInFlight; ++j) {
+        const int c = min(c0 + j, n - 1);
+        const size_t base = ((size_t)(mi.slot0 + c) * Hkv + h) * RT + r;
+        ml[j] = p.part_ml[base];
+        const float* po = p.part_o + base * D + lane * VPL;
+        if constexpr (VPL == 2) {
+          const float2 v = *reinterpret_cast<const float2*>(po);
+          vv[j][0] = v.x;
+          vv[j][1] = v.y;
+        } else {
+#pragma unroll
+          for (int i = 0; i < VPL; i += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(po + i);
+            vv[j][i] = v.x;
+            vv[j][i + 1] = v.y;
+            vv[j][i + 2] = v.z;
+            vv[j][i + 3] = v.w;
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kInFlight; ++j) {
+        if (c0 + j < n) {
+          const float f = fast_exp2(ml[j].x - mu);
+          l_tot += ml[j].y * f;
+#pragma unroll
+          for (int i = 0; i < VPL; ++i) acc[i] += vv[j][i] * f;
         }
       }
     }

@@ -33,6 +33,7 @@ constexpr int kConsumerWarps = 4;
 constexpr int kThreadsTma = (kConsumerWarps + 1) * 32;
 constexpr int kRingTma = 8;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kMergeInFlight = 8;      // partials whose loads the last-arriver merge keeps in flight per row
 constexpr float kLazyRescale = 8.0f;  // rescale the accumulators only when the max grows by 2^8
 
 struct ItemDesc {
@@ -862,13 +863,13 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
 #pragma unroll
                 for (int i = 0; i < VPL; ++i) accm[i] = 0.f;
                 float l_tot = 0.f;
-                // four chunks' loads in flight at a time (each is an L2 round trip); the sums still run in
+                // kMergeInFlight chunks' loads in flight at a time (each is an L2 round trip); the sums still run in
                 // chunk order
-                for (int c0 = 0; c0 < u.n_chunks; c0 += 4) {
-                  float2 ml[4];
-                  float vv[4][VPL];
+                for (int c0 = 0; c0 < u.n_chunks; c0 += kMergeInFlight) {
+                  float2 ml[kMergeInFlight];
+                  float vv[kMergeInFlight][VPL];
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) {
+                  for (int j = 0; j < kMergeInFlight; ++j) {
                     const int c = min(c0 + j, u.n_chunks - 1);
                     const size_t base = ((size_t)(slot0 + c) * Hkv + h) * RT + r;
                     ml[j] = __ldcg(&p.part_ml[base]);
@@ -889,7 +890,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
                     }
                   }
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) {
+                  for (int j = 0; j < kMergeInFlight; ++j) {
                     if (c0 + j < u.n_chunks) {
                       const float f = fast_exp2(ml[j].x - mu);
                       l_tot += ml[j].y * f;

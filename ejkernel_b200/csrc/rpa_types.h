@@ -62,7 +62,7 @@ struct WorkspaceLayout {
   // then cut along KV at CTA-quota boundaries and their parts combined by the part that finishes last
   size_t pprefix_off, ptickets_off, ppart_ml_off, ppart_o_off, total_split;
   int32_t ppart_slots;
-  int32_t max_units, max_merge, max_slots, rows_per_tile, target_units, max_punits;
+  int32_t max_units, max_merge, max_slots, rows_per_tile, target_units, target_units_max, max_punits;
 };
 
 struct Params {
@@ -93,6 +93,7 @@ struct Params {
   int32_t T, S_max, pages_per_seq, num_pages, page_size, Hq, Hkv, G, D;
   int32_t rows_per_tile;
   int32_t max_units, max_merge, max_slots, target_units, min_chunk;
+  int32_t target_units_max;  // the planner may aim for this many items instead (see its pass 1); sizes the workspace
   int32_t max_punits;
   int32_t prefill_item_rows; // rows one prefill work item covers (128 per tile, 1 or 2 tiles per CTA)
   int32_t Dkv;               // elements between consecutive combined heads of kv_pages (head_dim, or the padded

@@ -6,10 +6,20 @@ kernel object (``get_impl`` / ``run`` / ``create_shard_map_wrapper`` / ``heurist
 keywords -- minus the reference's multi-backend selection: there is exactly one implementation, it
 is looked up in the registry under ``Platform.CUDA`` and nothing else is ever tried.  Asking for
 another platform raises.
+
+What the reference's ``Executor`` does around ``run`` (ejkernel/ops/execution/executor.py:209-406) is done by
+``_select_cfg`` and ``_stamped`` below: the configuration comes from the selection chain (explicit ``cfg``,
+overlay, memory cache, persistent cache, autotune on the first call of a signature, heuristic;
+``EJKERNEL_AUTOTUNE_POLICY=autotune|heuristics``), and with ``EJKERNEL_OPS_STAMP=hash|json`` the launch is wrapped in
+an NVTX range labelled ``ejkernel_ops#ragged_page_attention@v0:<call key>`` (the reference stamps the same label
+into the HLO, :131-207, :373-380).
 """
 
 from __future__ import annotations
 
+import contextlib
+import json
+import os
 from typing import Literal
 
 import torch
@@ -17,7 +27,9 @@ import torch
 from ...kernels._registry import Backend, Platform, kernel_registry
 from ...sharding import Mesh1D, PartitionSpec, all_gather_heads
 from .configs import RaggedPageAttentionConfig
-from .tuning import PersistentCache, call_key, cuda_event_timer, device_fingerprint, pick_best
+from .tuning import (AutotunePolicy, ConfigSelectorChain, PersistentCache, call_key, cuda_event_timer,
+                     device_fingerprint, pick_best)
+from . import tuning as _tuning
 
 Array = torch.Tensor
 OP_ID = "ragged_page_attention"
@@ -41,9 +53,13 @@ class RaggedPageAttention:
     op_id = OP_ID
     version = OP_VERSION
 
-    def __init__(self, cache: PersistentCache | None = None):
-        # tuned configurations, looked up when a call gives no ``cfg``; None = always the heuristic
+    def __init__(self, cache: PersistentCache | None = None, policy: AutotunePolicy | None = None, on_event=None):
+        # ``cache``: tuned configurations kept across runs (None = memory only); ``policy``: what a call whose
+        # signature is in no cache does -- measure the candidates once (the reference's default) or take the heuristic
         self.cache = cache
+        self.selector = ConfigSelectorChain(policy=policy or AutotunePolicy.from_env(), persistent=cache, on_event=on_event)
+        self._fast: dict[tuple, RaggedPageAttentionConfig] = {}  # static call signature -> chosen cfg, no hashing
+        self._fingerprints: dict[int | None, str] = {}
 
     @property
     def op_id_v(self) -> str:
@@ -101,7 +117,7 @@ class RaggedPageAttention:
                                     softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap,
                                     sliding_window=sliding_window, softmax_aux=softmax_aux, cfg=cfg)
 
-        best, _ = pick_best(cands, run_with, timer)
+        best, _ = pick_best(cands, run_with, timer, margin=0.02)
         if self.cache is not None:
             self.cache.put(device_fingerprint(queries.device), self.op_id_v,
                            call_key(queries, kv_pages, block_tables, sliding_window=sliding_window,
@@ -110,6 +126,34 @@ class RaggedPageAttention:
 
     candidate_cfgs_gpu = candidate_cfgs
     candidate_cfgs_shard_map_gpu = candidate_cfgs
+
+    def select_cfg(self, queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, *, cfg=None,
+                   softmax_scale=None, logits_soft_cap=None, sliding_window=None, softmax_aux=None):
+        """The configuration for this call, in the order of the reference's ``ConfigSelectorChain.choose``
+        (ejkernel/ops/config/selection.py:384-566).  Returns ``(cfg, call_key or None)``.  Calls whose static
+        signature (shapes, dtypes, window, cap, sinks shape, device) was resolved before take a dictionary look-up."""
+        fast = (queries.device.index, tuple(queries.shape), queries.dtype, tuple(kv_pages.shape), kv_pages.dtype,
+                tuple(block_tables.shape), sliding_window, logits_soft_cap,
+                None if softmax_aux is None else tuple(softmax_aux.shape))
+        if cfg is None and not _tuning._overlays:
+            hit = self._fast.get(fast)
+            if hit is not None:
+                return hit, None
+        dev = self._fingerprints.get(queries.device.index)
+        if dev is None:
+            dev = self._fingerprints[queries.device.index] = device_fingerprint(queries.device)
+        key = call_key(queries, kv_pages, block_tables, sliding_window=sliding_window, logits_soft_cap=logits_soft_cap,
+                       softmax_aux=softmax_aux)
+        # measuring needs a device it can synchronise: not while the stream is being captured into a graph
+        can_measure = queries.is_cuda and not torch.cuda.is_current_stream_capturing()
+        chosen = self.selector.choose(
+            dev, self.op_id_v, key, override=cfg, may_autotune=can_measure, heuristic=self.heuristic_cfg,
+            autotune=lambda: self.autotune(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs,
+                                           softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap,
+                                           sliding_window=sliding_window, softmax_aux=softmax_aux))
+        if cfg is None and not _tuning._overlays and self.selector.cache.get(dev, self.op_id_v, key) is chosen:
+            self._fast[fast] = chosen
+        return chosen, key
 
     def run(
         self,
@@ -263,17 +307,57 @@ def ragged_page_attention(
     ``softmax_aux`` sinks.  With ``mesh``, ``in_specs`` and ``out_specs`` all given the call runs in
     shard-map mode on this process's local shards (see ``create_shard_map_wrapper``).
     """
-    cfg = cfg or _kernel.lookup_cfg(queries, kv_pages, block_tables, sliding_window=sliding_window,
-                                    logits_soft_cap=logits_soft_cap, softmax_aux=softmax_aux)
+    cfg, key = _kernel.select_cfg(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, cfg=cfg,
+                                  softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap,
+                                  sliding_window=sliding_window, softmax_aux=softmax_aux)
     common = dict(
         softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap, compute_dtype=compute_dtype,
         optimized=optimized, sliding_window=sliding_window, softmax_aux=softmax_aux, mask_value=mask_value,
         vmem_limit_bytes=vmem_limit_bytes, platform=platform, cfg=cfg,
     )
-    if mesh is not None and in_specs is not None and out_specs is not None:
-        fn, call_args = _kernel.create_shard_map_wrapper(
-            queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs,
-            mesh=mesh, in_specs=in_specs, out_specs=out_specs, **common,
-        )
-        return fn(*call_args)
-    return _kernel.run(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, **common)
+    with _stamped(queries, kv_pages, block_tables, key, cfg, sliding_window, logits_soft_cap, softmax_aux):
+        if mesh is not None and in_specs is not None and out_specs is not None:
+            fn, call_args = _kernel.create_shard_map_wrapper(
+                queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs,
+                mesh=mesh, in_specs=in_specs, out_specs=out_specs, **common,
+            )
+            return fn(*call_args)
+        return _kernel.run(queries, kv_pages, context_lens, block_tables, query_start_loc, num_seqs, **common)
+
+
+_STAMP_MODE = os.environ.get("EJKERNEL_OPS_STAMP", "none").lower()
+_STAMP_PREFIX = os.environ.get("EJKERNEL_OPS_PREFIX", "ejkernel_ops")
+
+
+def stamp_label(queries, kv_pages, block_tables, key, cfg, sliding_window=None, logits_soft_cap=None, softmax_aux=None,
+                mode: str = "hash") -> str:
+    """``<prefix>#ragged_page_attention@v0:<call key>`` (mode "hash"), or the prefix followed by a JSON description of
+    the call (mode "json") -- the labels of the reference's ``Executor._stamp_hash`` / ``_stamp_json``
+    (ejkernel/ops/execution/executor.py:131-184)."""
+    if mode == "json":
+        payload = json.dumps(dict(
+            op_id=_kernel.op_id_v, queries=[list(queries.shape), str(queries.dtype)],
+            kv_pages=[list(kv_pages.shape), str(kv_pages.dtype)], block_tables=list(block_tables.shape),
+            sliding_window=sliding_window, logits_soft_cap=logits_soft_cap,
+            cfg=dict(num_kv_pages_per_block=cfg.num_kv_pages_per_block, num_queries_per_block=cfg.num_queries_per_block),
+        ), sort_keys=True)
+        return f"{_STAMP_PREFIX}:{payload}"
+    if key is None:
+        key = call_key(queries, kv_pages, block_tables, sliding_window=sliding_window, logits_soft_cap=logits_soft_cap,
+                       softmax_aux=softmax_aux)
+    return f"{_STAMP_PREFIX}#{_kernel.op_id_v}:{key}"
+
+
+@contextlib.contextmanager
+def _stamped(queries, kv_pages, block_tables, key, cfg, sliding_window, logits_soft_cap, softmax_aux):
+    """NVTX range around the launch when ``EJKERNEL_OPS_STAMP`` is ``hash`` or ``json`` (read at import); nothing,
+    and no cost, otherwise."""
+    if _STAMP_MODE not in ("hash", "json") or not queries.is_cuda:
+        yield
+        return
+    torch.cuda.nvtx.range_push(stamp_label(queries, kv_pages, block_tables, key, cfg, sliding_window, logits_soft_cap,
+                                           softmax_aux, mode=_STAMP_MODE))
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()

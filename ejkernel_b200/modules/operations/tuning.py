@@ -3,9 +3,11 @@
 
 Mirrors the part of the reference's ops layer that EasyDeL-style callers rely on -- the
 ``PersistentCache`` of ejkernel/ops/config/persistent.py:58-200 with its ``device|op@v|call_key``
-keys (:114-125) and atomic file replacement (:190-200), and the measure-candidates-keep-the-best
-step of ``Tuner`` (ejkernel/ops/config/selection.py:226-245) -- without the seven-tier selector
-chain around it: there is one implementation here and two knobs.
+keys (:114-125) and atomic file replacement (:190-200), the measure-candidates-keep-the-best
+step of ``Tuner`` (ejkernel/ops/config/selection.py:226-245), and the selection order of
+``ConfigSelectorChain.choose`` (:384-566): explicit override, overlay, in-memory cache, persistent
+cache, autotune on the first call of a signature, heuristic.  There is one implementation here and two
+knobs, so the chain selects a configuration, never a backend.
 
 What is tuned: ``RaggedPageAttentionConfig.num_kv_pages_per_block`` (smallest KV chunk a row tile is
 split into, in pages) and ``num_queries_per_block`` (query tokens from which on a sequence is served
@@ -19,8 +21,9 @@ import json
 import os
 import pathlib
 import tempfile
+import contextlib
 from collections.abc import Callable, Sequence
-from dataclasses import asdict, is_dataclass
+from dataclasses import asdict, dataclass, is_dataclass
 from typing import Any
 
 import torch
@@ -116,9 +119,10 @@ def cuda_event_timer(fn: Callable[[], Any], warmup: int = 3, iters: int = 10) ->
 
 
 def pick_best(candidates: Sequence[Any], run_with: Callable[[Any], Callable[[], Any]],
-              timer: Callable[[Callable[[], Any]], float] = cuda_event_timer) -> tuple[Any, list[float]]:
+              timer: Callable[[Callable[[], Any]], float] = cuda_event_timer, margin: float = 0.0) -> tuple[Any, list[float]]:
     """Time ``run_with(cfg)`` for every candidate; the first of the fastest wins.  A candidate that
-    raises is skipped (its time is ``inf``)."""
+    raises is skipped (its time is ``inf``).  With ``margin`` > 0 the first candidate (the heuristic) is kept
+    unless another one is faster by more than that fraction: timing noise must not replace the default."""
     times: list[float] = []
     for cfg in candidates:
         try:
@@ -127,4 +131,131 @@ def pick_best(candidates: Sequence[Any], run_with: Callable[[Any], Callable[[], 
             times.append(float("inf"))
     if not times or min(times) == float("inf"):
         raise RuntimeError("no candidate configuration could be run")
-    return candidates[times.index(min(times))], times
+    best = times.index(min(times))
+    if margin > 0.0 and times[0] != float("inf") and times[best] >= times[0] * (1.0 - margin):
+        best = 0
+    return candidates[best], times
+
+
+# ----------------------------------------------------------------------------------------------------------
+# Selection chain (reference: ejkernel/ops/config/selection.py:82-578, cache.py:44-175)
+# ----------------------------------------------------------------------------------------------------------
+class ConfigCache:
+    """In-memory ``(device, op@v, call_key) -> cfg`` (reference: ejkernel/ops/config/cache.py:44-110)."""
+
+    def __init__(self):
+        self._data: dict[tuple[str, str, str], Any] = {}
+
+    def get(self, device: str, op_id: str, call_key: str):
+        return self._data.get((device, op_id, call_key))
+
+    def put(self, device: str, op_id: str, call_key: str, cfg) -> None:
+        self._data[(device, op_id, call_key)] = cfg
+
+    def clear(self) -> None:
+        self._data.clear()
+
+    def __len__(self) -> int:
+        return len(self._data)
+
+
+_overlays: list[dict[tuple[str, str, str], Any]] = []
+
+
+@contextlib.contextmanager
+def overlay_cache(mapping: dict[tuple[str, str, str], Any]):
+    """Temporary ``(device, op@v, call_key) -> cfg`` overrides that win over both caches while the context is
+    active; nested overlays are searched innermost first (reference: cache.py:113-175)."""
+    _overlays.append(dict(mapping))
+    try:
+        yield
+    finally:
+        _overlays.pop()
+
+
+@dataclass
+class AutotunePolicy:
+    """What a cache miss may do (reference: selection.py:82-110)."""
+
+    allow_autotune: bool = True
+    allow_heuristics: bool = True
+    cache_miss_fallback: str = "autotune"  # "autotune" | "heuristics"
+
+    @staticmethod
+    def from_env(default: str = "autotune") -> "AutotunePolicy":
+        """``EJKERNEL_AUTOTUNE_POLICY=autotune|heuristics``, the reference's switch
+        (ejkernel/modules/operations/ragged_page_attention.py:531)."""
+        mode = os.environ.get("EJKERNEL_AUTOTUNE_POLICY", default).lower()
+        if mode not in ("autotune", "heuristics"):
+            raise ValueError(f"EJKERNEL_AUTOTUNE_POLICY={mode!r}: expected 'autotune' or 'heuristics'")
+        return AutotunePolicy(allow_autotune=mode == "autotune", cache_miss_fallback=mode)
+
+
+class ConfigSelectorChain:
+    """override -> overlay -> memory cache -> persistent cache -> autotune -> heuristic, with the reference's
+    events (``override``, ``overlay_hit``, ``cache_hit``, ``autotune_start``, ``autotune_finish``, ``heuristics``,
+    ``error``) reported to ``on_event`` (selection.py:384-578)."""
+
+    def __init__(self, cache: ConfigCache | None = None, policy: AutotunePolicy | None = None,
+                 persistent: PersistentCache | None = None, on_event: Callable[..., None] | None = None,
+                 persist_autotune: bool = True, forbid_reautotune: bool = True):
+        self.cache = cache if cache is not None else ConfigCache()
+        self.policy = policy if policy is not None else AutotunePolicy()
+        self.persistent = persistent
+        self.on_event = on_event
+        self.persist_autotune = persist_autotune
+        self.forbid_reautotune = forbid_reautotune
+        self._autotuned_keys: set[tuple[str, str, str]] = set()
+
+    def _emit(self, event: str, **data) -> None:
+        if self.on_event:
+            self.on_event(event, **data)
+
+    def choose(self, device: str, op_id: str, call_key: str, *, override=None,
+               autotune: Callable[[], Any] | None = None, heuristic: Callable[[], Any] | None = None,
+               may_autotune: bool = True):
+        """``autotune()`` measures the candidates and returns the best; ``heuristic()`` returns the default.
+        ``may_autotune=False`` (the stream is being captured into a graph, say) skips the measuring tier for this
+        call without remembering the heuristic, so that a later call can still tune."""
+        key = (device, op_id, call_key)
+        if override is not None:
+            self._emit("override", device=device, op_id=op_id, call_key=call_key, cfg=override)
+            self.cache.put(*key, override)
+            if self.persistent is not None:
+                self.persistent.put(*key, override)
+            return override
+        for ov in reversed(_overlays):
+            if (cfg := ov.get(key)) is not None:
+                self._emit("overlay_hit", device=device, op_id=op_id, call_key=call_key, cfg=cfg)
+                return cfg
+        if (cfg := self.cache.get(*key)) is not None:
+            self._emit("cache_hit", level="memory", device=device, op_id=op_id, call_key=call_key, cfg=cfg)
+            return cfg
+        if self.persistent is not None and (cfg := self.persistent.get(*key)) is not None:
+            self._emit("cache_hit", level="persistent", device=device, op_id=op_id, call_key=call_key, cfg=cfg)
+            self.cache.put(*key, cfg)
+            return cfg
+        if self.policy.cache_miss_fallback == "autotune" and self.policy.allow_autotune and autotune is not None:
+            if not may_autotune:
+                if heuristic is None:
+                    raise RuntimeError("autotune is not possible here and there is no heuristic")
+                return heuristic()
+            if self.forbid_reautotune and key in self._autotuned_keys:
+                raise RuntimeError(f"Re-autotune requested for {key}")
+            self._emit("autotune_start", device=device, op_id=op_id, call_key=call_key)
+            best = autotune()
+            self._autotuned_keys.add(key)
+            self.cache.put(*key, best)
+            if self.persistent is not None and self.persist_autotune:
+                self.persistent.put(*key, best)
+            self._emit("autotune_finish", device=device, op_id=op_id, call_key=call_key, cfg=best)
+            return best
+        if self.policy.allow_heuristics and heuristic is not None:
+            cfg = heuristic()
+            self._emit("heuristics", device=device, op_id=op_id, call_key=call_key, cfg=cfg)
+            self.cache.put(*key, cfg)
+            if self.persistent is not None and self.persist_autotune:
+                self.persistent.put(*key, cfg)
+            return cfg
+        self._emit("error", device=device, op_id=op_id, call_key=call_key, reason="no_config")
+        raise RuntimeError("No config found: override/overlay/cache/persistent/autotune/heuristics all unavailable.")

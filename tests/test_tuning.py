@@ -95,3 +95,85 @@ def test_autotune_persists_and_the_operator_picks_it_up(tmp_path, monkeypatch):
     explicit = RaggedPageAttentionConfig(num_kv_pages_per_block=2, platform="cuda", backend="gpu")
     rpa_module.ragged_page_attention(q, kv, lens, tab, qsl, n, cfg=explicit)
     assert seen[-1] == explicit
+
+
+def test_selection_chain_order_and_events(tmp_path):
+    """override > overlay > memory cache > persistent cache > autotune > heuristic, as in the reference's
+    ConfigSelectorChain.choose (ejkernel/ops/config/selection.py:384-566), with its events."""
+    from ejkernel_b200.modules.operations.tuning import AutotunePolicy, ConfigSelectorChain, overlay_cache
+
+    events = []
+    pers = PersistentCache("op", str(tmp_path / "p.json"))
+    chain = ConfigSelectorChain(persistent=pers, on_event=lambda ev, **d: events.append((ev, d.get("level"))))
+    key = ("dev", "op@v0", "k1")
+    tuned = {"n": 0}
+
+    def autotune():
+        tuned["n"] += 1
+        return "tuned"
+
+    assert chain.choose(*key, autotune=autotune, heuristic=lambda: "heur") == "tuned"  # nothing cached: measure once
+    assert chain.choose(*key, autotune=autotune, heuristic=lambda: "heur") == "tuned" and tuned["n"] == 1  # memory tier
+    assert pers.get(*key) == "tuned"  # and persisted
+    with overlay_cache({key: "overlaid"}):
+        assert chain.choose(*key, autotune=autotune, heuristic=lambda: "heur") == "overlaid"
+        assert chain.choose(*key, override="explicit") == "explicit"  # an explicit cfg beats the overlay ...
+    assert chain.choose(*key, autotune=autotune) == "explicit"  # ... and is remembered, as in the reference
+    fresh = ConfigSelectorChain(persistent=PersistentCache("op", str(tmp_path / "p.json")),
+                                on_event=lambda ev, **d: events.append((ev, d.get("level"))))
+    assert fresh.choose(*key, autotune=autotune) == "explicit" and tuned["n"] == 1  # persistent tier of a new process
+    assert [e for e, _ in events] == ["autotune_start", "autotune_finish", "cache_hit", "overlay_hit", "override", "cache_hit",
+                                      "cache_hit"]
+    assert events[2][1] == "memory" and events[-1][1] == "persistent"
+    # policy "heuristics": no measuring; a call that may not measure right now takes the heuristic without caching it
+    h = ConfigSelectorChain(policy=AutotunePolicy(allow_autotune=False, cache_miss_fallback="heuristics"))
+    assert h.choose("d", "o", "k", autotune=autotune, heuristic=lambda: "heur") == "heur" and tuned["n"] == 1
+    a = ConfigSelectorChain()
+    assert a.choose("d", "o", "k", autotune=autotune, heuristic=lambda: "heur", may_autotune=False) == "heur"
+    assert a.choose("d", "o", "k", autotune=autotune, heuristic=lambda: "heur") == "tuned" and tuned["n"] == 2
+    with pytest.raises(RuntimeError):
+        ConfigSelectorChain(policy=AutotunePolicy(allow_autotune=False, allow_heuristics=False,
+                                                  cache_miss_fallback="heuristics")).choose("d", "o", "k")
+
+
+def test_policy_from_env_and_stamp_label(monkeypatch):
+    from ejkernel_b200.modules.operations.tuning import AutotunePolicy
+
+    monkeypatch.setenv("EJKERNEL_AUTOTUNE_POLICY", "heuristics")
+    p = AutotunePolicy.from_env()
+    assert not p.allow_autotune and p.cache_miss_fallback == "heuristics"
+    monkeypatch.setenv("EJKERNEL_AUTOTUNE_POLICY", "nonsense")
+    with pytest.raises(ValueError):
+        AutotunePolicy.from_env()
+    monkeypatch.delenv("EJKERNEL_AUTOTUNE_POLICY")
+    assert AutotunePolicy.from_env().cache_miss_fallback == "autotune"  # the reference's default
+    q, kv, lens, tab, qsl, n = _operands()
+    label = rpa_module.stamp_label(q, kv, tab, None, RaggedPageAttention().heuristic_cfg())
+    assert label == f"ejkernel_ops#ragged_page_attention@v0:{call_key(q, kv, tab)}"
+    js = rpa_module.stamp_label(q, kv, tab, None, RaggedPageAttention().heuristic_cfg(), mode="json")
+    assert js.startswith("ejkernel_ops:{") and json.loads(js.split(":", 1)[1])["op_id"] == "ragged_page_attention@v0"
+
+
+def test_operator_resolves_a_signature_once(monkeypatch):
+    """The first call of a static signature walks the chain (here: a fake measurement), later calls take the
+    dictionary look-up; a pick that does not beat the heuristic by 2 % keeps the heuristic."""
+    q, kv, lens, tab, qsl, n = _operands()
+    kern = RaggedPageAttention()
+    monkeypatch.setattr(RaggedPageAttention, "run", lambda self, *a, cfg, **kw: cfg)
+    calls = {"n": 0}
+
+    def fake_autotune(*a, **kw):
+        calls["n"] += 1
+        return RaggedPageAttentionConfig(num_kv_pages_per_block=2, platform="cuda", backend="gpu")
+
+    monkeypatch.setattr(kern, "autotune", fake_autotune)
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
+    monkeypatch.setattr(rpa_module, "device_fingerprint", lambda d=None: "cuda|fake|sm100|148")
+    c1, k1 = kern.select_cfg(q, kv, lens, tab, qsl, n)
+    c2, k2 = kern.select_cfg(q, kv, lens, tab, qsl, n)
+    assert c1.num_kv_pages_per_block == 2 and c2 is c1 and calls["n"] == 1 and k1 is not None and k2 is None
+    monkeypatch.undo()
+    slow = {"heur": 1.0, "other": 0.99}
+    best, _ = pick_best(["heur", "other"], lambda c: (lambda: c), timer=lambda fn: slow[fn()], margin=0.02)
+    assert best == "heur"

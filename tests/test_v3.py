@@ -101,7 +101,7 @@ def test_cuda_v3_scales_and_full_size_decode(rpa_lib):
 
     b = make_workload("c2", num_seqs=64, device="cuda")
     keys, values, cache, tab_flat, dist = to_v3_inputs(b)
-    ref = ej.ragged_page_attention(*b.args(), softmax_scale=b.softmax_scale)
+    ref = ej.ragged_page_attention(*b.args(), softmax_scale=b.softmax_scale, cfg=ej.RaggedPageAttention().heuristic_cfg())
     out, new_cache = ej.ragged_page_attention_v3(b.queries, keys, values, cache, b.context_lens, tab_flat,
                                                  b.query_start_loc, dist, softmax_scale=b.softmax_scale / 4.0,
                                                  k_scale=4.0, v_scale=2.0)
