@@ -4,13 +4,17 @@ Nothing in the product path may import this module: it is the checker used by ``
 by ``__graft_entry__.smoke()`` and by the ``cpu_baseline`` / ``--impl reference`` legs of
 ``bench.py``.
 
-PARITY UNPINNED.  The reference is pure JAX; JAX/jaxlib are not installed where this was
-written and cannot be installed (no network), so the reference itself could not be run to
-produce outputs, and its repository holds no golden vectors or known-answer files for this
-operator (the only numeric comparisons, test/kernels/_pallas/tpu/test_ragged_page_attention.py:465-554,
-are TPU-gated XLA-vs-Pallas checks with freshly drawn inputs).  What pins this file instead:
-the two restatements below follow two *independent* reference sources and must agree with
-each other (tests/test_oracle.py), and a set of analytically known answers (uniform
+PINNED to outputs of the reference's own kernel.  The reference's XLA implementation needs JAX, which is not
+installed where this was written and cannot be installed (no network), and its repository holds no golden
+vectors or known-answer files for this operator (the only numeric comparisons,
+test/kernels/_pallas/tpu/test_ragged_page_attention.py:465-554, are TPU-gated XLA-vs-Pallas checks with freshly
+drawn inputs).  Its Triton implementation of the same operator, ``_ragged_paged_attn_fwd``
+(ejkernel/kernels/_triton/ragged_page_attention/_triton_impl_fwd.py:27-208), is a plain ``@triton.jit`` function:
+tests/golden/make_reference_fixtures.py runs it from the reference checkout (Triton's interpreter on the CPU, and
+compiled for a B200) and tests/test_reference_fixtures.py holds ``dense_reference`` and ``blocked_as_written``
+against those outputs.  Not covered by that kernel, hence not pinned: attention sinks, and XLA's accumulation
+order inside bf16 contractions.  Further anchors: the two restatements below follow two *independent* reference
+sources and must agree with each other (tests/test_oracle.py), and a set of analytically known answers (uniform
 softmax over encoded values, single visible key, planted keys).
 
 Two modes:
