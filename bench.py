@@ -75,6 +75,7 @@ def parse_args():
     ap.add_argument("--shard-of", type=int, default=1,
                     help="on ONE GPU, run the shard one rank of an N-way kv-head split would get (profiling aid)")
     ap.add_argument("--fused-merge", type=int, default=None)
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "e4m3"], help="dtype of the KV pool of the headline batch")
     return ap.parse_args()
 
 
@@ -250,7 +251,8 @@ def make_config(args, world: int) -> dict:
     pool = int(shape.get("num_pages") or -(-pages * 11 // 10)) * shape["page_size"] * 2 * shape["num_kv_heads"] * shape["head_dim"] * 2
     pool_rank = pool // world
     return {
-        "workload": f"{args.workload}: {total} seqs" + (f" x len_scale {args.len_scale}" if args.len_scale != 1.0 else ""),
+        "workload": f"{args.workload}: {total} seqs" + (f" x len_scale {args.len_scale}" if args.len_scale != 1.0 else "")
+                    + (" on a float8 e4m3 KV pool" if getattr(args, "kv_dtype", "bf16") == "e4m3" else ""),
         "partition": (f"kv-head sharded over {world} GPU(s), {'weak: the N=1 lengths repeated N times' if weak else 'strong'}"
                       if world > 1 else "single GPU"),
         "l2": (f"KV pool {pool_rank / 2**30:.1f} GiB per GPU, far larger than the 126 MB L2: no flush needed"
@@ -522,7 +524,7 @@ def main():
 
     # ---------------- headline: resident inputs, device timed ----------------
     batch = build(args.workload, dev, head_slice_for(args.workload), num_seqs=n_seqs, len_scale=args.len_scale,
-                  tile=world if weak else 1)
+                  tile=world if weak else 1, kv_dtype=torch.float8_e4m3fn if args.kv_dtype == "e4m3" else None)
     T = batch.total_tokens
     kv_bytes_rank = algorithmic_kv_bytes(batch)
     with ClockSampler(local_rank) as clk:
@@ -596,7 +598,8 @@ def main():
 
     # ---------------- the other workloads (outside the headline's timed region) ----------------
     per_workload, c5_strong = None, None
-    default_run = args.workload == "c2" and args.num_seqs is None and args.len_scale == 1.0 and not args.strong
+    default_run = (args.workload == "c2" and args.num_seqs is None and args.len_scale == 1.0 and not args.strong
+                   and args.kv_dtype == "bf16" and args.shard_of == 1)
     if default_run and not args.headline_only:
         k_steps = max(5, min(args.steps, 30))
         # "c2_e4m3_kv": the headline batch on a float8 (e4m3) pool -- half the KV bytes per token
