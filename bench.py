@@ -75,6 +75,7 @@ def parse_args():
     ap.add_argument("--shard-of", type=int, default=1,
                     help="on ONE GPU, run the shard one rank of an N-way kv-head split would get (profiling aid)")
     ap.add_argument("--fused-merge", type=int, default=None)
+    ap.add_argument("--prefill-share", type=int, default=None, help="library option prefill_share (percent, 0 = off)")
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "e4m3"], help="dtype of the KV pool of the headline batch")
     return ap.parse_args()
 
@@ -420,6 +421,8 @@ def main():
         _cabi.set_option("path", args.path)
     if args.fused_merge is not None:
         _cabi.set_option("fused_merge", args.fused_merge)
+    if args.prefill_share is not None:
+        _cabi.set_option("prefill_share", args.prefill_share)
     hbm_peak, tensor_peak, peak_src = load_peaks()
 
     def head_slice_for(name):

@@ -173,8 +173,21 @@ def check(code: int, what: str = "ejk_rpa") -> None:
         raise RpaLibraryError(f"{what} failed with code {code}: {error_string(code)}")
 
 
+_option_mirror: dict[str, int] = {}  # values set or read through this module (options are process-wide and host-side)
+
+
 def set_option(name: str, value: int) -> None:
     check(load().ejk_rpa_set_option(name.encode(), int(value)), f"set_option({name})")
+    _option_mirror[name] = int(value)
+
+
+def get_option_cached(name: str) -> int:
+    """``get_option`` without the library call once the value is known; valid as long as options are only changed
+    through ``set_option`` of this module."""
+    v = _option_mirror.get(name)
+    if v is None:
+        v = _option_mirror[name] = get_option(name)
+    return v
 
 
 def get_option(name: str) -> int:

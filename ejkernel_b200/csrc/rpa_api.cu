@@ -26,6 +26,7 @@ struct Options {
   // 256 x 8 tokens at kv 128..8192 1.45 -> 1.18 ms, 256 x 12 tokens 2.16 -> 1.22 ms; at 17-31 rows it
   // depends on the lengths (faster at kv <= 1024, 7 % slower on long ragged contexts).
   int prefill_rows = 32;
+  int prefill_share = 120;  // see Params::prefill_share; 0 = the tile kernel always uses every SM
 };
 Options g_opt;
 thread_local int t_last_launches = 0;
@@ -257,7 +258,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
     p.ptickets = reinterpret_cast<int32_t*>(ws + L.ptickets_off);
     p.ppart_ml = reinterpret_cast<float2*>(ws + L.ppart_ml_off);
     p.ppart_o = reinterpret_cast<float*>(ws + L.ppart_o_off);
-    p.prefill_split = 1;
+    p.prefill_split = g_opt.prefill_split;
   }
   p.part_o = reinterpret_cast<float*>(ws + L.part_o_off);
   p.part_ml = reinterpret_cast<float2*>(ws + L.part_ml_off);
@@ -330,6 +331,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
                            (long long)s.total_tokens * p.G >= prefill_rows &&
                            s.total_tokens > s.max_num_seqs;  // more query rows than sequences: some are multi-token
   p.prefill_min_rows = use_prefill ? prefill_rows : 0;
+  p.prefill_share = g_opt.prefill_share;
   // The last-arriver merge inside the split-KV kernel saves a launch, but the chunk that arrives last
   // combines its tile alone: with many chunks per tile (few query rows, long contexts) the separate
   // merge kernel, which spreads the rows over the whole GPU, is faster.  Decided from static shapes:
@@ -496,7 +498,8 @@ int ejk_rpa_set_option(const char* name, int value) {
   } else if (!std::strcmp(name, "overlap")) {
     g_opt.overlap = value ? 1 : 0;
   } else if (!std::strcmp(name, "prefill_split")) {
-    g_opt.prefill_split = value ? 1 : 0;
+    if (value < 0 || value > 2) return EJK_RPA_E_ARG;
+    g_opt.prefill_split = value;
   } else if (!std::strcmp(name, "sort_items")) {
     g_opt.sort_items = value ? 1 : 0;
   } else if (!std::strcmp(name, "test_withhold")) {
@@ -511,6 +514,9 @@ int ejk_rpa_set_option(const char* name, int value) {
   } else if (!std::strcmp(name, "prefill_rows")) {
     if (value < 0) return EJK_RPA_E_ARG;
     g_opt.prefill_rows = value;
+  } else if (!std::strcmp(name, "prefill_share")) {
+    if (value < 0 || value > 1000) return EJK_RPA_E_ARG;
+    g_opt.prefill_share = value;
   } else {
     return EJK_RPA_E_ARG;
   }
@@ -530,6 +536,7 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "fused_merge")) *value = g_opt.fused_merge;
   else if (!std::strcmp(name, "wait_ms")) *value = g_opt.wait_ms;
   else if (!std::strcmp(name, "prefill_rows")) *value = g_opt.prefill_rows;
+  else if (!std::strcmp(name, "prefill_share")) *value = g_opt.prefill_share;
   else return EJK_RPA_E_ARG;
   return 0;
 }

@@ -443,8 +443,9 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
   // KV split of prefill items: exclusive prefix of their stage counts in queue order (the tile kernel
   // cuts the concatenated stage sequence of all (item, kv head) pairs into equal CTA quotas), and the
   // arrival counters of the parts
+  // (the stage total alone is also what the tile kernel's SM-sharing rule reads, whether or not items are split)
   int prefill_stages = 0;
-  if (p.prefill_split) {
+  if (p.prefill_min_rows > 0) {
     const int n_items = base[3] <= p.max_punits ? base[3] : 0;
     __syncthreads();  // the items scattered above by other threads
     int running = 0;
@@ -457,14 +458,16 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
       }
       int excl[kCnt], total[kCnt];
       block_scan(v, excl, total, s_warp);
-      if (i < n_items) p.pprefix[i] = running + excl[0];
+      if (p.prefill_split && i < n_items) p.pprefix[i] = running + excl[0];
       running += total[0];
     }
-    if (tid == 0) p.pprefix[n_items] = running;
     prefill_stages = running;
-    const int nt = p.prefill_item_rows / kPrefillRows;
-    const int n_pt = n_items * p.Hkv * nt * 4;
-    for (int i = tid; i < n_pt; i += kPlanThreads) p.ptickets[i] = 0;
+    if (p.prefill_split) {
+      if (tid == 0) p.pprefix[n_items] = running;
+      const int nt = p.prefill_item_rows / kPrefillRows;
+      const int n_pt = n_items * p.Hkv * nt * 4;
+      for (int i = tid; i < n_pt; i += kPlanThreads) p.ptickets[i] = 0;
+    }
   }
   if (tid == 0) {
     const bool over = base[0] > p.max_units || base[1] > p.max_merge || base[2] > p.max_slots || base[3] > p.max_punits;

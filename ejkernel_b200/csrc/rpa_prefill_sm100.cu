@@ -181,7 +181,30 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
   // plan is complete.
   if (p.pdl & 1) pdl_wait();
   pdl_trigger();
-  const int n_work = p.header[kHdrNumPrefill] * Hkv;
+  // Mixed batch: this kernel is compute-bound and the split-KV kernel that follows in the stream is bandwidth-bound, and
+  // the two only overlap on SMs this kernel has left (a CTA of each does not fit one SM together).  With all SMs this
+  // kernel finishes long before the decode rows' KV has streamed; so it keeps only as many CTAs as make it end about
+  // when the split-KV kernel does, and the others exit at once and hand their SMs over: the tensor pipes of some SMs
+  // and the memory system then work side by side for the whole call (64 decode sequences + four 512-token chunks:
+  // 0.466 -> 0.416 ms; with 0.8 of the estimated CTAs the tile kernel becomes the long pole, 0.465; with 1.3, 0.420).
+  // Estimated from the plan: T_p = stages * kStageUs / CTAs against T_d = decode bytes / kDecodeBpUs.
+  int n_cta = (int)gridDim.x;
+  if ((p.pdl & 1) && p.prefill_share > 0 && D <= 128) {
+    const float stages = (float)p.header[kHdrPrefillStages] * (float)Hkv;           // (item, head) stages of 64 tokens
+    const float dec_bytes = (float)p.header[kHdrTotalKeys] * (float)Hkv * (float)(2 * D * sizeof(T));
+    // one stage of two 128-row tiles: 2460 cycles measured on evenly divisible work at head_dim 128, 0.93 of that at 64
+    constexpr float kStageUs = D == 64 ? 1.15f : 1.25f;
+    constexpr float kDecodeBpUs = 6.6e6f;  // bytes per microsecond the split-KV kernel streams
+    const float t_p = stages * kStageUs / (float)gridDim.x, t_d = dec_bytes / kDecodeBpUs;
+    if (t_d > t_p && t_p > 0.f) {
+      int n = (int)ceilf((float)gridDim.x * (t_p / t_d) * (float)p.prefill_share * 0.01f);
+      const int floor_n = (int)gridDim.x / 8;
+      n = n < floor_n ? floor_n : n;
+      n_cta = n < (int)gridDim.x ? n : (int)gridDim.x;
+    }
+  }
+  const bool idle_cta = (int)blockIdx.x >= n_cta;
+  const int n_work = idle_cta ? 0 : p.header[kHdrNumPrefill] * Hkv;
 
   if (warp == 0) {
     // =============================== TMA producer ===============================
@@ -199,13 +222,13 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     // quota of at least 8 stages, e.g. 160
     // equal items on 148 CTAs (0.289 -> 0.203 ms), not 128 or 256 of them, nor short items.
     const int n_items = p.header[kHdrNumPrefill];
-    const long long W = (long long)p.header[kHdrPrefillStages] * Hkv;
+    const long long W = idle_cta ? 0 : (long long)p.header[kHdrPrefillStages] * Hkv;
     constexpr int kMinQuota = 8;  // a part shorter than this is all overhead
     bool split = p.prefill_split && W > 0 && W < (1ll << 30);
-    long long quota_ll = (W + gridDim.x - 1) / gridDim.x;
+    long long quota_ll = (W + n_cta - 1) / n_cta;
     if (quota_ll < kMinQuota) quota_ll = kMinQuota;
-    if (split) {
-      const long long U = (long long)n_items * Hkv, Cn = gridDim.x;
+    if (split && p.prefill_split < 2) {  // 2 = always split (measurement aid)
+      const long long U = (long long)n_items * Hkv, Cn = n_cta;
       const long long rounds = (U + Cn - 1) / Cn;
       split = rounds * W * 20 >= 23 * U * (quota_ll + 16);  // rounds * W / U >= 1.15 * (quota + 16)
     }
@@ -223,7 +246,7 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
       it = lo;
     }
     int wid = 0;
-    if (!split) {
+    if (!split && !idle_cta) {  // a CTA that has handed its SM over must not draw from the queue
       if (lane == 0) wid = atomicAdd(&p.header[kHdrPrefillQueue], 1);
       wid = __shfl_sync(0xffffffffu, wid, 0);
     }

@@ -104,6 +104,7 @@ struct Params {
                              // (EJK_RPA_ST_TIMEOUT); 0 in production
   int32_t pdl;               // bit 0: the prefill kernel, bit 1: the split-KV kernel must pdl_wait() before reading the plan
   int32_t prefill_min_rows;  // sequences with q_len*G >= this go to the prefill-tile kernel; 0 = never
+  int32_t prefill_share;     // percent: in a mixed batch the tile kernel keeps this share of the CTAs its estimate asks for (0 = all CTAs always)
   int32_t window;      // <= 0: none
   int32_t num_sinks, sink_rows;
   int32_t kv8;         // 1: the cache holds e4m3 bytes (queries / out keep their 16-bit dtype)

@@ -63,11 +63,22 @@ class RpaWorkspace:
         assert self.buffer.data_ptr() % 256 == 0
 
 
+_need_cache: dict[tuple, int] = {}
+
+
 def workspace_bytes(shape: _cabi.Shape, device: torch.device) -> int:
-    with torch.cuda.device(device):
-        nbytes = int(_cabi.load().ejk_rpa_workspace_bytes(ctypes.byref(shape)))
-    if nbytes == 0:
-        raise ValueError("ejk_rpa_workspace_bytes rejected the shape")
+    """``ejk_rpa_workspace_bytes`` for this static shape on this device; remembered per (device, shape, option
+    "waves"), so that the call path of a serving loop does not cross into the library for it every step."""
+    key = (device.index, _cabi.get_option_cached("waves"), *[getattr(shape, f) for f, _ in shape._fields_])
+    nbytes = _need_cache.get(key)
+    if nbytes is None:
+        with torch.cuda.device(device):
+            nbytes = int(_cabi.load().ejk_rpa_workspace_bytes(ctypes.byref(shape)))
+        if nbytes == 0:
+            raise ValueError("ejk_rpa_workspace_bytes rejected the shape")
+        if len(_need_cache) > 4096:
+            _need_cache.clear()
+        _need_cache[key] = nbytes
     return nbytes
 
 

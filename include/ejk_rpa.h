@@ -214,9 +214,14 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *   "path"       0 = auto, 1 = force the cp.async gather, 2 = force the TMA gather
  *   "prefill_rows" sequences with at least this many (query token, head-in-group) rows per kv head are
  *                served by 128-row tcgen05 tiles instead of 8-row split-KV tiles (default 32; 0 = never)
+ *   "prefill_share" percent (default 120; 0 = off): in a batch that mixes multi-token sequences with decode rows the
+ *                tensor-tile kernel keeps only as many CTAs as make it finish about when the bandwidth-bound split-KV
+ *                kernel does (estimated on the device from the plan, times this percentage) and leaves the other SMs to
+ *                that kernel from the start
  *   "prefill_split" 1 (default) = when the workspace has the size ejk_rpa_workspace_bytes reports, prefill items are
  *                cut along KV at per-CTA quota boundaries and their parts combined by the last one to finish;
- *                0 = whole items from a longest-first queue (also what a smaller workspace gets)
+ *                0 = whole items from a longest-first queue (also what a smaller workspace gets);
+ *                2 = cut at every quota boundary, whatever the rule says (a measurement aid)
  *   "sort_items" 1 (default) = the planner queues split-KV work items longest first, 0 = in sequence order
  *   "overlap"    1 (default) = the kernels of one call are launched as programmatic dependents: each starts under
  *                the tail of the one before and waits on the device for what it needs; 0 = plain stream order

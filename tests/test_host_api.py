@@ -104,7 +104,7 @@ def test_library_exports_every_declared_symbol(rpa_lib):
     _cabi.set_option("waves", 5)
     assert _cabi.get_option("waves") == 5
     _cabi.set_option("waves", old)
-    for name in ("waves", "min_chunk", "path", "prefill_rows", "prefill_split", "sort_items", "overlap", "fused_merge", "wait_ms", "profile"):
+    for name in ("waves", "min_chunk", "path", "prefill_rows", "prefill_share", "prefill_split", "sort_items", "overlap", "fused_merge", "wait_ms", "profile"):
         assert isinstance(_cabi.get_option(name), int), name  # every option the header documents is readable
     with pytest.raises(_cabi.RpaLibraryError):
         _cabi.set_option("no_such_option", 1)

@@ -730,3 +730,29 @@ def test_rows_past_the_last_sequence_are_zero_filled_by_the_launch(rpa_lib):
     ragged_page_attention_into(out, ws, *b.args(), softmax_scale=b.softmax_scale)
     torch.cuda.synchronize()
     assert torch.count_nonzero(out) == 0
+
+
+def test_tile_kernel_hands_sms_to_the_split_kv_kernel_in_mixed_batches(rpa_lib):
+    """In a mixed batch the tensor-tile kernel keeps only as many CTAs as its estimate of the two kernels' times
+    asks for (option ``prefill_share``, a percentage on that estimate) and the rest exit at once; whatever the
+    share -- none, far too few CTAs, the default, far too many -- every item is still served exactly once."""
+    from ejkernel_b200 import _cabi
+    b = make_workload("c3", num_seqs=20, len_scale=0.25)  # 16 decode sequences + 4 prefill chunks
+    want = oracle(b)
+    bc = b.to("cuda")
+    old = _cabi.get_option("prefill_share"), _cabi.get_option("prefill_split")
+    try:
+        for split in (1, 0):
+            _cabi.set_option("prefill_split", split)
+            outs = []
+            for share in (0, 10, 120, 1000):
+                _cabi.set_option("prefill_share", share)
+                out = run_cuda(bc)
+                assert status_word(bc) == 0
+                assert_parity(out, want, b.total_tokens, what=f"prefill_share {share}, split {split}")
+                outs.append(out)
+            if split == 0:  # whole items: which CTA serves an item does not change its arithmetic
+                assert all(torch.equal(o, outs[0]) for o in outs)
+    finally:
+        _cabi.set_option("prefill_share", old[0])
+        _cabi.set_option("prefill_split", old[1])
