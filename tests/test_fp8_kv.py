@@ -177,3 +177,48 @@ def test_e4m3_decode_batch_at_benchmark_shape(rpa_lib):
     want, wb = dense_reference(*bc.args(), **bc.kwargs(), seq_subset=ids, return_weight_bound=True, precision="fp32")
     rows = torch.tensor(ids)
     _within(out[rows], want[ids], wb[ids], len(ids))
+
+
+@pytest.mark.gpu
+def test_e4m3_pool_with_attention_sinks_and_refusals(rpa_lib):
+    """Sinks enter the denominator in the shared epilogues, whatever the cache dtype; shapes the e4m3 kernels do not
+    serve are refused by the host layer with a clear error (and by the C ABI with a negative code), never served wrongly."""
+    import ctypes
+
+    from ejkernel_b200 import _cabi
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import ragged_page_attention
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import RpaWorkspace, _shape_of
+    from tests.helpers import run_cuda, status_word
+
+    b = make_ragged_batch([1, 6, 1], [400, 90, 33], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=82,
+                          kv_dtype=FP8)
+    b.softmax_aux = torch.tensor([[0.5, -1.0], [2.0, 0.0]])
+    bc = b.to("cuda")
+    out = run_cuda(bc)
+    assert status_word(bc) == 0
+    want, wb = dense_reference(*b.args(), **b.kwargs(), return_weight_bound=True)
+    _within(out, want, wb, b.total_tokens)
+
+    bad = make_ragged_batch([1], [40], num_q_heads=4, num_kv_heads=2, head_dim=64, page_size=16, seed=1, kv_dtype=FP8).to("cuda")
+    with pytest.raises(NotImplementedError):
+        ragged_page_attention(*bad.args(), softmax_scale=0.1)  # head_dim 64
+    odd = make_ragged_batch([1], [40], num_q_heads=4, num_kv_heads=2, head_dim=128, page_size=24, seed=1, kv_dtype=FP8).to("cuda")
+    with pytest.raises(NotImplementedError):
+        ragged_page_attention(*odd.args(), softmax_scale=0.1)  # page size not a power of two
+    # the same through the raw C ABI: negative codes, nothing launched
+    shape = _shape_of(bc.queries, bc.kv_pages, bc.block_tables)
+    ws = RpaWorkspace(shape, bc.queries.device)
+    o = torch.full_like(bc.queries, 7.0)
+    attrs = _cabi.Attrs(0.1, 0.0, 0, 0, 0, 0, 0)
+    args = lambda sh: (bc.queries.data_ptr(), bc.kv_pages.data_ptr(), bc.context_lens.data_ptr(), bc.block_tables.data_ptr(),
+                       bc.query_start_loc.data_ptr(), bc.num_seqs.data_ptr(), None, o.data_ptr(), ws.buffer.data_ptr(),
+                       ws.nbytes, ws.status.data_ptr(), ctypes.byref(sh), ctypes.byref(attrs),
+                       torch.cuda.current_stream().cuda_stream)
+    for field, value, code in (("head_dim", 64, -3), ("page_size", 24, -2), ("num_kv_heads", 1, -2), ("kv_dtype", 7, -4)):
+        sh = _cabi.Shape(*[getattr(shape, f) for f, _ in shape._fields_])
+        setattr(sh, field, value)
+        if field == "num_kv_heads":
+            sh.num_q_heads = 4
+        assert rpa_lib.ejk_rpa_launch(*args(sh)) == code, field
+    torch.cuda.synchronize()
+    assert bool((o == 7.0).all())

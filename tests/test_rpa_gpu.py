@@ -756,3 +756,24 @@ def test_tile_kernel_hands_sms_to_the_split_kv_kernel_in_mixed_batches(rpa_lib):
     finally:
         _cabi.set_option("prefill_share", old[0])
         _cabi.set_option("prefill_split", old[1])
+
+
+def test_opt_in_status_check_raises_when_outputs_are_invalid(rpa_lib, monkeypatch):
+    """``EJKERNEL_B200_CHECK_STATUS=1`` makes the operator read its status word after every call and raise when it says
+    the outputs are invalid.  A wait is made to run out with the test hook (nothing faults or hangs); the call after it,
+    with the hook off, is clean again."""
+    from ejkernel_b200 import _cabi
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import ragged_page_attention
+    b = make_ragged_batch([1, 1, 2], [700, 64, 1500], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=97).to("cuda")
+    monkeypatch.setenv("EJKERNEL_B200_CHECK_STATUS", "1")
+    old = _cabi.get_option("wait_ms")
+    try:
+        _cabi.set_option("wait_ms", 50)
+        _cabi.set_option("test_withhold", 1)
+        with pytest.raises(_cabi.RpaLibraryError, match="wait inside a kernel ran out"):
+            ragged_page_attention(*b.args(), softmax_scale=b.softmax_scale)
+    finally:
+        _cabi.set_option("test_withhold", 0)
+        _cabi.set_option("wait_ms", old)
+    out = ragged_page_attention(*b.args(), softmax_scale=b.softmax_scale)  # raises nothing
+    assert_parity(out, oracle(b), b.total_tokens, what="after a timed-out call")
