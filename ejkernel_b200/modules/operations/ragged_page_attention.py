@@ -117,7 +117,11 @@ class RaggedPageAttention:
                                     softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap,
                                     sliding_window=sliding_window, softmax_aux=softmax_aux, cfg=cfg)
 
-        best, _ = pick_best(cands, run_with, timer, margin=0.02)
+        best, times = pick_best(cands, run_with, timer, margin=0.02)
+        if os.environ.get("EJKERNEL_LOG_AUTOTUNE", "0") == "1":  # the reference's switch (ejkernel/ops/config/selection.py:328,338)
+            for c, t in zip(cands, times):
+                print(f"[ejkernel_b200 autotune] {self.op_id_v} num_kv_pages_per_block={c.num_kv_pages_per_block} "
+                      f"num_queries_per_block={c.num_queries_per_block}: {t:.4f} ms" + ("  <- chosen" if c is best else ""))
         if self.cache is not None:
             self.cache.put(device_fingerprint(queries.device), self.op_id_v,
                            call_key(queries, kv_pages, block_tables, sliding_window=sliding_window,
