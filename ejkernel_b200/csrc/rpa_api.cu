@@ -78,7 +78,7 @@ int check_shape(const ejk_rpa_shape* s) {
   if (s->kv_dtype != 0 && s->kv_dtype != EJK_RPA_E4M3) return EJK_RPA_E_DTYPE;
   if (s->kv_dtype == EJK_RPA_E4M3) {
     if (s->head_dim != 128 && s->head_dim != 256) return EJK_RPA_E_HEAD_DIM;
-    if (s->page_size < 8 || (s->page_size & (s->page_size - 1)) != 0 || (s->num_kv_heads & 1)) return EJK_RPA_E_SHAPE;
+    if (s->page_size < 8 || s->page_size % 8 != 0 || (s->num_kv_heads & 1)) return EJK_RPA_E_SHAPE;
   }
   return 0;
 }
@@ -170,7 +170,7 @@ size_t ejk_rpa_workspace_bytes(const ejk_rpa_shape* shape) {
   // launch with only L.total bytes still works, without that split
   const bool multi = shape->total_tokens > shape->max_num_seqs;
   const int ps = shape->page_size;
-  return (multi && ps >= 8 && (ps & (ps - 1)) == 0) ? L.total_split : L.total;
+  return (multi && ps >= 8 && ps % 8 == 0) ? L.total_split : L.total;
 }
 
 // Shared body of the launch entry points.  `value_cache` != null selects the split cache layout
@@ -315,7 +315,11 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
     p.page_shift = sh;
   }
 
-  p.tma_block_tokens = s.page_size < kTileTokens ? s.page_size : kTileTokens;
+  // tokens per TMA box: the largest power of two that divides the page size, at most one 64-token stage -- a box
+  // never straddles a page, and boxes are whole 8-token swizzle atoms (page sizes that are no multiple of 8 take
+  // the cp.async gather).  16 -> 16, 128 -> 64, 24 -> 8, 48 -> 16.
+  p.tma_block_tokens = 1;
+  while (p.tma_block_tokens < kTileTokens && s.page_size % (p.tma_block_tokens * 2) == 0) p.tma_block_tokens *= 2;
   p.tma_block_shift = 0;
   while ((1 << p.tma_block_shift) < p.tma_block_tokens) ++p.tma_block_shift;
   p.wait_timeout_ms = g_opt.wait_ms;

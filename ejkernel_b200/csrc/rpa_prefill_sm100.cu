@@ -977,7 +977,7 @@ int prefill_rows_per_item(int head_dim) { return head_dim <= 128 ? 2 * kPrefillR
 
 bool prefill_path_supported(const Params& p) {
   const int ps = p.page_size;
-  if (ps < 8 || (ps & (ps - 1)) != 0) return false;
+  if (ps < 8 || ps % 8 != 0) return false;  // one TMA box per 8-token group: a group must not straddle a page
   return encode_fn_p() != nullptr;
 }
 

@@ -1008,7 +1008,7 @@ cudaError_t dispatch(const Params& p, const CUtensorMap& map, const CUtensorMap&
 
 bool tma_path_supported(const Params& p) {
   const int ps = p.page_size;
-  if (ps < 8 || (ps & (ps - 1)) != 0) return false;  // boxes must be whole 1024-byte swizzle atoms
+  if (ps < 8 || ps % 8 != 0) return false;  // boxes are whole 8-token (1024-byte) swizzle atoms inside one page
   return encode_fn() != nullptr;
 }
 

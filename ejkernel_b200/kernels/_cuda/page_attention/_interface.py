@@ -13,7 +13,7 @@ it).  ``max_context_len``, ``num_splits``, ``mask_value``, ``pages_per_compute_b
 split of long contexts is chosen on the device.
 
 It runs the same split-KV kernels as ``ragged_page_attention`` through a tensor map over the split
-layout (``ejk_page_attention_launch``); a ``block_size`` that is not a power of two >= 8 goes through
+layout (``ejk_page_attention_launch``); a ``block_size`` that is not a multiple of 8 goes through
 the cp.async gather instead (slower).  A sequence
 with ``context_len == 0`` yields zeros (the reference's softmax over all-masked scores would average
 stale blocks).  There is no CPU fallback.

@@ -82,7 +82,7 @@ typedef struct ejk_rpa_shape {
   int32_t dtype;         /* EJK_RPA_BF16 | EJK_RPA_F16: queries and out (and the cache, unless kv_dtype says otherwise) */
   int32_t kv_dtype;      /* 0 = the cache has `dtype`; EJK_RPA_E4M3 = kv_pages / kv_cache hold e4m3 bytes (the fp8 KV cache of
                             the v3 operator, ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:45-57,157-159,249-291).
-                            Needs head_dim 128 or 256, a page_size that is a power of two >= 8 and an even num_kv_heads
+                            Needs head_dim 128 or 256, a page_size that is a multiple of 8 and an even num_kv_heads
                             (the reference packs four combined heads per 32-bit word); every sequence is then served by the
                             split-KV kernel. */
 } ejk_rpa_shape;
@@ -104,7 +104,7 @@ typedef struct ejk_rpa_attrs {
                             rounded to it as they are staged (_kernel.py:249-254); with an e4m3 cache Q.K^T then runs on
                             e4m3 operands.  The caller folds q_scale (and k_scale) into softmax_scale, as the reference
                             multiplies the logits back (:262-265).  Every sequence is then served by the split-KV kernel;
-                            needs a page_size the TMA gather supports (a power of two >= 8). */
+                            needs a page_size the TMA gather supports (a multiple of 8). */
   float out_scale;       /* 0 = none (1.0): factor applied to the normalised output in float32, before the cast to
                             the output dtype -- `v_scale` of the v3 operator
                             (ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:283-284) */
@@ -169,7 +169,7 @@ EJK_RPA_API int ejk_rpa_v3_launch(const void* queries, const void* keys, const v
  * Triton split-KV + reduce version ejkernel/kernels/_triton/page_attention/_interface.py:88-369).  Same
  * kernels as ejk_rpa_launch with a different tensor map: every sequence has one query row that sees all
  * keys below its context length.  `shape`: total_tokens = max_num_seqs = num_seqs, pages_per_seq =
- * max_blocks, num_pages = num_blocks, page_size = block_size (a power of two >= 8 for the TMA gather; any other size takes the cp.async gather).
+ * max_blocks, num_pages = num_blocks, page_size = block_size (a multiple of 8 for the TMA gather; any other size takes the cp.async gather).
  * `attrs`: softmax_scale = attn_scale, logits_soft_cap = attn_logits_soft_cap (0 = none); the rest 0. */
 EJK_RPA_API int ejk_page_attention_launch(const void* query, const void* key_cache, const void* value_cache,
                                           const int32_t* context_lens, const int32_t* block_tables, void* out,

@@ -29,6 +29,7 @@ def _cases():
     yield "gqa16_wide_tiles", mk([1, 2, 1], [700, 130, 33], num_q_heads=32, num_kv_heads=2, head_dim=128, page_size=32, seed=73)
     yield "d256", mk([2, 70, 1], [100, 300, 1000], num_q_heads=4, num_kv_heads=2, head_dim=256, page_size=32, seed=74)
     yield "page8", mk([1, 9], [333, 100], num_q_heads=8, num_kv_heads=4, head_dim=128, page_size=8, seed=75)
+    yield "page24", mk([1, 30, 1], [500, 130, 24], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=24, seed=83)
     yield "page128", mk([1, 5, 1], [1000, 129, 128], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=128, seed=76)
     yield "f16_queries", mk([1, 7], [260, 64], num_q_heads=8, num_kv_heads=2, head_dim=128, page_size=16, seed=77,
                             dtype=torch.float16)
@@ -202,9 +203,9 @@ def test_e4m3_pool_with_attention_sinks_and_refusals(rpa_lib):
     bad = make_ragged_batch([1], [40], num_q_heads=4, num_kv_heads=2, head_dim=64, page_size=16, seed=1, kv_dtype=FP8).to("cuda")
     with pytest.raises(NotImplementedError):
         ragged_page_attention(*bad.args(), softmax_scale=0.1)  # head_dim 64
-    odd = make_ragged_batch([1], [40], num_q_heads=4, num_kv_heads=2, head_dim=128, page_size=24, seed=1, kv_dtype=FP8).to("cuda")
+    odd = make_ragged_batch([1], [40], num_q_heads=4, num_kv_heads=2, head_dim=128, page_size=12, seed=1, kv_dtype=FP8).to("cuda")
     with pytest.raises(NotImplementedError):
-        ragged_page_attention(*odd.args(), softmax_scale=0.1)  # page size not a power of two
+        ragged_page_attention(*odd.args(), softmax_scale=0.1)  # page size not a multiple of 8
     # the same through the raw C ABI: negative codes, nothing launched
     shape = _shape_of(bc.queries, bc.kv_pages, bc.block_tables)
     ws = RpaWorkspace(shape, bc.queries.device)
@@ -214,7 +215,7 @@ def test_e4m3_pool_with_attention_sinks_and_refusals(rpa_lib):
                        bc.query_start_loc.data_ptr(), bc.num_seqs.data_ptr(), None, o.data_ptr(), ws.buffer.data_ptr(),
                        ws.nbytes, ws.status.data_ptr(), ctypes.byref(sh), ctypes.byref(attrs),
                        torch.cuda.current_stream().cuda_stream)
-    for field, value, code in (("head_dim", 64, -3), ("page_size", 24, -2), ("num_kv_heads", 1, -2), ("kv_dtype", 7, -4)):
+    for field, value, code in (("head_dim", 64, -3), ("page_size", 12, -2), ("num_kv_heads", 1, -2), ("kv_dtype", 7, -4)):
         sh = _cabi.Shape(*[getattr(shape, f) for f, _ in shape._fields_])
         setattr(sh, field, value)
         if field == "num_kv_heads":

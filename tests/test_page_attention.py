@@ -34,7 +34,8 @@ def test_oracle_page_attention_agrees_with_ragged_oracle():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("page,hq,hkv,d", [(16, 8, 2, 128), (8, 8, 4, 64), (32, 16, 8, 256), (64, 4, 4, 128), (16, 32, 2, 128),
-                                           (4, 8, 2, 128), (24, 8, 4, 64), (1, 4, 2, 128)])  # the last three: cp.async gather
+                                           (24, 8, 4, 64), (48, 8, 2, 128), (4, 8, 2, 128), (12, 8, 4, 64), (1, 4, 2, 128)])
+# 24 and 48: 8- and 16-token TMA boxes; the last three (no multiple of 8): cp.async gather
 def test_cuda_page_attention_matches_oracle(rpa_lib, page, hq, hkv, d):
     import ejkernel_b200 as ej
 

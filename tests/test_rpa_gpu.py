@@ -62,9 +62,12 @@ def test_head_configs(rpa_lib, head_dim, hq, hkv):
     _check(b, f"hq{hq} hkv{hkv} d{head_dim}")
 
 
-@pytest.mark.parametrize("page_size", [1, 3, 8, 16, 32, 64, 128])
+@pytest.mark.parametrize("page_size", [1, 3, 4, 8, 12, 16, 24, 32, 40, 48, 64, 96, 128, 136])
 def test_page_sizes(rpa_lib, page_size):
-    b = make_ragged_batch([1, 1, 5, 1], [777, 129, 300, 64], num_q_heads=8, num_kv_heads=2, head_dim=128,
+    """Multiples of 8 take the TMA gather (boxes of the largest power of two dividing the page, 8 to 64 tokens, so
+    that no box straddles a page), every other size the cp.async gather; mixed batch, so the tensor-tile kernel's
+    8-token boxes are covered too."""
+    b = make_ragged_batch([1, 1, 5, 1, 70], [777, 129, 300, 64, 400], num_q_heads=8, num_kv_heads=2, head_dim=128,
                           page_size=page_size, seed=page_size)
     _check(b, f"page_size {page_size}")
 

@@ -20,9 +20,11 @@ def _cases():
     # head_dim 64: the cache's last dim is padded to 128 (align_to(D, 128), _kernel.py:45-57)
     yield "d64_padded", make_ragged_batch([1, 33, 2, 90], [700, 33, 130, 400], num_q_heads=8, num_kv_heads=2, head_dim=64,
                                           page_size=16, seed=65, sliding_window=300)
-    # ... and with a page size the TMA gather cannot express (cp.async gather)
+    # ... and with a page size that is no power of two (8-token TMA boxes) / no multiple of 8 (cp.async gather)
     yield "d64_padded_page24", make_ragged_batch([1, 20], [333, 100], num_q_heads=4, num_kv_heads=2, head_dim=64,
                                                  page_size=24, seed=66)
+    yield "d64_padded_page12", make_ragged_batch([1, 20], [333, 100], num_q_heads=4, num_kv_heads=2, head_dim=64,
+                                                 page_size=12, seed=67)
     yield "empty_seq", make_ragged_batch([1, 0, 5], [50, 20, 5], num_q_heads=4, num_kv_heads=4, head_dim=128, page_size=8,
                                          max_num_seqs=5, pad_query_rows=3, seed=64)
 
