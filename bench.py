@@ -25,7 +25,7 @@ checks results:
                             head_dim 256) and c5 (long context), each with step time, kernel time and roofline;
   ``c5_strong`` (N > 1)     the SAME 64 long-context sequences with Hkv/N kv heads per rank: strong scaling;
   ``parity_sample``         every rank compares a few sequences of every batch it ran with the CPU oracle
-                            (float32 contractions) and the verdicts and status words of all ranks are reduced.
+                            (float32 contractions) and the results and status words of all ranks are reduced.
 """
 
 from __future__ import annotations
@@ -634,7 +634,7 @@ def main():
             c5_strong["scaling"] = "strong: the same 64 sequences at every N, kv heads split over the ranks"
 
     if world > 1:
-        # one flag per status bit plus the parity verdict, MAX over ranks = OR
+        # one flag per status bit plus the parity result, MAX over ranks = OR
         bits = torch.tensor([(status_all >> i) & 1 for i in range(8)] + [0 if parity["ok"] else 1], device=dev,
                             dtype=torch.int64)
         dist.all_reduce(bits, op=dist.ReduceOp.MAX)

@@ -39,7 +39,7 @@ Where the Triton kernels differ from the XLA implementation, and how the cases d
     Triton 3.6 does not have.  The attempt and its error message are kept in the fixture file (``qblock_error``).
   * attention sinks are not implemented by either Triton kernel: unpinned.
 
-    python tests/golden/make_reference_fixtures.py --device cpu
+    python tests/golden/make_reference_fixtures.py --device cpu --reference-root <checkout of erfanzar/ejkernel>
 """
 
 from __future__ import annotations
@@ -189,9 +189,12 @@ def bits(t):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--device", choices=("cpu", "cuda"), default="cpu")
-    ap.add_argument("--reference-root", default=os.environ.get("EJK_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference-root", default=os.environ.get("EJK_REFERENCE_ROOT"),
+                    help="checkout of erfanzar/ejkernel (v0.0.16) to load the Triton kernels from; or set EJK_REFERENCE_ROOT")
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
+    if not a.reference_root:
+        ap.error("--reference-root (or EJK_REFERENCE_ROOT) must name a checkout of the reference")
     if a.device == "cpu":
         os.environ["TRITON_INTERPRET"] = "1"  # must be set before triton is imported
     import numpy as np

@@ -65,7 +65,7 @@ def test_parity_sample_accepts_the_oracle_and_rejects_a_wrong_row():
     bad = good.clone()
     bad[0] += 0.5  # sequence 0 is always among the sampled ones
     assert not bench.parity_sample(b, bad)["ok"]
-    # an e4m3 pool is judged by the weight-rounding bound
+    # an e4m3 pool is checked against the weight-rounding bound
     b8 = make_workload("c2", num_seqs=6, len_scale=0.05, kv_dtype=torch.float8_e4m3fn)
     good8 = torch.from_numpy(dense_reference(*b8.args(), **b8.kwargs())).to(torch.bfloat16)
     assert bench.parity_sample(b8, good8)["ok"]
