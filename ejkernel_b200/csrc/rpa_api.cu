@@ -26,7 +26,7 @@ struct Options {
   // 256 x 8 tokens at kv 128..8192 1.45 -> 1.18 ms, 256 x 12 tokens 2.16 -> 1.22 ms; at 17-31 rows it
   // depends on the lengths (faster at kv <= 1024, 7 % slower on long ragged contexts).
   int prefill_rows = 32;
-  int prefill_share = 120;  // see Params::prefill_share; 0 = the tile kernel always uses every SM
+  int prefill_share = 125;  // see Params::prefill_share; 0 = the tile kernel always uses every SM
 };
 Options g_opt;
 thread_local int t_last_launches = 0;

@@ -193,7 +193,8 @@ rpa_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const Params p) 
     const float stages = (float)p.header[kHdrPrefillStages] * (float)Hkv;           // (item, head) stages of 64 tokens
     const float dec_bytes = (float)p.header[kHdrTotalKeys] * (float)Hkv * (float)(2 * D * sizeof(T));
     // one stage of two 128-row tiles: 2460 cycles measured on evenly divisible work at head_dim 128, 0.93 of that at 64
-    constexpr float kStageUs = D == 64 ? 1.15f : 1.25f;
+    // (a soft cap puts a tanh on every logit: the softmax threads, which bound the stage, take about 1.6 times as long)
+    const float kStageUs = (D == 64 ? 1.15f : 1.25f) * (p.cap != 0.f ? 1.6f : 1.f);
     constexpr float kDecodeBpUs = 6.6e6f;  // bytes per microsecond the split-KV kernel streams
     const float t_p = stages * kStageUs / (float)gridDim.x, t_d = dec_bytes / kDecodeBpUs;
     if (t_d > t_p && t_p > 0.f) {

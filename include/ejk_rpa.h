@@ -214,7 +214,7 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *   "path"       0 = auto, 1 = force the cp.async gather, 2 = force the TMA gather
  *   "prefill_rows" sequences with at least this many (query token, head-in-group) rows per kv head are
  *                served by 128-row tcgen05 tiles instead of 8-row split-KV tiles (default 32; 0 = never)
- *   "prefill_share" percent (default 120; 0 = off): in a batch that mixes multi-token sequences with decode rows the
+ *   "prefill_share" percent (default 125; 0 = off): in a batch that mixes multi-token sequences with decode rows the
  *                tensor-tile kernel keeps only as many CTAs as make it finish about when the bandwidth-bound split-KV
  *                kernel does (estimated on the device from the plan, times this percentage) and leaves the other SMs to
  *                that kernel from the start
