@@ -156,6 +156,8 @@ class RaggedPageAttention:
                                            softmax_scale=softmax_scale, logits_soft_cap=logits_soft_cap,
                                            sliding_window=sliding_window, softmax_aux=softmax_aux))
         if cfg is None and not _tuning._overlays and self.selector.cache.get(dev, self.op_id_v, key) is chosen:
+            if len(self._fast) > 4096:  # a serving loop with ever new shapes must not grow this without bound
+                self._fast.clear()
             self._fast[fast] = chosen
         return chosen, key
 
