@@ -136,7 +136,9 @@ class RaggedPageAttention:
         """The configuration for this call, in the order of the reference's ``ConfigSelectorChain.choose``
         (ejkernel/ops/config/selection.py:384-566).  Returns ``(cfg, call_key or None)``.  Calls whose static
         signature (shapes, dtypes, window, cap, sinks shape, device) was resolved before take a dictionary look-up."""
-        fast = (queries.device.index, tuple(queries.shape), queries.dtype, tuple(kv_pages.shape), kv_pages.dtype,
+        # token count and pool size enter as their bit lengths (= rounded up to a power of two, as in ``call_key``)
+        fast = (queries.device.index, (queries.shape[0] - 1).bit_length(), queries.shape[1:], queries.dtype,
+                (kv_pages.shape[0] - 1).bit_length(), kv_pages.shape[1:], kv_pages.dtype,
                 tuple(block_tables.shape), sliding_window, logits_soft_cap,
                 None if softmax_aux is None else tuple(softmax_aux.shape))
         if cfg is None and not _tuning._overlays:

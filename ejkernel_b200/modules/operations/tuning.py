@@ -93,9 +93,15 @@ def call_key(queries: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.
              softmax_aux: torch.Tensor | None = None) -> str:
     """Hash of everything static about a call: operand shapes and dtypes and the static keywords.
     The lengths are data and are not part of it (the device planner adapts to them)."""
+    # The token count and the pool size change from step to step in a serving loop, and the two tuned hints depend on
+    # them only weakly: both enter rounded up to a power of two, so that a loop with ragged batches resolves (and, under
+    # the autotune policy, measures) a handful of signatures instead of one per step.
+    up = lambda n: 1 << max(0, int(n) - 1).bit_length()
+    q_shape = (up(queries.shape[0]), *queries.shape[1:])
+    kv_shape = (up(kv_pages.shape[0]), *kv_pages.shape[1:])
     sig = {
-        "queries": (tuple(queries.shape), str(queries.dtype)),
-        "kv_pages": (tuple(kv_pages.shape), str(kv_pages.dtype)),
+        "queries": (tuple(q_shape), str(queries.dtype)),
+        "kv_pages": (tuple(kv_shape), str(kv_pages.dtype)),
         "block_tables": tuple(block_tables.shape),
         "sliding_window": None if sliding_window is None else int(sliding_window),
         "logits_soft_cap": None if logits_soft_cap is None else float(logits_soft_cap),

@@ -43,7 +43,9 @@ def test_call_key_depends_on_static_facts_only():
     q, kv, lens, tab, _, _ = _operands()
     k0 = call_key(q, kv, tab)
     assert k0 == call_key(q.clone(), kv.clone(), tab + 3)  # values do not matter
-    assert k0 != call_key(q[:5], kv, tab)
+    assert k0 == call_key(q[:5], kv, tab)  # 6 and 5 query tokens round up to the same power of two: one signature ...
+    assert k0 != call_key(q[:4], kv, tab) and k0 != call_key(q, kv[:8], tab)  # ... 4 tokens, or half the pool, do not
+    assert k0 != call_key(q[:, :4], kv, tab)  # every other dimension counts exactly
     assert k0 != call_key(q, kv, tab, sliding_window=128)
     assert k0 != call_key(q, kv, tab, logits_soft_cap=30.0)
     assert k0 != call_key(q.half(), kv.half(), tab)
