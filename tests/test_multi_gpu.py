@@ -1,7 +1,7 @@
 """KV-head sharding on real GPUs: two processes, one GPU each, NCCL.  Each rank runs the CUDA operator
 on its head shard through the public shard-map style entry; the head-sharded output needs no
-collective, the replicated one is an NCCL all-gather of the output heads.  Skipped unless the box has
-at least two GPUs."""
+collective, the replicated one is an NCCL all-gather of the output heads; that test is skipped unless the
+box has at least two GPUs.  The partitioning alone (shards run one after another) is checked on any box."""
 
 import os
 import socket
@@ -71,3 +71,23 @@ def test_two_gpu_head_sharding_matches_oracle(rpa_lib):
     assert r["finite"] and r["allclose"] and r["tight"] and r["max_rel_rms"] <= REL_RMS, r
     for o in outs:
         np.testing.assert_array_equal(o[True], sharded)  # the all-gather moves bits, it does not change them
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_head_shards_run_one_after_another_on_one_gpu(rpa_lib, world):
+    """The partitioning itself needs no second GPU to be checked: the KV-head shards are independent problems, so
+    running them one after another on one device and joining the heads must give the operator's answer."""
+    import ejkernel_b200 as ej
+    from ejkernel_b200.sharding import local_shard
+
+    b = _batch()
+    rest = [t.cuda() for t in (b.context_lens, b.block_tables, b.query_start_loc, b.num_seqs)]
+    parts = []
+    for rank in range(world):
+        q, kv, _ = local_shard(b.queries, b.kv_pages, rank, world)
+        parts.append(ej.ragged_page_attention(q.cuda(), kv.cuda(), *rest, softmax_scale=b.softmax_scale,
+                                              sliding_window=b.sliding_window))
+    torch.cuda.synchronize()
+    joined = torch.cat(parts, dim=1).float().cpu().numpy()
+    r = compare(joined, dense_reference(*b.args(), **b.kwargs()), atol=ATOL, rtol=RTOL)
+    assert r["finite"] and r["allclose"] and r["tight"] and r["max_rel_rms"] <= REL_RMS, r
