@@ -9,24 +9,26 @@
 namespace ejk {
 namespace {
 
+// Process-wide options.  Atomic because ejk_rpa_set_option may be called from one host thread while another
+// launches; a launch reads each option once.
 struct Options {
-  int waves = 4;           // split-KV work items per CTA (with longest-first queueing, fewer and longer items win)
-  int min_chunk = 256;
-  int path = 0;
-  int profile = 0;
-  int prefill_split = 1;   // prefill items are cut along KV at CTA-quota boundaries (needs the larger workspace)
-  int sort_items = 1;      // split-KV work items longest first
-  int test_withhold = 0;   // test hook, see Params::test_withhold
-  int overlap = 1;         // programmatic dependent launches: kernels of one call overlap where they are independent
-  int fused_merge = 1;     // the TMA split-KV kernel combines the chunks of a tile itself (no merge kernel)
-  int wait_ms = 2000;      // bound of every in-kernel wait; expiry sets EJK_RPA_ST_TIMEOUT
+  std::atomic<int> waves{4};           // split-KV work items per CTA (with longest-first queueing, fewer and longer items win)
+  std::atomic<int> min_chunk{256};
+  std::atomic<int> path{0};
+  std::atomic<int> profile{0};
+  std::atomic<int> prefill_split{1};   // prefill items are cut along KV at CTA-quota boundaries (needs the larger workspace)
+  std::atomic<int> sort_items{1};      // split-KV work items longest first
+  std::atomic<int> test_withhold{0};   // test hook, see Params::test_withhold
+  std::atomic<int> overlap{1};         // programmatic dependent launches: kernels of one call overlap where they are independent
+  std::atomic<int> fused_merge{1};     // the TMA split-KV kernel combines the chunks of a tile itself (no merge kernel)
+  std::atomic<int> wait_ms{2000};      // bound of every in-kernel wait; expiry sets EJK_RPA_ST_TIMEOUT
   // Sequences with at least this many (token, head-in-group) rows use 128-row tensor tiles.  8-row split-KV
   // tiles re-read a sequence's KV once per tile, so from four tiles on (8 query tokens at G = 4) the
   // tensor-tile kernel, which reads it once, is faster even with three quarters of its rows empty:
   // 256 x 8 tokens at kv 128..8192 1.45 -> 1.18 ms, 256 x 12 tokens 2.16 -> 1.22 ms; at 17-31 rows it
   // depends on the lengths (faster at kv <= 1024, 7 % slower on long ragged contexts).
-  int prefill_rows = 32;
-  int prefill_share = 125;  // see Params::prefill_share; 0 = the tile kernel always uses every SM
+  std::atomic<int> prefill_rows{32};
+  std::atomic<int> prefill_share{125};  // see Params::prefill_share; 0 = the tile kernel always uses every SM
 };
 Options g_opt;
 thread_local int t_last_launches = 0;
@@ -35,6 +37,7 @@ thread_local int t_last_launches = 0;
 struct ProfileEvents {  // before the planner, after it, after the prefill-tile kernel, after the split-KV kernel, after the merge
   cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
   bool created = false, recorded = false;
+  int device = -1;  // the device the events belong to (events cannot time work of another device)
 };
 thread_local ProfileEvents t_prof;
 
@@ -75,6 +78,8 @@ int check_shape(const ejk_rpa_shape* s) {
   if (s->head_dim != 64 && s->head_dim != 128 && s->head_dim != 256) return EJK_RPA_E_HEAD_DIM;
   if (s->dtype != EJK_RPA_BF16 && s->dtype != EJK_RPA_F16) return EJK_RPA_E_DTYPE;
   if ((long long)s->pages_per_seq * s->page_size > 0x3fffffffLL) return EJK_RPA_E_SHAPE;
+  // row, tile and work-item counts are 32-bit in the planner and the work lists
+  if ((long long)s->total_tokens * s->num_q_heads > 0x3fffffffLL || s->max_num_seqs > 0x00ffffff) return EJK_RPA_E_SHAPE;
   if (s->kv_dtype != 0 && s->kv_dtype != EJK_RPA_E4M3) return EJK_RPA_E_DTYPE;
   if (s->kv_dtype == EJK_RPA_E4M3) {
     if (s->head_dim != 128 && s->head_dim != 256) return EJK_RPA_E_HEAD_DIM;
@@ -351,10 +356,19 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool prof = g_opt.profile != 0;
-  if (prof && !t_prof.created) {
-    for (auto& ev : t_prof.ev)
-      if (cudaError_t ce = cudaEventCreate(&ev); ce != cudaSuccess) return static_cast<int>(ce);
-    t_prof.created = true;
+  if (prof) {
+    int dev = -1;
+    if (cudaError_t ce = cudaGetDevice(&dev); ce != cudaSuccess) return static_cast<int>(ce);
+    if (t_prof.created && t_prof.device != dev) {  // the thread moved to another GPU: its events stay behind
+      for (auto& ev : t_prof.ev) cudaEventDestroy(ev);
+      t_prof.created = false;
+    }
+    if (!t_prof.created) {
+      for (auto& ev : t_prof.ev)
+        if (cudaError_t ce = cudaEventCreate(&ev); ce != cudaSuccess) return static_cast<int>(ce);
+      t_prof.created = true;
+      t_prof.device = dev;
+    }
   }
   t_prof.recorded = false;
   if (prof) cudaEventRecord(t_prof.ev[0], st);

@@ -50,7 +50,7 @@ extern "C" {
 
 /* invalid-argument codes */
 #define EJK_RPA_E_NULL (-1)      /* a required pointer is null */
-#define EJK_RPA_E_SHAPE (-2)     /* a dimension is <= 0, Hq % Hkv != 0, ... */
+#define EJK_RPA_E_SHAPE (-2)     /* a dimension is <= 0 or beyond its limit, Hq % Hkv != 0, ... */
 #define EJK_RPA_E_HEAD_DIM (-3)  /* head_dim not in {64, 128, 256} */
 #define EJK_RPA_E_DTYPE (-4)     /* unknown dtype code */
 #define EJK_RPA_E_WORKSPACE (-5) /* workspace smaller than ejk_rpa_workspace_bytes_min() / misaligned */
@@ -69,7 +69,9 @@ extern "C" {
 #define EJK_RPA_ST_INTERNAL 16u /* planner produced more work items than the workspace holds */
 #define EJK_RPA_ST_TIMEOUT 32u  /* a bounded wait inside a kernel ran out (outputs are invalid) */
 
-/* Static problem description: everything here is known from array shapes at trace time. */
+/* Static problem description: everything here is known from array shapes at trace time.
+ * Limits (EJK_RPA_E_SHAPE beyond them): total_tokens * num_q_heads < 2^30, max_num_seqs < 2^24,
+ * pages_per_seq * page_size < 2^30 -- row, sequence and token positions are 32-bit in the work lists. */
 typedef struct ejk_rpa_shape {
   int32_t total_tokens;  /* rows of queries / out */
   int32_t max_num_seqs;  /* block_tables.shape[0] */

@@ -577,6 +577,20 @@ def test_host_errors(rpa_lib):
         ragged_page_attention(b.queries, b.kv_pages.float(), b.context_lens, b.block_tables, b.query_start_loc, b.num_seqs)
     with pytest.raises(Exception):  # rank mismatch is a type-check error, as in the reference
         ragged_page_attention(b.queries[0], b.kv_pages, b.context_lens, b.block_tables, b.query_start_loc, b.num_seqs)
+    # shapes whose row or sequence counts do not fit the 32-bit work lists are refused on the host
+    import ctypes
+
+    from ejkernel_b200 import _cabi
+
+    lib = _cabi.load()
+    for shape in (_cabi.Shape(1 << 28, 4, 4, 16, 8, 8, 2, 64, _cabi.BF16, 0),   # 2^31 query rows
+                  _cabi.Shape(8, 1 << 24, 4, 16, 8, 4, 2, 64, _cabi.BF16, 0)):  # 2^24 sequences
+        assert lib.ejk_rpa_workspace_bytes(ctypes.byref(shape)) == 0
+        rc = lib.ejk_rpa_launch(b.queries.data_ptr(), b.kv_pages.data_ptr(), b.context_lens.data_ptr(),
+                                b.block_tables.data_ptr(), b.query_start_loc.data_ptr(), b.num_seqs.data_ptr(), None,
+                                b.queries.data_ptr(), b.queries.data_ptr(), 1 << 20, None, ctypes.byref(shape),
+                                ctypes.byref(_cabi.Attrs(1.0, 0.0, 0, 0, 0, 0, 0)), None)
+        assert rc == -2 and lib.ejk_rpa_last_launch_count() == 0  # EJK_RPA_E_SHAPE, nothing enqueued
 
 
 def test_enqueue_only_call_can_be_captured_in_a_cuda_graph(rpa_lib):
