@@ -28,7 +28,11 @@
 // Things measured and left out: a polynomial 2^x on the FMA pipe for part of the exponentials (no gain:
 // issue slots are as scarce as MUFU slots with so few warps), two threads per row (the exchange of
 // row maxima costs more than the shorter rows save), 80/96/128-token stages with P aliased on S
-// (the tile's S -> softmax -> P.V chain then bounds the stage).
+// (the tile's S -> softmax -> P.V chain then bounds the stage; at 128 tokens also with one thread
+// issuing all MMAs in order, K and V in separate slots and the row's 128 logits fetched with a single
+// TMEM wait under a register hand-over between warpgroups: level with this kernel, not faster --
+// with the tiles half a stage apart one softmax warp per scheduler works at a time, and a warp
+// cannot issue while one of its ex2 is dispatched to the MUFU unit).
 //
 // Warp roles (384 threads with two tiles, one CTA per SM, persistent over the planner's prefill queue):
 //   warp 0        TMA producer: one box {64 elems, 8 tokens, D/64, (K_h, V_h)} per 8-token group,
