@@ -379,7 +379,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   // a prefill kernel the split-KV kernel is the planner's dependent and waits for the plan itself.
   const bool pdl = g_opt.overlap != 0 && !prof && use_tma;
   p.pdl = pdl ? (use_prefill ? 1 : 2) : 0;
-  cudaError_t e = launch_plan(p, st);
+  cudaError_t e = launch_plan(p, st, pdl);
   if (e != cudaSuccess) return static_cast<int>(e);
   ++t_last_launches;
   if (prof) cudaEventRecord(t_prof.ev[1], st);
@@ -394,7 +394,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   ++t_last_launches;
   if (prof) cudaEventRecord(t_prof.ev[3], st);
   if (!p.fused_merge) {
-    e = launch_merge(p, s.dtype, d->sm_count, st);
+    e = launch_merge(p, s.dtype, d->sm_count, st, pdl);
     if (e != cudaSuccess) return static_cast<int>(e);
     ++t_last_launches;
   }

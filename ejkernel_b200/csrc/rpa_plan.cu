@@ -154,6 +154,10 @@ __device__ void block_scan(int (&v)[kCnt], int (&excl)[kCnt], int (&total)[kCnt]
 __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) {
   // kernels launched as programmatic dependents may start their prologue now; they pdl_wait() for the plan
   pdl_trigger();
+  // The planner itself is launched as a programmatic dependent of whatever precedes it in the stream (the previous
+  // call's last kernel in a serving loop), which hides its launch latency; it touches no memory before that kernel has
+  // completed.  (The kernels released above wait for this grid's completion, so they are ordered behind it as well.)
+  pdl_wait();
   __shared__ int s_warp[32][kCnt];
   __shared__ unsigned long long s_keys;
   __shared__ int s_tiles;
@@ -483,9 +487,8 @@ __global__ void __launch_bounds__(kPlanThreads) rpa_plan_kernel(const Params p) 
 
 }  // namespace
 
-cudaError_t launch_plan(const Params& p, cudaStream_t stream) {
-  rpa_plan_kernel<<<1, kPlanThreads, 0, stream>>>(p);
-  return cudaGetLastError();
+cudaError_t launch_plan(const Params& p, cudaStream_t stream, bool pdl) {
+  return launch_kernel(rpa_plan_kernel, dim3(1), dim3(kPlanThreads), 0, stream, pdl, p);
 }
 
 }  // namespace ejk

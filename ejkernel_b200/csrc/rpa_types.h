@@ -122,7 +122,7 @@ struct Params {
 };
 
 // launchers (each returns cudaError_t of the launch)
-cudaError_t launch_plan(const Params& p, cudaStream_t stream);
+cudaError_t launch_plan(const Params& p, cudaStream_t stream, bool pdl);
 cudaError_t launch_splitkv(const Params& p, int dtype, int n_sm, cudaStream_t stream);
 bool tma_path_supported(const Params& p);
 cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_t stream, bool pdl);
@@ -149,7 +149,7 @@ inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, 
   cfg.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
-cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stream);
+cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stream, bool pdl);
 cudaError_t launch_kv_update(const void* k_new, const void* v_new, void* cache, const int32_t* kv_lens,
                              const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                              int32_t* status, int T, int S_max, int pages_per_seq, int num_pages, int page_size, int Hkv,
