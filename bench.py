@@ -344,8 +344,18 @@ def parity_sample(batch, out, n_check: int = 4) -> dict:
 
 
 # --------------------------------------------------------------------------------------------
+def emit(line: dict, out_fd: int) -> None:
+    os.write(out_fd, (json.dumps(line) + "\n").encode())
+
+
 def main():
     args = parse_args()
+    # The contract is ONE line on stdout.  Libraries loaded below may write there too (NCCL prints its version to stdout
+    # when NCCL_DEBUG is set), so everything but the result line is sent to stderr: file descriptor 1 is pointed at
+    # stderr for the run, and the JSON line goes to the original stdout.
+    sys.stdout.flush()
+    out_fd = os.dup(1)
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -398,7 +408,7 @@ def main():
             "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
         }
-        print(json.dumps(line))
+        emit(line, out_fd)
         return
 
     # ---------------- our arm ----------------
@@ -688,7 +698,7 @@ def main():
         line["per_workload"] = per_workload
     if c5_strong is not None:
         line["c5_strong"] = c5_strong
-    print(json.dumps(line))
+    emit(line, out_fd)
     if world > 1:
         dist.destroy_process_group()
 
