@@ -226,7 +226,10 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *                2 = cut at every quota boundary, whatever the rule says (a measurement aid)
  *   "sort_items" 1 (default) = the planner queues split-KV work items longest first, 0 = in sequence order
  *   "overlap"    1 (default) = the kernels of one call are launched as programmatic dependents: each starts under
- *                the tail of the one before and waits on the device for what it needs; 0 = plain stream order
+ *                the tail of the one before and waits on the device for what it needs.  The first of them, the
+ *                planner, is launched the same way behind whatever precedes the call in the stream and waits for
+ *                that work's completion before it touches memory, so the call is ordered exactly as in plain
+ *                stream order; only launch latency is hidden.  0 = plain stream order
  *   "fused_merge" 1 (default) = where a row tile gets few KV chunks (decided from the static shapes) the split-KV
  *                kernel's last-finishing chunk combines the chunks of its tile; 0 = always a separate merge kernel;
  *                2 = always fused
