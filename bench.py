@@ -354,8 +354,11 @@ def main():
     # when NCCL_DEBUG is set), so everything but the result line is sent to stderr: file descriptor 1 is pointed at
     # stderr for the run, and the JSON line goes to the original stdout.
     sys.stdout.flush()
-    out_fd = os.dup(1)
-    os.dup2(2, 1)
+    try:
+        out_fd = os.dup(1)
+        os.dup2(2, 1)
+    except OSError:  # no usable stderr: leave stdout alone
+        out_fd = 1
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
