@@ -83,7 +83,7 @@ int check_shape(const ejk_rpa_shape* s) {
   if (s->kv_dtype != 0 && s->kv_dtype != EJK_RPA_E4M3) return EJK_RPA_E_DTYPE;
   if (s->kv_dtype == EJK_RPA_E4M3) {
     if (s->head_dim != 128 && s->head_dim != 256) return EJK_RPA_E_HEAD_DIM;
-    if (s->page_size < 8 || s->page_size % 8 != 0 || (s->num_kv_heads & 1)) return EJK_RPA_E_SHAPE;
+    if (s->page_size < 8 || s->page_size % 8 != 0) return EJK_RPA_E_SHAPE;
   }
   return 0;
 }
@@ -231,7 +231,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
                        const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                        const float* softmax_aux, void* out, void* workspace, size_t workspace_bytes,
                        int32_t* status, const ejk_rpa_shape* shape, const ejk_rpa_attrs* attrs, void* stream,
-                       int kv_dim = 0) {
+                       int kv_dim = 0, int kv_heads_alloc = 0) {
   t_last_launches = 0;
   const DeviceInfo* d = nullptr;
   if (int e = validate(queries, kv_pages, value_cache, context_lens, block_tables, query_start_loc, num_seqs,
@@ -278,6 +278,7 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.G = s.num_q_heads / s.num_kv_heads;
   p.D = s.head_dim;
   p.Dkv = kv_dim > 0 ? kv_dim : s.head_dim;
+  p.C2 = kv_heads_alloc > 0 ? kv_heads_alloc : 2 * s.num_kv_heads;
   p.rows_per_tile = L.rows_per_tile;
   p.max_units = L.max_units;
   p.max_merge = L.max_merge;
@@ -448,13 +449,17 @@ int ejk_rpa_v3_launch(const void* queries, const void* keys, const void* values,
   const int d_align = (shape->head_dim + 127) / 128 * 128;
   if ((reinterpret_cast<uintptr_t>(keys) | reinterpret_cast<uintptr_t>(values)) & 15) return EJK_RPA_E_ALIGN;
   const int32_t* num_seqs = distribution + 2;  // distribution = (decode_end, prefill_end, num_seqs), _kernel.py:211
+  // the cache also pads the combined heads to a multiple of the packing -- 32 bits' worth of elements, i.e. 2 at 16
+  // bits (never any padding) and 4 for e4m3 (an odd number of kv heads leaves two padding heads), _kernel.py:45-57
+  const int pack = shape->kv_dtype == EJK_RPA_E4M3 ? 4 : 2;
+  const int c2 = (2 * shape->num_kv_heads + pack - 1) / pack * pack;
   cudaError_t ce = launch_kv_update(keys, values, kv_cache, kv_lens, block_tables, query_start_loc, num_seqs, status,
                                     shape->total_tokens, shape->max_num_seqs, shape->pages_per_seq, shape->num_pages,
-                                    shape->page_size, shape->num_kv_heads, shape->head_dim, d_align,
+                                    shape->page_size, shape->num_kv_heads, c2, shape->head_dim, d_align,
                                     shape->kv_dtype == EJK_RPA_E4M3 ? 1 : 2, static_cast<cudaStream_t>(stream));
   if (ce != cudaSuccess) return static_cast<int>(ce);
   const int rc = launch_impl(queries, kv_cache, nullptr, kv_lens, block_tables, query_start_loc, num_seqs, nullptr, out,
-                             workspace, workspace_bytes, status, shape, attrs, stream, d_align);
+                             workspace, workspace_bytes, status, shape, attrs, stream, d_align, c2);
   if (rc == 0) ++t_last_launches;
   return rc;
 }

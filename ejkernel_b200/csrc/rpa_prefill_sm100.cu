@@ -990,7 +990,7 @@ cudaError_t launch_prefill(const Params& p, int dtype, int n_sm, cudaStream_t st
   EncodeFn enc = encode_fn_p();
   if (!enc) return cudaErrorNotSupported;
   const uint64_t esz = 2;
-  const uint64_t D = p.D, Dkv = p.Dkv, C2 = 2ull * p.Hkv;
+  const uint64_t D = p.D, Dkv = p.Dkv, C2 = (uint64_t)p.C2;
   cuuint64_t dims[5] = {64, (cuuint64_t)p.page_size, D / 64, C2, (cuuint64_t)p.num_pages};
   cuuint64_t strides[4] = {C2 * Dkv * esz, 64 * esz, Dkv * esz, (cuuint64_t)p.page_size * C2 * Dkv * esz};
   // one box = 8 tokens x (K_h, V_h) x all of D: per token one contiguous 2*D-element run in global memory

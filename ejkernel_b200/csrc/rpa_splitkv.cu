@@ -122,7 +122,7 @@ rpa_splitkv_kernel(const Params p) {
     const uint32_t sbase = smem_base + slot * C::STAGE_BYTES;
     const int32_t* tab = p.block_tables + (size_t)c.u.seq * p.pages_per_seq;
     const size_t head_stride = (size_t)p.Dkv * sizeof(T);  // K_h and V_h are one (possibly padded) row apart
-    const size_t tok_stride = (size_t)2 * Hkv * head_stride;
+    const size_t tok_stride = (size_t)p.C2 * head_stride;
     const uint8_t* kvb = reinterpret_cast<const uint8_t*>(p.kv) + (size_t)(2 * c.h) * head_stride;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {

@@ -1018,7 +1018,7 @@ cudaError_t launch_splitkv_tma(const Params& p, int dtype, int n_sm, cudaStream_
   // elements of the innermost dimension: one 128-byte swizzle row = 64 16-bit or 128 e4m3 values
   const bool kv8 = p.kv8 != 0;
   const uint64_t esz = kv8 ? 1 : 2, inner = 128 / esz;
-  const uint64_t D = p.D, Dkv = p.Dkv, C2 = 2ull * p.Hkv;
+  const uint64_t D = p.D, Dkv = p.Dkv, C2 = (uint64_t)p.C2;
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   const CUtensorMapDataType dt = kv8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                      : (dtype == EJK_RPA_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;

@@ -98,6 +98,8 @@ struct Params {
   int32_t prefill_item_rows; // rows one prefill work item covers (128 per tile, 1 or 2 tiles per CTA)
   int32_t Dkv;               // elements between consecutive combined heads of kv_pages (head_dim, or the padded
                              // head_dim of a v3 cache)
+  int32_t C2;                // combined heads per token row in memory: 2 * Hkv, or more in a v3 cache that pads them to
+                             // a multiple of the packing (four e4m3 heads per 32-bit word)
   int32_t sort_items;        // 1: split-KV work items are queued longest first, 0: in sequence order
   int32_t test_withhold;     // test hook: bit 0 / bit 1 = the CTA of the split-KV / prefill kernel that takes work item 0
                              // never announces the item's first KV stage, so that the waits on it run out
@@ -153,6 +155,6 @@ cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stre
 cudaError_t launch_kv_update(const void* k_new, const void* v_new, void* cache, const int32_t* kv_lens,
                              const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                              int32_t* status, int T, int S_max, int pages_per_seq, int num_pages, int page_size, int Hkv,
-                             int D, int Dalign, int elem_bytes, cudaStream_t stream);
+                             int C2, int D, int Dalign, int elem_bytes, cudaStream_t stream);
 
 }  // namespace ejk

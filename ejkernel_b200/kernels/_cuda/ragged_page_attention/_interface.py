@@ -137,9 +137,8 @@ def _validate(queries, kv_pages, context_lens, block_tables, query_start_loc, nu
     _, num_q_heads, head_dim = queries.shape
     _, page_size, num_combined_kv_heads, head_dim_k = kv_pages.shape
     if kv_pages.dtype == FP8:
-        if head_dim not in (128, 256) or page_size % 8 or num_combined_kv_heads % 4:
-            raise NotImplementedError("an e4m3 KV cache needs head_dim 128 or 256, a page size that is a multiple of 8 "
-                                      "and an even number of kv heads")
+        if head_dim not in (128, 256) or page_size % 8:
+            raise NotImplementedError("an e4m3 KV cache needs head_dim 128 or 256 and a page size that is a multiple of 8")
     if num_combined_kv_heads % 2 != 0:
         raise ValueError(f"{num_combined_kv_heads=} must be even (K and V heads interleaved)")
     num_kv_heads = num_combined_kv_heads // 2

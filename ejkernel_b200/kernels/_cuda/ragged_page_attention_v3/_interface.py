@@ -97,8 +97,8 @@ def ragged_page_attention_v3(
         raise ValueError("packing mismatch")
     if d_align != -(-D // 128) * 128:
         raise ValueError("cache last dim must be align_to(D,128)")
-    if hx2_per_pack * pack != 2 * Hkv:
-        raise NotImplementedError("a cache whose combined-head axis is padded beyond 2*num_kv_heads is not supported")
+    if hx2_per_pack * pack != -(-2 * Hkv // pack) * pack:
+        raise ValueError("cache combined-head axis must be align_to(2*num_kv_heads, packing)")  # merge_kv, _kernel.py:45-57
     S_max = kv_lens.shape[0]
     if block_tables.numel() % S_max != 0:
         raise ValueError("block_tables size % num_seqs != 0")

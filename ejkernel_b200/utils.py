@@ -310,9 +310,10 @@ def to_v3_inputs(batch: RaggedBatch, fill: float = float("nan"), pad_fill: float
     the batch's (complete) pool; in the returned cache those positions hold ``fill`` so that the
     operator's page write is observable.  Returns ``(keys, values, kv_cache_5d, block_tables_flat,
     distribution)``; after a correct v3 call the cache equals ``batch.kv_pages`` bit for bit.  When
-    ``head_dim`` is not a multiple of 128 the cache's last dim is padded to one, as the reference pads it;
-    the padding lanes start as ``pad_fill`` (the operator must step over them when it reads and zero
-    them in the rows it writes).
+    ``head_dim`` is not a multiple of 128 the cache's last dim is padded to one, as the reference pads it,
+    and so is the combined-head axis when ``2 * num_kv_heads`` is not a multiple of the packing (an e4m3 cache with
+    an odd number of kv heads); the padding starts as ``pad_fill`` (the operator must step over it when it reads
+    and zero it in the rows it writes).
     Layout as in the reference's ``merge_kv`` / cache (ragged_page_attention_v3/_kernel.py:45-57).
     """
     m = batch.meta
@@ -346,7 +347,12 @@ def to_v3_inputs(batch: RaggedBatch, fill: float = float("nan"), pad_fill: float
         padded = torch.full((*cache.shape[:-1], d_align), pad_fill, dtype=cache.dtype, device=dev)
         padded[..., :D] = cache
         cache = padded
-    cache5 = cache.view(pool.shape[0], page, 2 * Hkv // pack, pack, d_align)
+    c2 = -(-2 * Hkv // pack) * pack  # the combined heads are padded to a multiple of the packing as well (merge_kv)
+    if c2 != 2 * Hkv:
+        padded = torch.full((pool.shape[0], page, c2, d_align), pad_fill, dtype=cache.dtype, device=dev)
+        padded[:, :, : 2 * Hkv] = cache
+        cache = padded
+    cache5 = cache.view(pool.shape[0], page, c2 // pack, pack, d_align)
     if eight:
         keys, values, cache5 = (t.view(pool_t.dtype) for t in (keys, values, cache5))
     S = len(m["q_lens"])

@@ -341,7 +341,9 @@ def v3_reference(
         for r in range(q1 - q0):
             pos = kl - (q1 - q0) + r
             flat[int(tab[s, pos // page]), pos % page, : 2 * Hkv, : k.shape[2]] = fused[q0 + r]
-            flat[int(tab[s, pos // page]), pos % page, : 2 * Hkv, k.shape[2] :] = 0  # merge_kv pads with zeros (:45-57)
+            # merge_kv pads the row with zeros, lanes beyond head_dim and combined heads beyond 2*Hkv alike (:45-57)
+            flat[int(tab[s, pos // page]), pos % page, : 2 * Hkv, k.shape[2] :] = 0
+            flat[int(tab[s, pos // page]), pos % page, 2 * Hkv :, :] = 0
     scale = float(softmax_scale) * (1.0 if k_scale is None else float(k_scale))
     q_in = queries
     if q_scale is not None:
@@ -349,8 +351,9 @@ def v3_reference(
         lim = float(torch.finfo(cache.dtype).max)
         q_in = (qt / float(q_scale)).clamp(-lim, lim).to(cache.dtype)  # :249-254 (the division rounds to q's dtype first)
         scale *= float(q_scale)  # :264-265
-    # the cache's last dim is align_to(D, 128); attention reads the first D lanes (:240-241)
-    res = dense_reference(q_in, flat.view(cache.dtype)[..., : k.shape[2]], ctx, tab, cu, np.array([S]), softmax_scale=scale,
+    # the cache's last dim is align_to(D, 128) and its combined-head axis align_to(2*Hkv, pack); attention reads the
+    # first D lanes of the first 2*Hkv heads (:240-241)
+    res = dense_reference(q_in, flat.view(cache.dtype)[:, :, : 2 * Hkv, : k.shape[2]], ctx, tab, cu, np.array([S]), softmax_scale=scale,
                           sliding_window=sliding_window, logits_soft_cap=logits_soft_cap, precision=precision,
                           p_dtype=cache.dtype if round_p else None, return_weight_bound=return_weight_bound)
     out, wb = res if return_weight_bound else (res, None)

@@ -215,11 +215,73 @@ def test_e4m3_pool_with_attention_sinks_and_refusals(rpa_lib):
                        bc.query_start_loc.data_ptr(), bc.num_seqs.data_ptr(), None, o.data_ptr(), ws.buffer.data_ptr(),
                        ws.nbytes, ws.status.data_ptr(), ctypes.byref(sh), ctypes.byref(attrs),
                        torch.cuda.current_stream().cuda_stream)
-    for field, value, code in (("head_dim", 64, -3), ("page_size", 12, -2), ("num_kv_heads", 1, -2), ("kv_dtype", 7, -4)):
+    for field, value, code in (("head_dim", 64, -3), ("page_size", 12, -2), ("kv_dtype", 7, -4)):
         sh = _cabi.Shape(*[getattr(shape, f) for f, _ in shape._fields_])
         setattr(sh, field, value)
-        if field == "num_kv_heads":
-            sh.num_q_heads = 4
         assert rpa_lib.ejk_rpa_launch(*args(sh)) == code, field
     torch.cuda.synchronize()
     assert bool((o == 7.0).all())
+
+
+# ---- odd numbers of kv heads: MQA, or one rank's share of an 8-way head split of an 8-kv-head model.  The plain
+# operator reads a dense [P, page, 2*Hkv, D] pool; the v3 cache pads the combined heads to four per 32-bit word
+# (merge_kv, _kernel.py:45-57), two padding heads that the page write zeroes and the attention steps over. ----
+def _odd_cases():
+    mk = lambda ql, kl, **kw: make_ragged_batch(ql, kl, kv_dtype=FP8, **kw)
+    yield "mqa", mk([1, 1, 9, 1], [600, 33, 140, 2100], num_q_heads=8, num_kv_heads=1, head_dim=128, page_size=16, seed=91)
+    yield "three_heads", mk([1, 20, 2], [300, 90, 1000], num_q_heads=12, num_kv_heads=3, head_dim=128, page_size=32, seed=92,
+                            sliding_window=400)
+    yield "mqa_d256", mk([1, 3], [500, 64], num_q_heads=4, num_kv_heads=1, head_dim=256, page_size=16, seed=93)
+
+
+ODD = list(_odd_cases())
+ODD_IDS = [n for n, _ in ODD]
+
+
+def _check_padded_cache(new_cache, before, b):
+    """Rows the step wrote: the pool's bytes in the first 2*Hkv heads, zeros in the padding heads; every other row as
+    it was (the padding heads keep their fill)."""
+    Hkv, page = b.meta["num_kv_heads"], b.meta["page_size"]
+    P = b.kv_pages.shape[0]
+    got = new_cache.view(torch.uint8).reshape(P, page, -1, new_cache.shape[-1]).cpu()
+    old = before.view(torch.uint8).reshape(got.shape).cpu()
+    pool = b.kv_pages.view(torch.uint8).cpu()
+    assert torch.equal(got[:, :, : 2 * Hkv], pool), "page write: live heads"
+    written = torch.zeros(P, page, dtype=torch.bool)
+    tab = b.block_tables.cpu()
+    for s, (ql, kl) in enumerate(zip(b.meta["q_lens"], b.meta["kv_lens"])):
+        for pos in range(kl - ql, kl):
+            written[int(tab[s, pos // page]), pos % page] = True
+    assert got.shape[2] == 2 * Hkv + 2
+    assert torch.count_nonzero(got[:, :, 2 * Hkv :][written]) == 0, "padding heads of written rows are zeros"
+    assert torch.equal(got[:, :, 2 * Hkv :][~written], old[:, :, 2 * Hkv :][~written]), "other rows untouched"
+
+
+@pytest.mark.parametrize("name,b", ODD, ids=ODD_IDS)
+def test_oracle_v3_with_padded_combined_heads(name, b):
+    keys, values, cache, tab, dist = to_v3_inputs(b)
+    assert cache.shape[2] * cache.shape[3] == 2 * b.meta["num_kv_heads"] + 2 and cache.shape[3] == 4
+    out, new_cache = v3_reference(b.queries, keys, values, cache, b.context_lens, tab, b.query_start_loc, dist,
+                                  softmax_scale=b.softmax_scale, sliding_window=b.sliding_window)
+    np.testing.assert_allclose(out, dense_reference(*b.args(), **b.kwargs()), atol=1e-12)
+    _check_padded_cache(new_cache, cache, b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,b", ODD, ids=ODD_IDS)
+def test_cuda_e4m3_with_an_odd_number_of_kv_heads(rpa_lib, name, b):
+    import ejkernel_b200 as ej
+    from tests.helpers import run_cuda, status_word
+
+    bc = b.to("cuda")
+    want, wb = dense_reference(*b.args(), **b.kwargs(), return_weight_bound=True)
+    out = run_cuda(bc)  # the plain operator on the dense pool
+    assert status_word(bc) == 0
+    _within(out, want, wb, b.total_tokens)
+    keys, values, cache, tab, dist = to_v3_inputs(bc)
+    before = cache.clone()
+    out3, new_cache = ej.ragged_page_attention_v3(bc.queries, keys, values, cache, bc.context_lens, tab, bc.query_start_loc,
+                                                  dist, softmax_scale=b.softmax_scale, sliding_window=b.sliding_window)
+    torch.cuda.synchronize()
+    _within(out3, want, wb, b.total_tokens)
+    _check_padded_cache(new_cache, before, b)
