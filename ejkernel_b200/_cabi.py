@@ -42,6 +42,7 @@ EXPORTS = (
     "ejk_rpa_launch_static_scratch",
     "ejk_rpa_v3_launch",
     "ejk_page_attention_launch",
+    "ejk_rpa_stream_probe",
 )
 
 
@@ -160,6 +161,8 @@ def load() -> ctypes.CDLL:
     lib.ejk_rpa_profile_read.argtypes = [POINTER(c_float), POINTER(c_float), POINTER(c_float)]
     lib.ejk_rpa_profile_read_kernels.restype = c_int
     lib.ejk_rpa_profile_read_kernels.argtypes = [POINTER(c_float)] * 4
+    lib.ejk_rpa_stream_probe.restype = c_int
+    lib.ejk_rpa_stream_probe.argtypes = [c_void_p, c_size_t, c_void_p, c_void_p]
     _lib = lib
     return lib
 
@@ -208,6 +211,49 @@ def profile_read_kernels() -> tuple[float, float, float, float]:
     v = [c_float(0) for _ in range(4)]
     check(load().ejk_rpa_profile_read_kernels(*[ctypes.byref(x) for x in v]), "profile_read_kernels")
     return tuple(x.value for x in v)
+
+
+# (KB per copy, slots per CTA, CTAs per SM) the probe is tried with.  Measured on a B200 over a 4 GiB buffer, GB/s:
+# 64/1/2 7360-7420, 32/1/4 7380, 32/2/3 7280, 64/3/1 7265, 32/3/2 (the split-KV kernel's own shape) 7235-7255,
+# 16/3/4 7200, 16/4/3 7050, 32/6/1 6810, 16/6/2 6770, 8/6/4 6780, 16/12/1 and 8/12/2 6280, 4/12/4 6165: few large
+# copies in flight beat many small ones.
+PROBE_SHAPES = ((64, 1, 2), (32, 1, 4), (32, 3, 2))
+
+
+def stream_probe_gbs(tensor, passes: int = 5) -> float:
+    """Read-only streaming rate of the tensor's device in GB/s: the best of ``PROBE_SHAPES``, each timed over ``passes``
+    passes of ``ejk_rpa_stream_probe`` over the tensor's bytes (use one far larger than the L2) after one untimed
+    pass.  The practical ceiling of the split-KV kernel on that device."""
+    import torch
+
+    if not tensor.is_cuda or not tensor.is_contiguous():
+        raise ValueError("stream_probe_gbs needs a contiguous CUDA tensor")
+    nbytes = tensor.numel() * tensor.element_size() // 65536 * 65536
+    sink = torch.zeros(2, dtype=torch.int32, device=tensor.device)
+    lib = load()
+    with torch.cuda.device(tensor.device):
+        st = torch.cuda.current_stream(tensor.device)
+        run = lambda: check(lib.ejk_rpa_stream_probe(tensor.data_ptr(), nbytes, sink.data_ptr(), st.cuda_stream), "stream_probe")
+        old = [get_option(k) for k in ("probe_chunk_kb", "probe_slots", "probe_ctas")]
+        best = 0.0
+        try:
+            for shape in PROBE_SHAPES:
+                for k, v in zip(("probe_chunk_kb", "probe_slots", "probe_ctas"), shape):
+                    set_option(k, v)
+                run()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(st)
+                for _ in range(passes):
+                    run()
+                e1.record(st)
+                e1.synchronize()
+                best = max(best, nbytes * passes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+        finally:
+            for k, v in zip(("probe_chunk_kb", "probe_slots", "probe_ctas"), old):
+                set_option(k, v)
+        if int(sink[1].item()) != 0:
+            raise RpaLibraryError("stream_probe: a wait inside the probe ran out")
+        return best
 
 
 def decode_status(word: int) -> list[str]:

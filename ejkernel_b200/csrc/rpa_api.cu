@@ -28,7 +28,9 @@ struct Options {
   // 256 x 8 tokens at kv 128..8192 1.45 -> 1.18 ms, 256 x 12 tokens 2.16 -> 1.22 ms; at 17-31 rows it
   // depends on the lengths (faster at kv <= 1024, 7 % slower on long ragged contexts).
   std::atomic<int> prefill_rows{32};
-  std::atomic<int> prefill_share{125};  // see Params::prefill_share; 0 = the tile kernel always uses every SM
+  std::atomic<int> prefill_share{125};
+  // shape of the read-only streaming probe (0 = its defaults): KB per copy, slots per CTA, CTAs per SM
+  std::atomic<int> probe_chunk_kb{0}, probe_slots{0}, probe_ctas{0};  // see Params::prefill_share; 0 = the tile kernel always uses every SM
 };
 Options g_opt;
 thread_local int t_last_launches = 0;
@@ -540,6 +542,15 @@ int ejk_rpa_set_option(const char* name, int value) {
   } else if (!std::strcmp(name, "prefill_share")) {
     if (value < 0 || value > 1000) return EJK_RPA_E_ARG;
     g_opt.prefill_share = value;
+  } else if (!std::strcmp(name, "probe_chunk_kb")) {
+    if (value < 0 || value > 64 || (value & (value - 1))) return EJK_RPA_E_ARG;  // a power of two, at most 64
+    g_opt.probe_chunk_kb = value;
+  } else if (!std::strcmp(name, "probe_slots")) {
+    if (value < 0 || value > 12) return EJK_RPA_E_ARG;
+    g_opt.probe_slots = value;
+  } else if (!std::strcmp(name, "probe_ctas")) {
+    if (value < 0 || value > 8) return EJK_RPA_E_ARG;
+    g_opt.probe_ctas = value;
   } else {
     return EJK_RPA_E_ARG;
   }
@@ -560,11 +571,29 @@ int ejk_rpa_get_option(const char* name, int* value) {
   else if (!std::strcmp(name, "wait_ms")) *value = g_opt.wait_ms;
   else if (!std::strcmp(name, "prefill_rows")) *value = g_opt.prefill_rows;
   else if (!std::strcmp(name, "prefill_share")) *value = g_opt.prefill_share;
+  else if (!std::strcmp(name, "probe_chunk_kb")) *value = g_opt.probe_chunk_kb;
+  else if (!std::strcmp(name, "probe_slots")) *value = g_opt.probe_slots;
+  else if (!std::strcmp(name, "probe_ctas")) *value = g_opt.probe_ctas;
   else return EJK_RPA_E_ARG;
   return 0;
 }
 
 int ejk_rpa_last_launch_count(void) { return t_last_launches; }
+
+int ejk_rpa_stream_probe(const void* src, size_t bytes, void* sink, void* stream) {
+  t_last_launches = 0;
+  if (!src || !sink) return EJK_RPA_E_NULL;
+  if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(sink) & 7)) return EJK_RPA_E_ALIGN;
+  if (bytes < 65536) return EJK_RPA_E_ARG;
+  const DeviceInfo* d = device_info();
+  if (!d || d->cc_major != 10) return EJK_RPA_E_DEVICE;
+  cudaError_t e = launch_stream_probe(src, bytes, static_cast<unsigned*>(sink), d->sm_count, g_opt.wait_ms,
+                                      g_opt.probe_chunk_kb, g_opt.probe_slots, g_opt.probe_ctas,
+                                      static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  t_last_launches = 1;
+  return 0;
+}
 
 int ejk_rpa_profile_read_kernels(float* plan_ms, float* prefill_ms, float* splitkv_ms, float* merge_ms) {
   if (!t_prof.recorded) return EJK_RPA_E_ARG;

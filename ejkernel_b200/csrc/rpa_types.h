@@ -152,6 +152,9 @@ inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, 
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 cudaError_t launch_merge(const Params& p, int dtype, int n_sm, cudaStream_t stream, bool pdl);
+// read-only streaming probe (rpa_stream_probe.cu): reads `bytes` (rounded down to whole 32 KiB chunks) into shared memory
+cudaError_t launch_stream_probe(const void* src, size_t bytes, unsigned* sink, int n_sm, int wait_ms, int chunk_kb, int slots,
+                                int ctas_per_sm, cudaStream_t stream);
 cudaError_t launch_kv_update(const void* k_new, const void* v_new, void* cache, const int32_t* kv_lens,
                              const int32_t* block_tables, const int32_t* query_start_loc, const int32_t* num_seqs,
                              int32_t* status, int T, int S_max, int pages_per_seq, int num_pages, int page_size, int Hkv,

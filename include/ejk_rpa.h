@@ -240,6 +240,9 @@ EJK_RPA_API int ejk_rpa_launch_static_scratch(const void* queries, const void* k
  *                EJK_RPA_ST_TIMEOUT (no fault, no hang; the context stays usable)
  *   "wait_ms"    wall-time bound, in milliseconds, of every wait inside a kernel (default 2000)
  *   "profile"    1 = record CUDA events around each kernel of a launch (see ejk_rpa_profile_read)
+ *   "probe_chunk_kb", "probe_slots", "probe_ctas"  shape of ejk_rpa_stream_probe: KB per copy (a power of two up to 64),
+ *                copies in flight per CTA (up to 12), CTAs per SM (up to 8); 0 = the defaults 32 / 3 / 2, the shape the
+ *                split-KV kernel itself runs with
  * Returns 0, or EJK_RPA_E_ARG for an unknown name.  Counterpart of the reference's
  * EJKERNEL_* environment switches (ejkernel/ops/config/selection.py:328). */
 EJK_RPA_API int ejk_rpa_set_option(const char* name, int value);
@@ -248,6 +251,14 @@ EJK_RPA_API int ejk_rpa_get_option(const char* name, int* value);
 /* Number of kernels the last ejk_rpa_launch on this thread enqueued (host-side counter, for
  * benchmark bookkeeping). */
 EJK_RPA_API int ejk_rpa_last_launch_count(void);
+
+/* Diagnostic: enqueue one read-only pass over `bytes` of device memory at `src` (16-byte aligned, at least 64 KiB; rounded down to
+ * whole 32 KiB copies) with the bulk asynchronous copies the split-KV kernel gathers KV pages with, two
+ * CTAs per SM, nothing done with the data.  Timed with events around it, it gives the practical ceiling of that kernel
+ * on this device: a copy benchmark reads and writes, a read-only stream can be faster.  `sink` points to 8 bytes of
+ * device memory the caller zeroed: word 1 is set to 1 if a wait inside the probe ran out (option "wait_ms").  No
+ * reference counterpart. */
+EJK_RPA_API int ejk_rpa_stream_probe(const void* src, size_t bytes, void* sink, void* stream);
 
 /* With option "profile" = 1, waits for the calling thread's last launch and returns the device
  * time of its planner, gather/attention and merge kernels in milliseconds (null pointers are

@@ -146,3 +146,25 @@ def test_product_code_never_imports_the_oracle():
     for path in list((ROOT / "ejkernel_b200").rglob("*.py")):
         text = path.read_text()
         assert "oracle" not in re.sub(r'""".*?"""', "", text, flags=re.S).replace("# oracle", ""), path
+
+
+@pytest.mark.gpu
+def test_stream_probe_reads_a_buffer_and_refuses_bad_arguments(rpa_lib):
+    """The read-only streaming probe (the practical ceiling of the split-KV kernel): runs, reports no expired wait and a
+    plausible rate on a buffer larger than the L2; null, misaligned and too-short arguments get negative codes."""
+    import torch
+
+    from ejkernel_b200 import _cabi
+
+    buf = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    buf.random_(0, 255)
+    rate = _cabi.stream_probe_gbs(buf, passes=3)
+    assert 1000.0 < rate < 12000.0, rate
+    sink = torch.zeros(2, dtype=torch.int32, device="cuda")
+    lib = _cabi.load()
+    assert lib.ejk_rpa_stream_probe(None, 1 << 20, sink.data_ptr(), None) == -1
+    assert lib.ejk_rpa_stream_probe(buf.data_ptr() + 4, 1 << 20, sink.data_ptr(), None) == -8
+    assert lib.ejk_rpa_stream_probe(buf.data_ptr(), 100, sink.data_ptr(), None) == -6
+    assert lib.ejk_rpa_last_launch_count() == 0
+    torch.cuda.synchronize()
+    assert int(sink.abs().sum()) == 0
