@@ -84,7 +84,7 @@ int check_shape(const ejk_rpa_shape* s) {
   if ((long long)s->total_tokens * s->num_q_heads > 0x3fffffffLL || s->max_num_seqs > 0x00ffffff) return EJK_RPA_E_SHAPE;
   if (s->kv_dtype != 0 && s->kv_dtype != EJK_RPA_E4M3) return EJK_RPA_E_DTYPE;
   if (s->kv_dtype == EJK_RPA_E4M3) {
-    if (s->head_dim != 128 && s->head_dim != 256) return EJK_RPA_E_HEAD_DIM;
+    // head_dim 64 only in the v3 cache, whose rows are padded to 128 bytes (launch_impl checks the row stride)
     if (s->page_size < 8 || s->page_size % 8 != 0) return EJK_RPA_E_SHAPE;
   }
   return 0;
@@ -121,7 +121,9 @@ WorkspaceLayout layout_for(const ejk_rpa_shape& s, int n_sm) {
   L.part_ml_off = off;
   off = align_up(off + (size_t)L.max_slots * s.num_kv_heads * L.rows_per_tile * sizeof(float2), 256);
   L.part_o_off = off;
-  off = align_up(off + (size_t)L.max_slots * s.num_kv_heads * L.rows_per_tile * s.head_dim * sizeof(float), 256);
+  // an e4m3 cache of head_dim 64 is attended as head_dim 128 (its rows are padded to 128 bytes): partials are that wide
+  const int d_part = (s.kv_dtype == EJK_RPA_E4M3 && s.head_dim == 64) ? 128 : s.head_dim;
+  off = align_up(off + (size_t)L.max_slots * s.num_kv_heads * L.rows_per_tile * d_part * sizeof(float), 256);
   L.total = off;
   {
     const int nt = prefill_rows_per_item(s.head_dim) / kPrefillRows;
@@ -279,7 +281,15 @@ static int launch_impl(const void* queries, const void* kv_pages, const void* va
   p.Hkv = s.num_kv_heads;
   p.G = s.num_q_heads / s.num_kv_heads;
   p.D = s.head_dim;
+  p.Dq = s.head_dim;
   p.Dkv = kv_dim > 0 ? kv_dim : s.head_dim;
+  if (s.kv_dtype == EJK_RPA_E4M3 && s.head_dim == 64) {
+    // 64 e4m3 bytes are half a 128-byte swizzle row: served only where the cache pads the row to 128 bytes (the v3
+    // layout), as head_dim 128 with the queries' upper half zero; the padding lanes of K meet those zeros, those of
+    // V land in output columns that are not stored
+    if (p.Dkv != 128) return EJK_RPA_E_HEAD_DIM;
+    p.D = 128;
+  }
   p.C2 = kv_heads_alloc > 0 ? kv_heads_alloc : 2 * s.num_kv_heads;
   p.rows_per_tile = L.rows_per_tile;
   p.max_units = L.max_units;

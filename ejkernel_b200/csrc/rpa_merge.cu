@@ -135,10 +135,12 @@ __global__ void __launch_bounds__(kMergeWarps * 32) rpa_merge_kernel(const Param
       for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
     }
     sc = (l_fin > 0.f) ? sc * p.out_scale / l_fin : 0.f;  // out_scale: v_scale of the v3 operator, else 1
-    T* dst = out + ((size_t)(mi.q_start + qt) * p.Hq + hq) * D + lane * VPL;
+    T* dst = out + ((size_t)(mi.q_start + qt) * p.Hq + hq) * p.Dq + lane * VPL;
+    if (lane * VPL < p.Dq) {  // p.Dq < D: the output row is narrower than the partials (see Params::Dq)
 #pragma unroll
-    for (int i = 0; i < VPL; i += 2) {
-      *reinterpret_cast<uint32_t*>(dst + i) = Mma<T>::pack(acc[i] * sc, acc[i + 1] * sc);
+      for (int i = 0; i < VPL; i += 2) {
+        *reinterpret_cast<uint32_t*>(dst + i) = Mma<T>::pack(acc[i] * sc, acc[i + 1] * sc);
+      }
     }
   }
 }

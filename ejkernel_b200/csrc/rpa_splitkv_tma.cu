@@ -234,11 +234,11 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
             const int r = cidx / QCH, ch = cidx % QCH;
             const int R = u.row0 + r;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (R < rows_total) {
+            if (R < rows_total && ch * 8 < p.Dq) {  // p.Dq < D: a row of queries is narrower than the cache row, the rest is 0
               const int qt = R / G, g = R - qt * G;
               v = __ldg(reinterpret_cast<const uint4*>(
                   reinterpret_cast<const uint8_t*>(p.q) +
-                  ((size_t)(u.q_start + qt) * p.Hq + h * G + g) * D * sizeof(T) + ch * 16));
+                  ((size_t)(u.q_start + qt) * p.Hq + h * G + g) * p.Dq * sizeof(T) + ch * 16));
             }
             if constexpr (KV8 == 2) {
               // queries / q_scale, saturated to the e4m3 range and rounded to e4m3 (_kernel.py:249-254): 8 bytes
@@ -823,8 +823,9 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
             const int qt = R / G, g = R - qt * G;
             const float scl = row_scale[r];
             const float2 v = *reinterpret_cast<float2*>(&obuf[r * D + d]);
-            *reinterpret_cast<uint32_t*>(out + ((size_t)(u.q_start + qt) * p.Hq + h * G + g) * D + d) =
-                Mma<T>::pack(v.x * scl, v.y * scl);
+            if (d < p.Dq)
+              *reinterpret_cast<uint32_t*>(out + ((size_t)(u.q_start + qt) * p.Hq + h * G + g) * p.Dq + d) =
+                  Mma<T>::pack(v.x * scl, v.y * scl);
           }
         } else {
           float* po = p.part_o + ((size_t)u.slot * Hkv + h) * RT * D;
@@ -915,10 +916,12 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
                   for (int i = 0; i < p.num_sinks; ++i) l_fin += fast_exp2(sk[i] * kLog2e - mf);
                 }
                 scl = (l_fin > 0.f) ? scl * p.out_scale / l_fin : 0.f;  // out_scale: v_scale of the v3 operator, else 1
-                T* dst = out + ((size_t)(u.q_start + qt) * p.Hq + hq) * D + lane * VPL;
+                T* dst = out + ((size_t)(u.q_start + qt) * p.Hq + hq) * p.Dq + lane * VPL;
+                if (lane * VPL < p.Dq) {
 #pragma unroll
-                for (int i = 0; i < VPL; i += 2)
-                  *reinterpret_cast<uint32_t*>(dst + i) = Mma<T>::pack(accm[i] * scl, accm[i + 1] * scl);
+                  for (int i = 0; i < VPL; i += 2)
+                    *reinterpret_cast<uint32_t*>(dst + i) = Mma<T>::pack(accm[i] * scl, accm[i + 1] * scl);
+                }
               }
             }
           }
@@ -936,7 +939,7 @@ rpa_splitkv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_co
     if (*abort_flag) flags |= EJK_RPA_ST_TIMEOUT;
   }
   if (flags && p.status) atomicOr(reinterpret_cast<unsigned*>(p.status), flags);
-  zero_tail_rows(p.out, p.header[kHdrTailStart], p.T, (size_t)p.Hq * D * sizeof(T));
+  zero_tail_rows(p.out, p.header[kHdrTailStart], p.T, (size_t)p.Hq * p.Dq * sizeof(T));
   // In a mixed batch this grid is a programmatic dependent of the prefill-tile grid and never waited for it
   // (the two write different rows).  Whatever follows in the stream, though, is only ordered after THIS grid:
   // one thread per CTA now waits for the prefill grid, so this grid cannot complete before it, and a later

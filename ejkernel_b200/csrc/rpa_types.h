@@ -98,6 +98,8 @@ struct Params {
   int32_t prefill_item_rows; // rows one prefill work item covers (128 per tile, 1 or 2 tiles per CTA)
   int32_t Dkv;               // elements between consecutive combined heads of kv_pages (head_dim, or the padded
                              // head_dim of a v3 cache)
+  int32_t Dq;                // elements of a row of queries / out: D, except for an e4m3 v3 cache of head_dim 64, whose rows
+                             // are padded to 128 bytes and are attended as head_dim 128 (the queries' upper half reads as zeros)
   int32_t C2;                // combined heads per token row in memory: 2 * Hkv, or more in a v3 cache that pads them to
                              // a multiple of the packing (four e4m3 heads per 32-bit word)
   int32_t sort_items;        // 1: split-KV work items are queued longest first, 0: in sequence order

@@ -88,8 +88,8 @@ def ragged_page_attention_v3(
     if kv_cache.dtype not in (queries.dtype, FP8) or keys.dtype != kv_cache.dtype or values.dtype != kv_cache.dtype:
         raise NotImplementedError("keys, values and kv_cache must share one dtype: that of the queries, or float8_e4m3fn")
     fp8 = kv_cache.dtype == FP8
-    if fp8 and (D not in (128, 256) or page_size % 8):
-        raise NotImplementedError("an e4m3 KV cache needs head_dim 128 or 256 and a page size that is a multiple of 8")
+    if fp8 and (D not in (64, 128, 256) or page_size % 8):
+        raise NotImplementedError("an e4m3 KV cache needs head_dim 64, 128 or 256 and a page size that is a multiple of 8")
     for name, sc in (("q_scale", q_scale), ("k_scale", k_scale), ("v_scale", v_scale)):
         if sc is not None and not (sc > 0.0 and sc < float("inf")):
             raise ValueError(f"{name} must be positive and finite")

@@ -84,8 +84,9 @@ typedef struct ejk_rpa_shape {
   int32_t dtype;         /* EJK_RPA_BF16 | EJK_RPA_F16: queries and out (and the cache, unless kv_dtype says otherwise) */
   int32_t kv_dtype;      /* 0 = the cache has `dtype`; EJK_RPA_E4M3 = kv_pages / kv_cache hold e4m3 bytes (the fp8 KV cache of
                             the v3 operator, ejkernel/kernels/_xla/ragged_page_attention_v3/_kernel.py:45-57,157-159,249-291).
-                            Needs head_dim 128 or 256 and a page_size that is a multiple of 8; every sequence is then
-                            served by the split-KV kernel.  The v3 cache pads its combined-head axis to a multiple of four
+                            Needs head_dim 128 or 256 and a page_size that is a multiple of 8 (head_dim 64 only through
+                            ejk_rpa_v3_launch, whose cache pads a row to 128 bytes: it is attended as head_dim 128 with
+                            the queries' upper half zero); every sequence is then served by the split-KV kernel.  The v3 cache pads its combined-head axis to a multiple of four
                             (the reference packs four e4m3 heads per 32-bit word), i.e. by two heads when num_kv_heads is
                             odd: ejk_rpa_v3_launch derives that stride itself, ejk_rpa_launch reads a dense
                             [P, page, 2*num_kv_heads, D] pool. */

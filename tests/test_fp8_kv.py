@@ -285,3 +285,49 @@ def test_cuda_e4m3_with_an_odd_number_of_kv_heads(rpa_lib, name, b):
     torch.cuda.synchronize()
     _within(out3, want, wb, b.total_tokens)
     _check_padded_cache(new_cache, before, b)
+
+
+# ---- head_dim 64: the v3 cache pads a row to 128 bytes, and the operator attends it as head_dim 128 with the upper half
+# of every query zero (the padding lanes of K meet zeros; those of V land in output columns that are not stored).  The
+# plain operator's dense e4m3 pool has 64-byte rows, half a swizzle row: refused. ----
+def _d64_cases():
+    mk = lambda ql, kl, **kw: make_ragged_batch(ql, kl, kv_dtype=FP8, **kw)
+    yield "d64", mk([1, 1, 12, 1], [700, 20, 130, 3000], num_q_heads=8, num_kv_heads=2, head_dim=64, page_size=16, seed=95)
+    yield "d64_mqa_window", mk([1, 30], [900, 200], num_q_heads=8, num_kv_heads=1, head_dim=64, page_size=32, seed=96,
+                               sliding_window=300, logits_soft_cap=20.0)
+
+
+D64 = list(_d64_cases())
+
+
+@pytest.mark.parametrize("name,b", D64, ids=[n for n, _ in D64])
+def test_oracle_v3_e4m3_head_dim_64(name, b):
+    keys, values, cache, tab, dist = to_v3_inputs(b)
+    assert cache.shape[-1] == 128
+    out, _ = v3_reference(b.queries, keys, values, cache, b.context_lens, tab, b.query_start_loc, dist,
+                          softmax_scale=b.softmax_scale, sliding_window=b.sliding_window, logits_soft_cap=b.logits_soft_cap)
+    np.testing.assert_allclose(out, dense_reference(*b.args(), **b.kwargs()), atol=1e-12)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("q_scale", [None, 0.05])
+@pytest.mark.parametrize("name,b", D64, ids=[n for n, _ in D64])
+def test_cuda_v3_e4m3_head_dim_64(rpa_lib, name, b, q_scale):
+    import ejkernel_b200 as ej
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import ragged_page_attention
+
+    bc = b.to("cuda")
+    keys, values, cache, tab, dist = to_v3_inputs(bc)
+    kw = dict(softmax_scale=b.softmax_scale, sliding_window=b.sliding_window, logits_soft_cap=b.logits_soft_cap,
+              q_scale=q_scale, v_scale=0.75)
+    out, new_cache = ej.ragged_page_attention_v3(bc.queries, keys, values, cache, bc.context_lens, tab, bc.query_start_loc,
+                                                 dist, **kw)
+    torch.cuda.synchronize()
+    ck, cv, cc, ctab, cdist = to_v3_inputs(b)
+    want, want_cache, wb = v3_reference(b.queries, ck, cv, cc, b.context_lens, ctab, b.query_start_loc, cdist, **kw,
+                                        return_weight_bound=True)
+    _within(out, want, wb, b.total_tokens)
+    # rows the step wrote equal the oracle's (data, zeroed padding); the others keep their fill
+    assert torch.equal(new_cache.view(torch.uint8).cpu(), want_cache.view(torch.uint8))
+    with pytest.raises(NotImplementedError):
+        ragged_page_attention(*bc.args(), softmax_scale=b.softmax_scale)  # dense pool with 64-byte rows
