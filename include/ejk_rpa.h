@@ -10,7 +10,10 @@
  *   ejkernel/callib/_triton_call.py:737-757 (operands in, results out, XLA's stream, no host sync).
  *
  * Conventions
- *   - every pointer is a DEVICE pointer on the current CUDA device unless stated otherwise;
+ *   - every pointer is a DEVICE pointer on the current CUDA device unless stated otherwise; `queries` and `out` of the
+ *     launch entry points may also point to page-locked host memory that is mapped into the device's address space
+ *     (cudaHostAlloc / cudaHostRegister under unified addressing): the kernels read each query row once per work item
+ *     and write each output row once, so host-resident queries and results need no staging copies;
  *   - tensors are dense row-major:
  *       queries          [total_tokens, num_q_heads, head_dim]
  *       kv_pages         [num_pages, page_size, 2*num_kv_heads, head_dim]  (K_h at 2h, V_h at 2h+1)

@@ -803,3 +803,26 @@ def test_opt_in_status_check_raises_when_outputs_are_invalid(rpa_lib, monkeypatc
         _cabi.set_option("wait_ms", old)
     out = ragged_page_attention(*b.args(), softmax_scale=b.softmax_scale)  # raises nothing
     assert_parity(out, oracle(b), b.total_tokens, what="after a timed-out call")
+
+
+def test_queries_and_output_in_pinned_host_memory(rpa_lib):
+    """Page-locked host memory is mapped into the device's address space: the kernels can read the query rows from it
+    and write the output rows to it, bit for bit what they do with device buffers (mixed batch: split-KV tiles, tensor
+    tiles and the zero-filled padding rows all store to the host buffer)."""
+    from ejkernel_b200.kernels._cuda.ragged_page_attention import RpaWorkspace, ragged_page_attention_into
+    from ejkernel_b200.kernels._cuda.ragged_page_attention._interface import _shape_of
+
+    b = make_ragged_batch([1, 1, 200, 3, 1], [5000, 64, 900, 77, 2500], num_q_heads=16, num_kv_heads=4, head_dim=128,
+                          page_size=16, seed=97, pad_query_rows=5)
+    bc = b.to("cuda")
+    ws = RpaWorkspace(_shape_of(bc.queries, bc.kv_pages, bc.block_tables), bc.queries.device)
+    dev_out = torch.full_like(bc.queries, float("nan"))
+    ragged_page_attention_into(dev_out, ws, *bc.args(), softmax_scale=b.softmax_scale)
+    host_q = b.queries.clone().pin_memory()
+    host_out = torch.full(b.queries.shape, float("nan"), dtype=b.queries.dtype).pin_memory()
+    ragged_page_attention_into(host_out, ws, host_q, *bc.args()[1:], softmax_scale=b.softmax_scale)
+    torch.cuda.synchronize()
+    assert int(ws.status.item()) == 0
+    assert torch.equal(host_out, dev_out.cpu())
+    assert_parity(host_out, oracle(b), b.total_tokens, what="pinned host queries and output")
+    assert torch.count_nonzero(host_out[b.total_tokens:]) == 0
