@@ -108,3 +108,72 @@ def test_constant_value_rows_come_back_exactly(rpa_lib):
     G = b.meta["num_q_heads"] // Hkv
     want = vals.repeat_interleave(G)[None, :, None].expand_as(out)
     assert (out.float() - want.float()).abs().max().item() <= 2.0**-7 * Hkv  # one bf16 ulp of the largest value
+
+
+def _float32_restatement_on_device(b: RaggedBatch) -> torch.Tensor:
+    """Every sequence of a device batch with plain PyTorch float32 operations on the GPU: gather the sequence's pages,
+    two einsums, scale, soft cap, causal / window mask, softmax -- the operator's definition
+    (ejkernel/kernels/_xla/ragged_page_attention/_xla_impl_fwd.py:105-177), independent of the CUDA kernels.  It is held
+    against the CPU oracle on sampled sequences below, and the CUDA output is held against it on ALL of them."""
+    m = b.meta
+    page, Hkv = m["page_size"], m["num_kv_heads"]
+    Hq, D = b.queries.shape[1], b.queries.shape[2]
+    G = Hq // Hkv
+    cu = b.query_start_loc.cpu().tolist()
+    out = torch.zeros(b.queries.shape, dtype=torch.float32, device=b.queries.device)
+    for s, (ql, kl) in enumerate(zip(m["q_lens"], m["kv_lens"])):
+        if ql == 0:
+            continue
+        ids = b.block_tables[s, : cdiv(kl, page)].long()
+        kv = b.kv_pages[ids].reshape(-1, 2 * Hkv, D)[:kl].float()
+        k, v = kv[:, 0::2], kv[:, 1::2]  # [kl, Hkv, D]
+        q = b.queries[cu[s] : cu[s] + ql].float().view(ql, Hkv, G, D)
+        logits = torch.einsum("qhgd,khd->hgqk", q, k) * b.softmax_scale
+        if b.logits_soft_cap is not None:
+            logits = b.logits_soft_cap * torch.tanh(logits / b.logits_soft_cap)
+        pos = (kl - ql + torch.arange(ql, device=q.device))[:, None]
+        key = torch.arange(kl, device=q.device)[None, :]
+        vis = key <= pos
+        if b.sliding_window is not None:
+            vis &= key > pos - b.sliding_window
+        logits = logits.masked_fill(~vis[None, None], float("-inf"))
+        p = torch.softmax(logits, dim=-1)
+        out[cu[s] : cu[s] + ql] = torch.einsum("hgqk,khd->qhgd", p, v).reshape(ql, Hq, D)
+        del kv, k, v, logits, p
+    return out
+
+
+def test_every_sequence_matches_a_float32_restatement_on_the_device(full):
+    """Full coverage at full size: the sampled comparison against the CPU oracle pins a plain-PyTorch float32
+    restatement that runs on the GPU, and the CUDA output is compared with that on every sequence of the workload."""
+    name, b, out = full
+    old_tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        ref = _float32_restatement_on_device(b)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old_tf32
+    torch.cuda.synchronize()
+    T = b.total_tokens
+    # (1) the restatement against the oracle on a sample (float32 against float32: tight)
+    S = len(b.meta["kv_lens"])
+    order = np.argsort(b.meta["kv_lens"])
+    seqs = sorted({int(order[0]), int(order[S // 2]), S - 1})
+    host = _sample_to_host(b, seqs)
+    want = dense_reference(*host.args(), **host.kwargs(), precision="fp32")
+    cu = b.query_start_loc.cpu().tolist()
+    got = torch.cat([ref[cu[s] : cu[s + 1]] for s in seqs]).cpu().numpy()
+    assert np.allclose(got, want, atol=2e-5, rtol=2e-4), (name, float(np.abs(got - want).max()))
+    # (2) the CUDA output against the restatement, every sequence, per sequence (the tight criterion scales with
+    # the rms of the expected rows, and short and long contexts differ tenfold)
+    ref_np = ref[:T].cpu().numpy().astype(np.float64)
+    out_np = out[:T].float().cpu().numpy()
+    worst = 0.0
+    for s in range(S):
+        if cu[s + 1] == cu[s]:
+            continue
+        r = compare(out_np[cu[s] : cu[s + 1]], ref_np[cu[s] : cu[s + 1]], atol=ATOL, rtol=RTOL)
+        assert r["finite"] and r["allclose"] and r["tight"] and r["max_rel_rms"] <= REL_RMS, (name, s, r)
+        worst = max(worst, r["max_rel_rms"])
+    assert torch.count_nonzero(out[T:]) == 0
+    print(f"{name}: {S} sequences, worst error / rms {worst:.4f}")
