@@ -2,7 +2,9 @@
 KV in seconds, so each workload is checked (a) against the oracle on a seeded sample of its
 sequences, whose pages are pulled out of the device pool, and (b) through size-independent
 properties: renumbering the pool's pages leaves the output bit-identical, a constant V comes back
-exactly, two runs agree bitwise, and a different split granularity agrees within tolerance."""
+exactly, two runs agree bitwise, and a different split granularity agrees within tolerance; and (c) on
+EVERY sequence against a plain-PyTorch float32 restatement of the operator that runs on the GPU and is
+itself held against the oracle on a sample."""
 
 import numpy as np
 import pytest
