@@ -33,7 +33,7 @@ static ffi::Error EjkRpaSm100Impl(cudaStream_t stream, ffi::AnyBuffer queries, f
   const auto td = block_tables.dimensions();
   if (qd.size() != 3 || kd.size() != 4 || td.size() != 2)
     return ffi::Error::InvalidArgument("ragged_page_attention: wrong operand ranks");
-  ejk_rpa_shape shape;
+  ejk_rpa_shape shape{};
   shape.total_tokens = static_cast<int32_t>(qd[0]);
   shape.num_q_heads = static_cast<int32_t>(qd[1]);
   shape.head_dim = static_cast<int32_t>(qd[2]);
@@ -47,6 +47,10 @@ static ffi::Error EjkRpaSm100Impl(cudaStream_t stream, ffi::AnyBuffer queries, f
     case ffi::F16: shape.dtype = EJK_RPA_F16; break;
     default: return ffi::Error::InvalidArgument("ragged_page_attention[cuda]: bf16 or f16 only");
   }
+  // the pool has the queries' dtype, or holds float8 e4m3 bytes
+  if (kv_pages.element_type() == ffi::F8E4M3FN) shape.kv_dtype = EJK_RPA_E4M3;
+  else if (kv_pages.element_type() != queries.element_type())
+    return ffi::Error::InvalidArgument("ragged_page_attention[cuda]: kv_pages must have the queries' dtype or be float8_e4m3fn");
   ejk_rpa_attrs attrs{};
   attrs.softmax_scale = softmax_scale;
   attrs.logits_soft_cap = logits_soft_cap;  // 0 = none
